@@ -1,0 +1,239 @@
+"""numpy front end of the CPU oracle (oracle/q4_oracle.c) and of the reference's own dequantiser
+compiled in place (oracle/_ref/libq4ref.so).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke check and by the CPU-baseline /
+reference arm of bench.py -- never by the shipped package.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+_REF = None
+
+u8p = C.POINTER(C.c_uint8)
+f32p = C.POINTER(C.c_float)
+i32p = C.POINTER(C.c_int32)
+u16p = C.POINTER(C.c_uint16)
+
+
+def build(ref_tree="/root/reference"):
+    """make -C oracle: the restatement always, _ref only when the reference tree is present."""
+    subprocess.run(["make", "-C", _HERE, "REF=" + ref_tree], check=True,
+                   stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        path = os.path.join(_HERE, "libq4oracle.so")
+        if not os.path.exists(path):
+            build()
+        L = C.CDLL(path)
+        L.q4o_u64.restype = C.c_uint64
+        L.q4o_u64.argtypes = [C.c_uint64] * 3
+        L.q4o_normal_f32.argtypes = [C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_void_p]
+        L.q4o_select.restype = C.c_uint32
+        L.q4o_select.argtypes = [C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32,
+                                 C.c_uint32, C.c_void_p, C.c_uint32]
+        L.q4o_f16_to_f32.restype = C.c_float
+        L.q4o_f16_to_f32.argtypes = [C.c_uint16]
+        L.q4o_f32_to_f16.restype = C.c_uint16
+        L.q4o_f32_to_f16.argtypes = [C.c_float]
+        L.q4o_f32_to_f16_n.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64]
+        L.q4o_f32_to_bf16.restype = C.c_uint16
+        L.q4o_f32_to_bf16.argtypes = [C.c_float]
+        L.q4o_quant_q8_0.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64]
+        L.q4o_dequant_q8_0.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p]
+        L.q4o_kv_token_bytes.restype = C.c_uint64
+        L.q4o_kv_token_bytes.argtypes = [C.c_uint32, C.c_uint32, C.c_int]
+        L.q4o_kv_write.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_int]
+        L.q4o_rope.argtypes = [C.c_void_p, C.c_uint32, C.c_int32, C.c_float]
+        L.q4o_rope_table.argtypes = [C.c_uint32, C.c_int32, C.c_uint32, C.c_float, C.c_void_p]
+        L.q4o_q_prep.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32,
+                                 C.c_uint32, C.c_uint32, C.c_int32, C.c_float, C.c_float,
+                                 C.c_uint32]
+        L.q4o_k_prep.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32,
+                                 C.c_int32, C.c_float, C.c_float, C.c_uint32]
+        L.q4o_attn.restype = C.c_int
+        L.q4o_attn.argtypes = [C.c_void_p] * 5 + [C.c_uint32] * 6 + [C.c_float, C.c_int,
+                                                                     C.c_void_p, C.c_uint32,
+                                                                     C.c_uint32, C.c_int, C.c_int]
+        L.q4o_attn_partial.restype = C.c_int
+        L.q4o_attn_partial.argtypes = [C.c_void_p] * 4 + [C.c_uint32] * 3 + [
+            C.c_float, C.c_int, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32]
+        L.q4o_lse_merge.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p,
+                                    C.c_void_p]
+        L.q4o_max_threads.restype = C.c_int
+        _LIB = L
+    return _LIB
+
+
+def ref_lib():
+    """The reference's q4_quant.c compiled in place (q4_dequant_row, q4_f16_to_f32); None when it
+    was never built (no reference tree and no prebuilt copy)."""
+    global _REF
+    if _REF is None:
+        path = os.path.join(_HERE, "_ref", "libq4ref.so")
+        if not os.path.exists(path):
+            return None
+        R = C.CDLL(path)
+        R.q4_f16_to_f32.restype = C.c_float
+        R.q4_f16_to_f32.argtypes = [C.c_uint16]
+        R.q4_dequant_row.restype = C.c_bool
+        R.q4_dequant_row.argtypes = [C.c_uint32, C.c_void_p, C.c_uint64, C.c_void_p]
+        _REF = R
+    return _REF
+
+
+Q4_T_Q8_0 = 8  # src/q4.h:26
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p) if a is not None else None
+
+
+def normal(seed, stream, n, offset=0):
+    out = np.empty(int(n), np.float32)
+    lib().q4o_normal_f32(seed, stream, offset, int(n), _p(out))
+    return out
+
+
+def select(seed, stream, ctx, width=2051, sink=4, recent=1024, nrand=1023):
+    out = np.empty(width, np.int32)
+    lib().q4o_select(seed, stream, ctx, sink, recent, nrand, _p(out), width)
+    return out
+
+
+def f32_to_f16(x):
+    x = np.ascontiguousarray(x, np.float32)
+    out = np.empty(x.shape, np.uint16)
+    lib().q4o_f32_to_f16_n(_p(x), _p(out), x.size)
+    return out
+
+
+def f32_to_bf16(x):
+    """RNE bfloat16 bits of fp32 values (numpy has no bf16)."""
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    return r
+
+
+def bf16_to_f32(b):
+    return (np.ascontiguousarray(b, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def quant_q8_0(x):
+    x = np.ascontiguousarray(x, np.float32)
+    assert x.size % 32 == 0
+    out = np.empty(x.size // 32 * 34, np.uint8)
+    lib().q4o_quant_q8_0(_p(x), _p(out), x.size)
+    return out
+
+
+def dequant_q8_0(b, n):
+    b = np.ascontiguousarray(b, np.uint8)
+    out = np.empty(int(n), np.float32)
+    lib().q4o_dequant_q8_0(_p(b), int(n), _p(out))
+    return out
+
+
+def ref_dequant_q8_0(b, n):
+    b = np.ascontiguousarray(b, np.uint8)
+    out = np.empty(int(n), np.float32)
+    assert ref_lib().q4_dequant_row(Q4_T_Q8_0, _p(b), int(n), _p(out))
+    return out
+
+
+def kv_token_bytes(n_kvh, hd, kind):
+    return int(lib().q4o_kv_token_bytes(n_kvh, hd, kind))
+
+
+def kv_write(x, kind):
+    """fp32 rows -> cache bytes in the reference layout (q8_0 / f16 / f32 for kind 2 / 1 / 0)."""
+    x = np.ascontiguousarray(x, np.float32)
+    nbytes = x.size // 32 * 34 if kind == 2 else x.size * (2 if kind == 1 else 4)
+    out = np.empty(nbytes, np.uint8)
+    lib().q4o_kv_write(_p(out), _p(x), x.size, kind)
+    return out
+
+
+def rope(x, n_rot, pos, base):
+    x = np.ascontiguousarray(x, np.float32).copy()
+    lib().q4o_rope(_p(x), n_rot, pos, base)
+    return x
+
+
+def rope_rows(x, n_rot, pos0, base):
+    """x: [n_tok][n_h][hd]; rotates every head of token t at position pos0+t."""
+    x = np.ascontiguousarray(x, np.float32).copy()
+    n_tok, n_h, hd = x.shape
+    for t in range(n_tok):
+        for h in range(n_h):
+            lib().q4o_rope(_p(x[t, h]), n_rot, pos0 + t, base)
+    return x
+
+
+def rope_table(n_rot, pos0, n_pos, base):
+    cs = np.empty((n_pos, n_rot // 2, 2), np.float32)
+    lib().q4o_rope_table(n_rot, pos0, n_pos, base, _p(cs))
+    return cs
+
+
+def q_prep(qg, wn, n_head, hd, n_rot, pos0, base, eps):
+    qg = np.ascontiguousarray(qg, np.float32)
+    n_tok = qg.size // (n_head * hd * 2)
+    q = np.empty((n_tok, n_head, hd), np.float32)
+    g = np.empty((n_tok, n_head, hd), np.float32)
+    lib().q4o_q_prep(_p(qg), _p(wn), _p(q), _p(g), n_head, hd, n_rot, pos0, base, eps, n_tok)
+    return q, g
+
+
+def k_prep(k, wn, n_kvh, hd, n_rot, pos0, base, eps):
+    k = np.ascontiguousarray(k, np.float32).copy()
+    n_tok = k.size // (n_kvh * hd)
+    lib().q4o_k_prep(_p(k), _p(wn), n_kvh, hd, n_rot, pos0, base, eps, n_tok)
+    return k
+
+
+def attn(q, kc, vc, gate, n_head, n_kvh, hd, n_tok, kv_base, max_kv, scale, kind, idx=None,
+         width=0, idx_kvh_stride=0, acc64=False, threads=1):
+    q = np.ascontiguousarray(q, np.float32)
+    out = np.empty(n_tok * n_head * hd, np.float32)
+    if gate is not None:
+        gate = np.ascontiguousarray(gate, np.float32)
+    if idx is not None:
+        idx = np.ascontiguousarray(idx, np.int32)
+    rc = lib().q4o_attn(_p(q), _p(kc), _p(vc), _p(gate), _p(out), n_head, n_kvh, hd, n_tok,
+                        kv_base, max_kv, scale, kind, _p(idx), width, idx_kvh_stride,
+                        int(acc64), threads)
+    assert rc == 0
+    return out.reshape(n_tok, n_head, hd)
+
+
+def attn_partial(q, kc, vc, n_head, n_kvh, hd, scale, kind, p0, p1, idx=None, idx_kvh_stride=0):
+    q = np.ascontiguousarray(q, np.float32)
+    part = np.empty((n_head, hd + 2), np.float32)
+    if idx is not None:
+        idx = np.ascontiguousarray(idx, np.int32)
+    rc = lib().q4o_attn_partial(_p(q), _p(kc), _p(vc), _p(part), n_head, n_kvh, hd, scale, kind,
+                                _p(idx), idx_kvh_stride, p0, p1)
+    assert rc == 0
+    return part
+
+
+def lse_merge(parts, n_head, hd, gate=None):
+    parts = np.ascontiguousarray(parts, np.float32)
+    n_parts = parts.size // (n_head * (hd + 2))
+    out = np.empty((n_head, hd), np.float32)
+    if gate is not None:
+        gate = np.ascontiguousarray(gate, np.float32)
+    lib().q4o_lse_merge(_p(parts), n_parts, n_head, hd, _p(gate), _p(out))
+    return out
+
+
+def max_threads():
+    return int(lib().q4o_max_threads())
