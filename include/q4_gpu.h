@@ -1,0 +1,225 @@
+/*
+ * q4_gpu.h -- C ABI of libq4gpu: the KV-cache + attention hot path of the q4 inference engine,
+ * implemented as hand-written CUDA for NVIDIA B200 (sm_100a).
+ *
+ * Two groups of entry points:
+ *
+ *  1. `q4_hip_*` -- the reference engine's own device ABI for this path, exported under the
+ *     same names, parameter lists and conventions (each cites the declaration it replaces in
+ *     the reference's src/q4.h and the implementation in src/q4_rocm.cu), so the C host
+ *     (src/q4_fwd.c, src/q4_mtp.c, src/q4_test.c) links against libq4gpu unchanged.  These
+ *     operate on caller-owned caches in the reference layout
+ *     [token][kv_head][hd/32 x {fp16 scale, 32 x int8}] (q8_0), or fp16 / fp32 rows.
+ *
+ *  2. `q4_gpu_*` -- additive entry points: a library-owned KV store with a B200-native planar
+ *     layout, fused K+V append, batched multi-session decode, bf16 queries, per-kv-head
+ *     selection lists, partial (m, l, acc) output + merge for sequence-sharded decode,
+ *     tensor-core prefill, and bulk prefix save/restore.
+ *
+ * Conventions (inherited from the reference, src/q4_rocm.cu:20-28,52-57,202-214):
+ *  - every operation returns bool: true = enqueued, false = rejected (bad argument, library not
+ *    initialised, launch failure); NULL / zero-size arguments return false and never crash;
+ *  - all work is asynchronous on ONE internal compute stream and ordered by it; only
+ *    q4_hip_h2d / q4_hip_d2h (outside capture), q4_hip_stream_sync and q4_hip_sync block;
+ *  - state is process-global and bound to one device (one process per GPU); the caller is
+ *    single-threaded with respect to launches;
+ *  - device pointers passed in are owned by the caller, scratch by the library;
+ *  - `kind` (the reference's `kv_f16` argument): 0 = fp32 rows, 1 = fp16 rows, 2 = q8_0;
+ *  - there is no CPU fallback: without a CUDA device q4_hip_init() returns false and every
+ *    other call fails.
+ */
+#ifndef Q4_GPU_H
+#define Q4_GPU_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ======================================================================================= */
+/* 1. Reference ABI (drop-in)                                                               */
+/* ======================================================================================= */
+
+/* src/q4.h:708-710, src/q4_rocm.cu:88-120.  Device = $Q4_GPU_DEVICE, else $LOCAL_RANK, else 0. */
+bool q4_hip_init(void);
+void q4_hip_shutdown(void);
+bool q4_hip_ok(void);
+
+/* src/q4.h:877-880, src/q4_rocm.cu:300-322.  h2d/d2h are enqueued on the compute stream and,
+ * outside graph capture, waited for. */
+void *q4_hip_malloc(size_t n);
+void q4_hip_free(void *p);
+bool q4_hip_h2d(void *d, const void *h, size_t n);
+bool q4_hip_d2h(void *h, const void *d, size_t n);
+/* src/q4.h:787-789, src/q4_rocm.cu:8417-8432 */
+bool q4_hip_d2h_async(void *h, const void *d, uint64_t n);
+bool q4_hip_h2d_async(void *d, const void *h, uint64_t n);
+bool q4_hip_stream_sync(void);
+/* src/q4.h:851,781, src/q4_rocm.cu:5656-5670 (n counts floats; copy is device-to-device) */
+bool q4_hip_copy(float *d, const float *s, uint64_t n);
+bool q4_hip_fill(float *d, float v, uint64_t n);
+/* src/q4.h:948-949, src/q4_rocm.cu:292-298 */
+void q4_hip_sync(void);
+void q4_hip_clear(void);
+
+/* Decode position word read by graph-captured kernels.  src/q4.h:686-688, src/q4_rocm.cu:6218-6227 */
+void q4_hip_pos_push(int32_t pos);
+int q4_hip_capturing(void);
+int q4_hip_pos_dev_ok(void);
+
+/* Stream capture of the compute stream.  src/q4.h:782-786, src/q4_rocm.cu:8162-8246 */
+int q4_hip_graph_begin(void);
+void *q4_hip_graph_end(void);
+uint32_t q4_hip_graph_nodes(void *exec);
+bool q4_hip_graph_launch(void *exec);
+void q4_hip_graph_free(void *exec);
+
+/* fp32 -> q8_0 blocks / fp16, n floats (n % 32 == 0 for q8).  src/q4.h:928-929,
+ * src/q4_rocm.cu:7208-7247.  q8_0 codes and scales are bit-exact with the IEEE evaluation of the
+ * reference quantiser. */
+bool q4_hip_f32_to_f16(void *dst_f16, const float *src, uint64_t n);
+bool q4_hip_f32_to_q8(void *dst_q8, const float *src, uint64_t n);
+/* fp32 -> fp16 at row `*pos` of dst_base (row stride in elements).  src/q4.h:696-697,
+ * src/q4_rocm.cu:7943-7958 */
+bool q4_hip_f32_to_f16_d(void *dst_base, uint32_t stride_elems, const float *src, uint64_t n);
+/* Append K and V (n floats each) at the token slot held in the device position word:
+ * destination = cache + pos * bpt.  src/q4.h:694-695, src/q4_rocm.cu:7962-8012 */
+bool q4_hip_kv_append_d(void *kcache, void *vcache, const float *k, const float *v, uint32_t n,
+                        uint32_t bpt, int kind);
+
+/* Per-head RMSNorm (+ weight), interleaved-pair RoPE on the first n_rot dims; q_prep also splits
+ * the packed [q | gate] projection.  `_n` = n_tok rows at pos0 + t; `_d` = position from the
+ * device word.  src/q4.h:689-693,895-905, src/q4_rocm.cu:6229-6343 */
+bool q4_hip_qsa_q_prep(const float *d_qg, const float *d_wn, float *d_q, float *d_g,
+                       uint32_t n_head, uint32_t hd, uint32_t n_rot, int32_t pos, float base,
+                       float eps);
+bool q4_hip_qsa_q_prep_n(const float *d_qg, const float *d_wn, float *d_q, float *d_g,
+                         uint32_t n_head, uint32_t hd, uint32_t n_rot, int32_t pos0, float base,
+                         float eps, uint32_t n_tok);
+bool q4_hip_qsa_q_prep_d(const float *qg, const float *wn, float *q, float *g, uint32_t n_head,
+                         uint32_t hd, uint32_t n_rot, float base, float eps);
+bool q4_hip_qsa_k_prep(float *d_k, const float *d_wn, uint32_t n_kvh, uint32_t hd, uint32_t n_rot,
+                       int32_t pos, float base, float eps);
+bool q4_hip_qsa_k_prep_n(float *d_k, const float *d_wn, uint32_t n_kvh, uint32_t hd,
+                         uint32_t n_rot, int32_t pos0, float base, float eps, uint32_t n_tok);
+bool q4_hip_qsa_k_prep_d(float *k, const float *wn, uint32_t n_kvh, uint32_t hd, uint32_t n_rot,
+                         float base, float eps);
+
+/* GQA attention over the cache; out = softmax(q.k * scale) v * sigmoid(gate).
+ *  decode    : one token over [0, n_kv)                      src/q4.h:621-624, q4_rocm.cu:8014-8022
+ *  decode_n  : token t over [0, min(kv_base+t+1, max_kv))    src/q4.h:906-909, q4_rocm.cu:7249-7305
+ *  decode_idx: token t over idx[t*width .. +width), -1 = skip  src/q4.h:911-915, q4_rocm.cu:7306-7364
+ * q, gate, out: [n_tok][n_head][hd] fp32 on the device.  hd in {32,64,128,256}, n_head/n_kvh <= 16. */
+bool q4_hip_qsa_decode(const float *d_q, const void *d_kcache, const void *d_vcache,
+                       const float *d_gate, float *d_out, uint32_t n_head, uint32_t n_kvh,
+                       uint32_t hd, uint32_t n_kv, uint32_t max_kv, float scale, int kv_f16);
+bool q4_hip_qsa_decode_n(const float *d_q, const void *d_kcache, const void *d_vcache,
+                         const float *d_gate, float *d_out, uint32_t n_head, uint32_t n_kvh,
+                         uint32_t hd, uint32_t n_tok, uint32_t kv_base, uint32_t max_kv,
+                         float scale, int kv_f16);
+bool q4_hip_qsa_decode_idx(const float *d_q, const void *d_kcache, const void *d_vcache,
+                           const float *d_gate, float *d_out, const int32_t *idx, uint32_t width,
+                           uint32_t n_head, uint32_t n_kvh, uint32_t hd, uint32_t n_tok,
+                           uint32_t max_kv, float scale, int kv_f16);
+/* Pre-allocates the attention scratch (split-KV partials) so nothing allocates inside a capture.
+ * src/q4.h:704, src/q4_rocm.cu:7698-7707 */
+bool q4_hip_qsa_topk_alloc(void);
+
+/* ======================================================================================= */
+/* 2. B200-native additions                                                                 */
+/* ======================================================================================= */
+
+/* Sticky status word of the last failed call / device-side check (0 = none); reading clears it.
+ * Bits: 1 bad argument, 2 CUDA error, 4 out-of-range position seen by a kernel (the position was
+ * skipped, nothing was accessed out of bounds), 8 scratch too small, 16 not initialised. */
+uint32_t q4_gpu_last_error(void);
+/* Internal compute stream as a cudaStream_t, and adoption of a caller's stream (NULL restores the
+ * internal one).  No counterpart in the reference (its stream is private, src/q4_rocm.cu:52-54). */
+void *q4_gpu_stream(void);
+bool q4_gpu_set_stream(void *cuda_stream);
+int q4_gpu_device(void);
+/* Device address of the position word written by q4_hip_pos_push. */
+const int32_t *q4_gpu_pos_word(void);
+
+/* ---- KV store: allocator + layout (replaces q4_sess KV fields, kv_at, kv_token_bytes,
+ * kv_write: src/q4_fwd.c:26-57,637-665,1944-1950; sizing q4_qsa_kv_bytes src/q4_place.c:92-105).
+ * One store per session.  q8_0 layout, per layer and kv head: quants [max_kv][hd] int8 for K and
+ * for V (one 128-byte line per row at hd 128) and one scale row [max_kv][2][hd/32] fp16 (K block
+ * scales then V block scales; 16 bytes at hd 128).  fp16 / fp32 kinds: [max_kv][hd] rows. */
+typedef struct q4_gpu_kv q4_gpu_kv;
+uint64_t q4_gpu_kv_bytes(uint32_t n_layers, uint32_t n_kvh, uint32_t hd, uint32_t max_kv, int kind);
+q4_gpu_kv *q4_gpu_kv_create(uint32_t n_layers, uint32_t n_kvh, uint32_t hd, uint32_t max_kv,
+                            int kind);
+void q4_gpu_kv_destroy(q4_gpu_kv *kv);
+/* Fused K+V append of n_tok rows ([n_tok][n_kvh*hd] fp32, device) at token slots pos0.. of one
+ * layer: quantise (q8_0) / convert / copy and scatter, one launch (replaces the two
+ * q4_hip_f32_to_q8 launches of src/q4_fwd.c:823-824,1738-1741). */
+bool q4_gpu_kv_append(q4_gpu_kv *kv, uint32_t layer, const float *k, const float *v, uint32_t pos0,
+                      uint32_t n_tok);
+/* Same for one token at the slot held in the device position word (replaces q4_hip_kv_append_d,
+ * src/q4_fwd.c:891). */
+bool q4_gpu_kv_append_d(q4_gpu_kv *kv, uint32_t layer, const float *k, const float *v);
+/* Rows [tok0, tok0+n_tok) of one layer's K (which = 0) or V (1) cache to / from the reference
+ * layout (n_tok * kv_token_bytes device bytes) -- what q4_sess_save writes per layer,
+ * src/q4_fwd.c:2353-2360. */
+bool q4_gpu_kv_export(const q4_gpu_kv *kv, uint32_t layer, int which, uint32_t tok0, uint32_t n_tok,
+                      void *dst);
+bool q4_gpu_kv_import(q4_gpu_kv *kv, uint32_t layer, int which, uint32_t tok0, uint32_t n_tok,
+                      const void *src);
+/* Prefix snapshot (the KV part of q4_sess_save / q4_sess_restore, src/q4_fwd.c:2314-2477) as bulk
+ * strided copies of rows [0, n_kv) of every plane.  buf is device memory (host = 0) or pinned /
+ * pageable host memory (host = 1); snapshot_bytes = n_kv * n_layers * 2 * kv_token_bytes. */
+uint64_t q4_gpu_kv_snapshot_bytes(const q4_gpu_kv *kv, uint32_t n_kv);
+bool q4_gpu_kv_save(const q4_gpu_kv *kv, uint32_t n_kv, void *buf, int host);
+bool q4_gpu_kv_restore(q4_gpu_kv *kv, uint32_t n_kv, const void *buf, int host);
+
+/* ---- decode attention over a store.  One launch covers every kv head and query head of the
+ * layer (split-KV over the position list, merged by the last block to finish).
+ *  q        : [n_head][hd], fp32 (q_bf16 = 0) or bf16 (q_bf16 = 1)
+ *  gate     : [n_head][hd] fp32 or NULL (no gate)
+ *  idx      : NULL = dense over [0, n_kv); else `width` int32 positions per list, -1 = skip;
+ *             idx_kvh_stride = 0: one list shared by all kv heads (the reference), else the list
+ *             of kv head kh starts at idx + kh*idx_kvh_stride (one list per kv head)
+ *  n_kv     : rows attended in dense mode, upper bound for positions in indexed mode; 0 = take
+ *             (device position word + 1), as the graph-captured reference path does
+ *  out      : [n_head][hd] fp32
+ * Replaces q4_hip_qsa_decode_idx / q4_hip_qsa_decode_n for n_tok = 1 (src/q4_fwd.c:738-741,922). */
+bool q4_gpu_kv_decode(const q4_gpu_kv *kv, uint32_t layer, const void *q, int q_bf16,
+                      const float *gate, float *out, uint32_t n_head, const int32_t *idx,
+                      uint32_t width, uint32_t idx_kvh_stride, uint32_t n_kv, float scale);
+/* Same, but stops before normalisation: part[n_head][hd+2] = {m, l, acc[hd]} over this store's
+ * rows, the record of src/q4_rocm.cu:6780,6957-6963 -- the payload exchanged between GPUs when one
+ * sequence is sharded by position. */
+bool q4_gpu_kv_decode_partial(const q4_gpu_kv *kv, uint32_t layer, const void *q, int q_bf16,
+                              float *part, uint32_t n_head, const int32_t *idx, uint32_t width,
+                              uint32_t idx_kvh_stride, uint32_t n_kv, float scale);
+/* Merge n_parts records per head (gqa_dec_comb_k, src/q4_rocm.cu:6968-7012):
+ * parts [n_parts][n_head][hd+2] -> out [n_head][hd], times sigmoid(gate) when gate != NULL. */
+bool q4_gpu_lse_merge(const float *parts, uint32_t n_parts, uint32_t n_head, uint32_t hd,
+                      const float *gate, float *out);
+
+/* ---- batched multi-session decode: one launch per layer for every session of the batch. */
+typedef struct q4_gpu_batch q4_gpu_batch;
+q4_gpu_batch *q4_gpu_batch_create(uint32_t max_sessions);
+void q4_gpu_batch_destroy(q4_gpu_batch *b);
+/* Bind session slot s to a store (all stores of a batch share n_layers, n_kvh, hd and kind). */
+bool q4_gpu_batch_bind(q4_gpu_batch *b, uint32_t slot, q4_gpu_kv *kv);
+/* Publish every session's decode position (host array of n_sessions int32), stream-ordered like
+ * q4_hip_pos_push. */
+bool q4_gpu_batch_set_pos(q4_gpu_batch *b, const int32_t *pos, uint32_t n_sessions);
+/* k, v: [n_sessions][n_kvh*hd] fp32; row s goes to slot pos[s] of session s. */
+bool q4_gpu_batch_append(q4_gpu_batch *b, uint32_t layer, const float *k, const float *v);
+/* q [n_sessions][n_head][hd]; gate, out likewise; idx [n_sessions][...] with idx_sess_stride
+ * entries between sessions (NULL = dense over [0, pos[s]+1)). */
+bool q4_gpu_batch_decode(q4_gpu_batch *b, uint32_t layer, const void *q, int q_bf16,
+                         const float *gate, float *out, const int32_t *idx, uint32_t width,
+                         uint32_t idx_kvh_stride, uint32_t idx_sess_stride, uint32_t n_head,
+                         float scale);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* Q4_GPU_H */

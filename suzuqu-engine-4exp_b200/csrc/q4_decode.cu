@@ -1,0 +1,723 @@
+/*
+ * Decode attention for one query token per unit over a q8_0 / fp16 / fp32 KV cache:
+ * split-KV flash decoding with the GQA group sharing every K/V row it reads.
+ *
+ * Replaces gqa_dec_split_k + gqa_dec_comb_k (and the gqa_decode_fast fallback) of the reference,
+ * src/q4_rocm.cu:6549-7012, with the semantics of its launchers (:7249-7364): positions < 0 are
+ * padding and are skipped, a unit with no live position outputs 0, the output is the
+ * softmax-weighted V times sigmoid(gate).
+ *
+ * Shape of the kernel.  The path is bound by HBM, and with 8 query heads sharing each K/V byte the
+ * scalar FMA pipe cannot keep up with B200's memory system (8 FMA per int8 byte at ~23 B/clk/SM
+ * is more than the 128 FMA/clk an SM has), so the two contractions run on the tensor cores with
+ * warp-level MMA while every byte of the cache goes straight from global memory into registers,
+ * once, with sector-aligned 4/8/16-byte loads -- no shared-memory staging, no block barrier in
+ * the main loop, so warps stream independently.
+ *
+ *   one warp-step = 16 positions:
+ *     S^T[16 pos x 8 heads]  = K[16 x hd] . Q^T        (m16n8k16, K rows are the A operand)
+ *     online softmax on S^T  (per head: max over positions by warp shuffles)
+ *     P^T -> fp16, 8x8 transposed in-warp (movmatrix) into the B operand
+ *     O^T[hd x 8 heads]     += V^T[hd x 16 pos] . P^T   (V bytes are the A operand)
+ *
+ *   q8_0: int8 codes are converted to exact fp16 integers in registers (byte permute + magic
+ *   subtract); K block scales multiply the four per-block partial dot products in fp32, V block
+ *   scales are folded into P^T per 32-wide block of hd.  Nothing is rounded except Q (to fp16 once)
+ *   and the softmax weights (fp16, and the denominator sums the same rounded weights).
+ *
+ * grid = (splits, kv heads, units).  Every block reduces its warps' partials in shared memory; with
+ * more than one split it writes an (m, l, acc) record to scratch and the last block to arrive
+ * (atomic counter per unit and kv head) merges the records and writes the output, so the whole
+ * layer is one launch.
+ */
+#include <cuda_bf16.h>
+#include <math_constants.h>
+#include <stdlib.h>
+
+#include "q4_internal.h"
+
+namespace {
+
+constexpr int DEC_WARPS = 4;
+constexpr int DEC_THREADS = DEC_WARPS * 32;
+constexpr uint32_t DEC_MAX_SPLIT = 256;
+constexpr uint32_t DEC_GROUP = 16;   /* records merged per level of the two-level merge */
+
+struct DecParams {
+    Q4Cache one;
+    const Q4Cache *const *many;
+    uint32_t layer, n_head, n_kvh, gqa;
+    const void *q;
+    int q_bf16;
+    const float *gate;
+    float *out, *part_out;
+    const int32_t *idx;
+    uint32_t width, idx_kvh_stride, idx_unit_stride;
+    const int32_t *pos;
+    uint32_t kv_base;
+    float scale_log2e;
+    uint32_t S;
+    float *scratch;
+    uint32_t *counters;
+    uint32_t *err;
+};
+
+/* ---- small device helpers ---------------------------------------------------------------- */
+__device__ __forceinline__ uint32_t ldg32(const void *p) {
+    uint32_t v;
+    asm("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg16(const void *p) {
+    uint16_t v;
+    asm("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg64(const void *p) {
+    uint2 v;
+    asm("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 ldg128(const void *p) {
+    uint4 v;
+    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+        : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+        : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t movmatrix_t(uint32_t x) {
+    uint32_t y;
+    asm("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t h2u(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+__device__ __forceinline__ __half2 u2h(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) { return h2u(__floats2half2_rn(lo, hi)); }
+
+/* 0x6480 is fp16 1152 = 1024 + 128: (code ^ 0x80) in the low mantissa bits of 1024.0 is the fp16
+ * number 1152 + code, so one subtract gives the int8 code as an exact fp16. */
+__device__ __forceinline__ uint32_t magic_sub(uint32_t v) {
+    return h2u(__hsub2(u2h(v), u2h(0x64806480u)));
+}
+/* 4 int8 in one word -> fp16x2 of bytes (0,1) and of bytes (2,3). */
+__device__ __forceinline__ void cvt_i8x4(uint32_t w, uint32_t &lo, uint32_t &hi) {
+    uint32_t x = w ^ 0x80808080u;
+    lo = magic_sub(__byte_perm(x, 0x64646464u, 0x4140));
+    hi = magic_sub(__byte_perm(x, 0x64646464u, 0x4342));
+}
+/* byte BI of word a and of word b -> fp16x2 {a.BI, b.BI}. */
+template <int BI>
+__device__ __forceinline__ uint32_t cvt_i8_pair(uint32_t a, uint32_t b) {
+    uint32_t u = __byte_perm(a, b, ((4 + BI) << 8) | BI);
+    return magic_sub((u & 0x00FF00FFu) ^ 0x64806480u);
+}
+__device__ __forceinline__ float warp_max_over_g(float v) {
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+    return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+}
+__device__ __forceinline__ float warp_sum_over_g(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    v += __shfl_xor_sync(0xffffffffu, v, 8);
+    return v + __shfl_xor_sync(0xffffffffu, v, 16);
+}
+
+/* Which head dimension the accumulator pair (c0,c1) / (c2,c3) of output tile mt holds for lane
+ * group g.  q8 layouts interleave so that each tile stays inside one 32-wide scale block. */
+template <int LAY>
+__device__ __forceinline__ int out_dim(int mt, int g, int hi) {
+    if (LAY == LAY_Q8P || LAY == LAY_Q8R) return 32 * (mt >> 1) + 4 * g + 2 * (mt & 1) + hi;
+    return 16 * mt + 2 * g + hi;
+}
+/* Which 4 head dimensions lane t feeds to k-step ks of the QK product (same map for Q and K). */
+template <int LAY>
+__device__ __forceinline__ int qk_dim(int ks, int t) {
+    if (LAY == LAY_Q8P || LAY == LAY_Q8R) return 32 * (ks >> 1) + 8 * t + 4 * (ks & 1);
+    return 16 * ks + 4 * t;
+}
+
+/* ---- the kernel ---------------------------------------------------------------------------- */
+template <int LAY, int HD, int NHT>
+__global__ void __launch_bounds__(DEC_THREADS, (HD * NHT <= 128) ? 3 : 1)
+q4_decode_k(const DecParams P) {
+    constexpr int NB = HD / 32;   /* q8_0 blocks per row */
+    constexpr int KS = HD / 16;   /* k-steps of the QK product */
+    constexpr int MT = HD / 16;   /* 16-dim output tiles of the PV product */
+    constexpr int HEADS = 8 * NHT;
+    constexpr int REC = HD + 2;
+    constexpr bool Q8 = (LAY == LAY_Q8P || LAY == LAY_Q8R);
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const uint32_t split = blockIdx.x, kh = blockIdx.y, u = blockIdx.z;
+    const uint32_t S = P.S;
+
+    const Q4Cache C = P.many ? *P.many[u] : P.one;
+    uint32_t n_kv = (P.pos ? (uint32_t)P.pos[P.many ? u : 0] : P.kv_base + u) + 1u;
+    if (n_kv > C.max_kv) n_kv = C.max_kv;
+    const int32_t *list = P.idx ? P.idx + (size_t)u * P.idx_unit_stride + (size_t)kh * P.idx_kvh_stride
+                                : nullptr;
+    const uint32_t n_pos = list ? P.width : n_kv;
+    const uint32_t steps = (n_pos + 15u) >> 4;
+    const uint32_t per = (steps + S - 1u) / S;
+    const uint32_t s_begin = split * per;
+    const uint32_t s_end = min(s_begin + per, steps);
+
+    const uint8_t *kbase = C.k + (uint64_t)P.layer * C.layer_stride + (uint64_t)kh * C.kvh_stride;
+    const uint8_t *vbase = C.v + (uint64_t)P.layer * C.layer_stride + (uint64_t)kh * C.kvh_stride;
+    const uint8_t *sbase = nullptr;
+    if (LAY == LAY_Q8P)
+        sbase = C.s + (uint64_t)P.layer * C.s_layer_stride + (uint64_t)kh * C.s_kvh_stride;
+    const uint32_t tok_stride = C.tok_stride, s_tok_stride = C.s_tok_stride;
+
+    /* ---- Q fragments (B operand of the QK product): head nt*8+g, dims qk_dim(ks, t)..+3 */
+    uint32_t qf[NHT][KS][2];
+#pragma unroll
+    for (int nt = 0; nt < NHT; nt++) {
+        const uint32_t hg = nt * 8 + g;
+        const bool live = hg < P.gqa;
+        const size_t qoff = ((size_t)u * P.n_head + (size_t)kh * P.gqa + hg) * HD;
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++) {
+            float x0 = 0.f, x1 = 0.f, x2 = 0.f, x3 = 0.f;
+            if (live) {
+                const int d = qk_dim<LAY>(ks, t);
+                if (P.q_bf16) {
+                    const uint2 w = *reinterpret_cast<const uint2 *>(
+                        reinterpret_cast<const __nv_bfloat16 *>(P.q) + qoff + d);
+                    x0 = __uint_as_float(w.x << 16);
+                    x1 = __uint_as_float(w.x & 0xffff0000u);
+                    x2 = __uint_as_float(w.y << 16);
+                    x3 = __uint_as_float(w.y & 0xffff0000u);
+                } else {
+                    const float4 w =
+                        *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(P.q) + qoff + d);
+                    x0 = w.x; x1 = w.y; x2 = w.z; x3 = w.w;
+                }
+            }
+            qf[nt][ks][0] = pack_h2(x0, x1);
+            qf[nt][ks][1] = pack_h2(x2, x3);
+        }
+    }
+
+    float m_run[NHT][2], l_run[NHT][2], acc[NHT][MT][4];
+#pragma unroll
+    for (int nt = 0; nt < NHT; nt++) {
+        m_run[nt][0] = m_run[nt][1] = -CUDART_INF_F;
+        l_run[nt][0] = l_run[nt][1] = 0.f;
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++)
+            acc[nt][mt][0] = acc[nt][mt][1] = acc[nt][mt][2] = acc[nt][mt][3] = 0.f;
+    }
+
+    for (uint32_t step = s_begin + warp; step < s_end; step += DEC_WARPS) {
+        /* ---- positions of this step: K rows are slots g, g+8; V rows are slots 2t,2t+1,2t+8,2t+9 */
+        const uint32_t j0 = step << 4;
+        int32_t pk[2], pv[4];
+        if (list) {
+            int32_t mine = -1;
+            const uint32_t j = j0 + (lane & 15);
+            if (j < n_pos) {
+                mine = list[j];
+                if (mine >= (int32_t)C.max_kv) {
+                    atomicOr(P.err, (uint32_t)Q4E_RANGE);
+                    mine = -1;
+                }
+            }
+            pk[0] = __shfl_sync(0xffffffffu, mine, g);
+            pk[1] = __shfl_sync(0xffffffffu, mine, g + 8);
+            pv[0] = __shfl_sync(0xffffffffu, mine, 2 * t);
+            pv[1] = __shfl_sync(0xffffffffu, mine, 2 * t + 1);
+            pv[2] = __shfl_sync(0xffffffffu, mine, 2 * t + 8);
+            pv[3] = __shfl_sync(0xffffffffu, mine, 2 * t + 9);
+        } else {
+            auto dense = [&](uint32_t s) -> int32_t { return j0 + s < n_pos ? (int32_t)(j0 + s) : -1; };
+            pk[0] = dense(g); pk[1] = dense(g + 8);
+            pv[0] = dense(2 * t); pv[1] = dense(2 * t + 1);
+            pv[2] = dense(2 * t + 8); pv[3] = dense(2 * t + 9);
+        }
+        const uint8_t *krow[2], *vrow[4];
+#pragma unroll
+        for (int r = 0; r < 2; r++) krow[r] = kbase + (uint64_t)(pk[r] < 0 ? 0 : pk[r]) * tok_stride;
+#pragma unroll
+        for (int r = 0; r < 4; r++) vrow[r] = vbase + (uint64_t)(pv[r] < 0 ? 0 : pv[r]) * tok_stride;
+
+        /* ---- issue the q8_0 loads of the whole step up front (memory-level parallelism) */
+        uint2 kw[Q8 ? 2 : 1][Q8 ? NB : 1];
+        uint32_t vw[Q8 ? 4 : 1][Q8 ? NB : 1];
+        float ksc[Q8 ? 2 : 1][Q8 ? NB : 1];       /* K block scales x softmax scale x log2(e) */
+        __half vsc[Q8 ? 4 : 1][Q8 ? NB : 1];
+        if constexpr (LAY == LAY_Q8P) {
+#pragma unroll
+            for (int r = 0; r < 2; r++)
+#pragma unroll
+                for (int b = 0; b < NB; b++)
+                    kw[r][b] = pk[r] >= 0 ? ldg64(krow[r] + 32 * b + 8 * t) : make_uint2(0u, 0u);
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int b = 0; b < NB; b++)
+                    vw[r][b] = pv[r] >= 0 ? ldg32(vrow[r] + 32 * b + 4 * g) : 0u;
+            /* scale row: NB fp16 for K then NB fp16 for V */
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                const uint8_t *sp = sbase + (uint64_t)(pk[r] < 0 ? 0 : pk[r]) * s_tok_stride;
+                __half h[NB];
+                if constexpr (NB == 4) { uint2 w = ldg64(sp); *reinterpret_cast<uint2 *>(h) = w; }
+                else if constexpr (NB == 8) { uint4 w = ldg128(sp); *reinterpret_cast<uint4 *>(h) = w; }
+                else if constexpr (NB == 2) { uint32_t w = ldg32(sp); *reinterpret_cast<uint32_t *>(h) = w; }
+                else { uint16_t w = (uint16_t)ldg16(sp); *reinterpret_cast<uint16_t *>(h) = w; }
+#pragma unroll
+                for (int b = 0; b < NB; b++)
+                    ksc[r][b] = pk[r] >= 0 ? __half2float(h[b]) * P.scale_log2e : 0.f;
+            }
+#pragma unroll
+            for (int r = 0; r < 4; r++) {
+                const uint8_t *sp = sbase + (uint64_t)(pv[r] < 0 ? 0 : pv[r]) * s_tok_stride + 2 * NB;
+                __half h[NB];
+                if constexpr (NB == 4) { uint2 w = ldg64(sp); *reinterpret_cast<uint2 *>(h) = w; }
+                else if constexpr (NB == 8) { uint4 w = ldg128(sp); *reinterpret_cast<uint4 *>(h) = w; }
+                else if constexpr (NB == 2) { uint32_t w = ldg32(sp); *reinterpret_cast<uint32_t *>(h) = w; }
+                else { uint16_t w = (uint16_t)ldg16(sp); *reinterpret_cast<uint16_t *>(h) = w; }
+#pragma unroll
+                for (int b = 0; b < NB; b++) vsc[r][b] = pv[r] >= 0 ? h[b] : __ushort_as_half(0);
+            }
+        } else if constexpr (LAY == LAY_Q8R) {
+            /* reference layout: 34-byte blocks {fp16 scale, 32 x int8}, only 2-byte aligned */
+#pragma unroll
+            for (int r = 0; r < 2; r++)
+#pragma unroll
+                for (int b = 0; b < NB; b++) {
+                    const uint8_t *bp = krow[r] + 34 * b;
+                    if (pk[r] >= 0) {
+                        const uint8_t *cp = bp + 2 + 8 * t;
+                        kw[r][b].x = ldg16(cp) | (ldg16(cp + 2) << 16);
+                        kw[r][b].y = ldg16(cp + 4) | (ldg16(cp + 6) << 16);
+                        ksc[r][b] = __half2float(__ushort_as_half((uint16_t)ldg16(bp))) * P.scale_log2e;
+                    } else {
+                        kw[r][b] = make_uint2(0u, 0u);
+                        ksc[r][b] = 0.f;
+                    }
+                }
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int b = 0; b < NB; b++) {
+                    const uint8_t *bp = vrow[r] + 34 * b;
+                    if (pv[r] >= 0) {
+                        const uint8_t *cp = bp + 2 + 4 * g;
+                        vw[r][b] = ldg16(cp) | (ldg16(cp + 2) << 16);
+                        vsc[r][b] = __ushort_as_half((uint16_t)ldg16(bp));
+                    } else {
+                        vw[r][b] = 0u;
+                        vsc[r][b] = __ushort_as_half(0);
+                    }
+                }
+        }
+
+        /* ---- S^T = K . Q^T (log2 domain: scale * log2(e) folded in) */
+        float sc[NHT][4];
+#pragma unroll
+        for (int nt = 0; nt < NHT; nt++) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+        if constexpr (Q8) {
+#pragma unroll
+            for (int b = 0; b < NB; b++) {
+                float cb[NHT][4];
+#pragma unroll
+                for (int nt = 0; nt < NHT; nt++) cb[nt][0] = cb[nt][1] = cb[nt][2] = cb[nt][3] = 0.f;
+#pragma unroll
+                for (int jj = 0; jj < 2; jj++) {
+                    uint32_t a0, a1, a2, a3;
+                    cvt_i8x4(jj ? kw[0][b].y : kw[0][b].x, a0, a2);
+                    cvt_i8x4(jj ? kw[1][b].y : kw[1][b].x, a1, a3);
+#pragma unroll
+                    for (int nt = 0; nt < NHT; nt++)
+                        mma16816(cb[nt], a0, a1, a2, a3, qf[nt][2 * b + jj][0], qf[nt][2 * b + jj][1]);
+                }
+#pragma unroll
+                for (int nt = 0; nt < NHT; nt++) {
+                    sc[nt][0] = fmaf(ksc[0][b], cb[nt][0], sc[nt][0]);
+                    sc[nt][1] = fmaf(ksc[0][b], cb[nt][1], sc[nt][1]);
+                    sc[nt][2] = fmaf(ksc[1][b], cb[nt][2], sc[nt][2]);
+                    sc[nt][3] = fmaf(ksc[1][b], cb[nt][3], sc[nt][3]);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++) {
+                uint32_t a[4];
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                    uint32_t lo = 0u, hi = 0u;
+                    if (pk[r] >= 0) {
+                        if constexpr (LAY == LAY_F16) {
+                            const uint2 w = ldg64(krow[r] + (16 * ks + 4 * t) * 2);
+                            lo = w.x; hi = w.y;
+                        } else {
+                            const uint4 w = ldg128(krow[r] + (16 * ks + 4 * t) * 4);
+                            lo = pack_h2(__uint_as_float(w.x), __uint_as_float(w.y));
+                            hi = pack_h2(__uint_as_float(w.z), __uint_as_float(w.w));
+                        }
+                    }
+                    a[r] = lo; a[2 + r] = hi;
+                }
+#pragma unroll
+                for (int nt = 0; nt < NHT; nt++)
+                    mma16816(sc[nt], a[0], a[1], a[2], a[3], qf[nt][ks][0], qf[nt][ks][1]);
+            }
+#pragma unroll
+            for (int nt = 0; nt < NHT; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) sc[nt][e] *= P.scale_log2e;
+        }
+
+        /* ---- online softmax; lanes (g, t) hold positions g / g+8 for heads 2t, 2t+1 */
+        uint32_t pb0[NHT], pb1[NHT];
+#pragma unroll
+        for (int nt = 0; nt < NHT; nt++) {
+            if (pk[0] < 0) sc[nt][0] = sc[nt][1] = -CUDART_INF_F;
+            if (pk[1] < 0) sc[nt][2] = sc[nt][3] = -CUDART_INF_F;
+            const float mx0 = warp_max_over_g(fmaxf(sc[nt][0], sc[nt][2]));
+            const float mx1 = warp_max_over_g(fmaxf(sc[nt][1], sc[nt][3]));
+            const float mn0 = fmaxf(m_run[nt][0], mx0), mn1 = fmaxf(m_run[nt][1], mx1);
+            const float mu0 = mn0 == -CUDART_INF_F ? 0.f : mn0;
+            const float mu1 = mn1 == -CUDART_INF_F ? 0.f : mn1;
+            const float al0 = ex2(m_run[nt][0] - mu0), al1 = ex2(m_run[nt][1] - mu1);
+            m_run[nt][0] = mn0;
+            m_run[nt][1] = mn1;
+            const __half2 h0 = __floats2half2_rn(ex2(sc[nt][0] - mu0), ex2(sc[nt][1] - mu1));
+            const __half2 h1 = __floats2half2_rn(ex2(sc[nt][2] - mu0), ex2(sc[nt][3] - mu1));
+            l_run[nt][0] = fmaf(l_run[nt][0], al0, __low2float(h0) + __low2float(h1));
+            l_run[nt][1] = fmaf(l_run[nt][1], al1, __high2float(h0) + __high2float(h1));
+            if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++) {
+                    acc[nt][mt][0] *= al0; acc[nt][mt][1] *= al1;
+                    acc[nt][mt][2] *= al0; acc[nt][mt][3] *= al1;
+                }
+            }
+            pb0[nt] = movmatrix_t(h2u(h0));   /* {P[pos 2t][head g], P[pos 2t+1][head g]} */
+            pb1[nt] = movmatrix_t(h2u(h1));   /* positions 2t+8, 2t+9 */
+        }
+
+        /* ---- O^T += V^T . P^T */
+        if constexpr (Q8) {
+#pragma unroll
+            for (int b = 0; b < NB; b++) {
+                const __half2 s01 = __halves2half2(vsc[0][b], vsc[1][b]);
+                const __half2 s23 = __halves2half2(vsc[2][b], vsc[3][b]);
+                uint32_t bb0[NHT], bb1[NHT];
+#pragma unroll
+                for (int nt = 0; nt < NHT; nt++) {
+                    bb0[nt] = h2u(__hmul2(u2h(pb0[nt]), s01));
+                    bb1[nt] = h2u(__hmul2(u2h(pb1[nt]), s23));
+                }
+                {
+                    const uint32_t a0 = cvt_i8_pair<0>(vw[0][b], vw[1][b]);
+                    const uint32_t a1 = cvt_i8_pair<1>(vw[0][b], vw[1][b]);
+                    const uint32_t a2 = cvt_i8_pair<0>(vw[2][b], vw[3][b]);
+                    const uint32_t a3 = cvt_i8_pair<1>(vw[2][b], vw[3][b]);
+#pragma unroll
+                    for (int nt = 0; nt < NHT; nt++) mma16816(acc[nt][2 * b], a0, a1, a2, a3, bb0[nt], bb1[nt]);
+                }
+                {
+                    const uint32_t a0 = cvt_i8_pair<2>(vw[0][b], vw[1][b]);
+                    const uint32_t a1 = cvt_i8_pair<3>(vw[0][b], vw[1][b]);
+                    const uint32_t a2 = cvt_i8_pair<2>(vw[2][b], vw[3][b]);
+                    const uint32_t a3 = cvt_i8_pair<3>(vw[2][b], vw[3][b]);
+#pragma unroll
+                    for (int nt = 0; nt < NHT; nt++)
+                        mma16816(acc[nt][2 * b + 1], a0, a1, a2, a3, bb0[nt], bb1[nt]);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) {
+                /* rows g / g+8 of the tile are dims 16mt+2g / 16mt+2g+1 */
+                uint32_t lo[4], hi[4];
+#pragma unroll
+                for (int r = 0; r < 4; r++) {
+                    lo[r] = hi[r] = 0u;
+                    if (pv[r] >= 0) {
+                        if constexpr (LAY == LAY_F16) {
+                            const uint32_t w = ldg32(vrow[r] + (16 * mt + 2 * g) * 2);
+                            lo[r] = w & 0xffffu; hi[r] = w >> 16;
+                        } else {
+                            const uint2 w = ldg64(vrow[r] + (16 * mt + 2 * g) * 4);
+                            const uint32_t h = pack_h2(__uint_as_float(w.x), __uint_as_float(w.y));
+                            lo[r] = h & 0xffffu; hi[r] = h >> 16;
+                        }
+                    }
+                }
+                const uint32_t a0 = lo[0] | (lo[1] << 16), a1 = hi[0] | (hi[1] << 16);
+                const uint32_t a2 = lo[2] | (lo[3] << 16), a3 = hi[2] | (hi[3] << 16);
+#pragma unroll
+                for (int nt = 0; nt < NHT; nt++) mma16816(acc[nt][mt], a0, a1, a2, a3, pb0[nt], pb1[nt]);
+            }
+        }
+    }
+
+    /* ---- block reduction of the warps' partials ------------------------------------------- */
+    extern __shared__ float sm[];   /* [DEC_WARPS][HEADS][REC] : m, l, acc[HD] */
+#pragma unroll
+    for (int nt = 0; nt < NHT; nt++) {
+        const float l0 = warp_sum_over_g(l_run[nt][0]), l1 = warp_sum_over_g(l_run[nt][1]);
+        float *r0 = sm + ((size_t)warp * HEADS + nt * 8 + 2 * t) * REC;
+        float *r1 = r0 + REC;
+        if (g == 0) {
+            r0[0] = m_run[nt][0]; r0[1] = l0;
+            r1[0] = m_run[nt][1]; r1[1] = l1;
+        }
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++) {
+            const int d0 = out_dim<LAY>(mt, g, 0), d1 = out_dim<LAY>(mt, g, 1);
+            r0[2 + d0] = acc[nt][mt][0]; r1[2 + d0] = acc[nt][mt][1];
+            r0[2 + d1] = acc[nt][mt][2]; r1[2 + d1] = acc[nt][mt][3];
+        }
+    }
+    __syncthreads();
+
+    const uint32_t gqa = P.gqa;
+    const size_t unit = (size_t)u * P.n_kvh + kh;
+    __shared__ uint32_t s_last;
+
+    auto finish = [&](uint32_t h, uint32_t d, float M, float L, float A) {
+        const uint32_t head = kh * gqa + h;
+        if (P.part_out) {
+            float *pr = P.part_out + ((size_t)u * P.n_head + head) * REC;
+            if (d == 0) {
+                pr[0] = L > 0.f ? M * 0.6931471805599453f : 0.f;   /* back to natural-log units */
+                pr[1] = L;
+            }
+            pr[2 + d] = A;
+        } else {
+            float o = L > 0.f ? A / L : 0.f;
+            if (P.gate) o *= 1.f / (1.f + __expf(-P.gate[((size_t)u * P.n_head + head) * HD + d]));
+            P.out[((size_t)u * P.n_head + head) * HD + d] = o;
+        }
+    };
+    /* store a merged record (log2-domain max) for a later merge level */
+    auto store_rec = [&](float *rec, uint32_t h, uint32_t d, float M, float L, float A) {
+        if (d == 0) { rec[(size_t)h * REC] = M; rec[(size_t)h * REC + 1] = L; }
+        rec[(size_t)h * REC + 2 + d] = A;
+    };
+    /* merge `count` records spaced HEADS*REC floats apart; thread d owns output dim d */
+    auto merge = [&](const float *recs, uint32_t count, bool from_smem, float *dst_rec) {
+        for (uint32_t h = 0; h < gqa; h++) {
+            float M = -CUDART_INF_F;
+            for (uint32_t s = 0; s < count; s++) {
+                const float *r = recs + ((size_t)s * HEADS + h) * REC;
+                M = fmaxf(M, from_smem ? r[0] : __ldcg(r));
+            }
+            const float Mu = M == -CUDART_INF_F ? 0.f : M;
+            float L = 0.f;
+            for (uint32_t s = 0; s < count; s++) {
+                const float *r = recs + ((size_t)s * HEADS + h) * REC;
+                L = from_smem ? fmaf(ex2(r[0] - Mu), r[1], L) : fmaf(ex2(__ldcg(r) - Mu), __ldcg(r + 1), L);
+            }
+            for (uint32_t d = threadIdx.x; d < (uint32_t)HD; d += DEC_THREADS) {
+                float A = 0.f;
+                for (uint32_t s = 0; s < count; s++) {
+                    const float *r = recs + ((size_t)s * HEADS + h) * REC;
+                    A = from_smem ? fmaf(ex2(r[0] - Mu), r[2 + d], A)
+                                  : fmaf(ex2(__ldcg(r) - Mu), __ldcg(r + 2 + d), A);
+                }
+                if (dst_rec) store_rec(dst_rec, h, d, M, L, A);
+                else finish(h, d, M, L, A);
+            }
+        }
+    };
+    /* arrive on a counter; true for the last of `expected` arrivals (which also re-arms it) */
+    auto arrive_last = [&](uint32_t *ctr, uint32_t expected) -> bool {
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const uint32_t prev = atomicAdd(ctr, 1u);
+            s_last = (prev == expected - 1u);
+            if (s_last) *ctr = 0u;   /* ready for the next launch / graph replay */
+        }
+        __syncthreads();
+        const bool last = s_last != 0u;
+        if (last) __threadfence();
+        return last;
+    };
+
+    if (S == 1) {
+        merge(sm, DEC_WARPS, true, nullptr);
+        return;
+    }
+    /* level 1: record per block; groups of DEC_GROUP blocks are merged by their last arrival,
+     * level 2: the group records are merged by the last group to finish. */
+    const uint32_t n_groups = (S + DEC_GROUP - 1u) / DEC_GROUP;
+    const uint32_t grp = split / DEC_GROUP;
+    const uint32_t grp_size = min(DEC_GROUP, S - grp * DEC_GROUP);
+    float *rec1 = P.scratch + (unit * (size_t)(S + n_groups)) * HEADS * REC;
+    float *rec2 = rec1 + (size_t)S * HEADS * REC;
+    uint32_t *ctr = P.counters + unit * (1u + DEC_MAX_SPLIT / DEC_GROUP);
+    merge(sm, DEC_WARPS, true, rec1 + (size_t)split * HEADS * REC);
+    if (!arrive_last(ctr + 1 + grp, grp_size)) return;
+    if (n_groups == 1) {
+        merge(rec1, S, false, nullptr);
+        return;
+    }
+    merge(rec1 + (size_t)grp * DEC_GROUP * HEADS * REC, grp_size, false, rec2 + (size_t)grp * HEADS * REC);
+    if (!arrive_last(ctr, n_groups)) return;
+    merge(rec2, n_groups, false, nullptr);
+}
+
+/* Merge of externally produced records (sequence-sharded decode): parts [n_parts][n_head][hd+2]
+ * with m in natural-log units, as gqa_dec_comb_k (src/q4_rocm.cu:6968-7012). */
+__global__ void q4_lse_merge_k(const float *parts, uint32_t n_parts, uint32_t n_head, uint32_t hd,
+                               const float *gate, float *out) {
+    const uint32_t h = blockIdx.x, rec = hd + 2;
+    float M = -CUDART_INF_F;
+    for (uint32_t s = 0; s < n_parts; s++) {
+        const float *r = parts + ((size_t)s * n_head + h) * rec;
+        if (r[1] > 0.f) M = fmaxf(M, r[0]);
+    }
+    float L = 0.f;
+    for (uint32_t s = 0; s < n_parts; s++) {
+        const float *r = parts + ((size_t)s * n_head + h) * rec;
+        if (r[1] > 0.f) L = fmaf(__expf(r[0] - M), r[1], L);
+    }
+    for (uint32_t d = threadIdx.x; d < hd; d += blockDim.x) {
+        float A = 0.f;
+        for (uint32_t s = 0; s < n_parts; s++) {
+            const float *r = parts + ((size_t)s * n_head + h) * rec;
+            if (r[1] > 0.f) A = fmaf(__expf(r[0] - M), r[2 + d], A);
+        }
+        float o = L > 0.f ? A / L : 0.f;
+        if (gate) o *= 1.f / (1.f + __expf(-gate[(size_t)h * hd + d]));
+        out[(size_t)h * hd + d] = o;
+    }
+}
+
+template <int LAY, int HD, int NHT>
+bool launch(const DecParams &p, dim3 grid) {
+    constexpr size_t smem = (size_t)DEC_WARPS * 8 * NHT * (HD + 2) * sizeof(float);
+    static bool attr_done = false;
+    if (!attr_done && smem > 48 * 1024) {
+        if (!q4i_check(cudaFuncSetAttribute(q4_decode_k<LAY, HD, NHT>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                       "decode smem attribute"))
+            return false;
+    }
+    attr_done = true;
+    q4_decode_k<LAY, HD, NHT><<<grid, DEC_THREADS, smem, g_q4.stream>>>(p);
+    return q4i_check(cudaGetLastError(), "decode launch");
+}
+template <int LAY, int HD>
+bool launch_nht(const DecParams &p, dim3 grid) {
+    return p.gqa <= 8 ? launch<LAY, HD, 1>(p, grid) : launch<LAY, HD, 2>(p, grid);
+}
+template <int LAY>
+bool launch_hd(const DecParams &p, dim3 grid, uint32_t hd) {
+    switch (hd) {
+    case 32: return launch_nht<LAY, 32>(p, grid);
+    case 64: return launch_nht<LAY, 64>(p, grid);
+    case 128: return launch_nht<LAY, 128>(p, grid);
+    case 256: return launch_nht<LAY, 256>(p, grid);
+    }
+    return q4i_fail(Q4E_ARG, "decode: hd must be 32, 64, 128 or 256");
+}
+
+uint32_t split_override() {
+    /* same knob as the reference (Q4_DEC_SPLIT_S, src/q4_rocm.cu:6750-6760); 0 = automatic */
+    static int s = -1;
+    if (s < 0) {
+        const char *e = getenv("Q4_DEC_SPLIT_S");
+        long v = e ? strtol(e, nullptr, 10) : 0;
+        s = (int)(v < 0 ? 0 : v > (long)DEC_MAX_SPLIT ? (long)DEC_MAX_SPLIT : v);
+    }
+    return (uint32_t)s;
+}
+
+}  // namespace
+
+bool q4i_decode(const Q4DecodeArgs &a) {
+    if (!g_q4.ok) return q4i_fail(Q4E_INIT, "decode: library not initialised");
+    Q4_REQUIRE(a.q && (a.out || a.part_out) && a.n_units && a.n_head && a.n_kvh, "decode: null/zero argument");
+    Q4_REQUIRE(a.n_head % a.n_kvh == 0 && a.n_head / a.n_kvh <= 16, "decode: n_head/n_kvh must be 1..16");
+    Q4_REQUIRE(!a.idx || a.width, "decode: zero-width index list");
+    const uint32_t gqa = a.n_head / a.n_kvh;
+    const uint32_t heads = gqa <= 8 ? 8 : 16;
+
+    /* split so that the grid fills every SM a few blocks deep, each block keeping its warps busy */
+    const uint32_t rows = a.idx ? a.width : (a.hint_rows ? a.hint_rows : 1u);
+    const uint32_t steps = (rows + 15u) / 16u;
+    const uint32_t units = a.n_units * a.n_kvh;
+    uint32_t S = split_override();
+    if (!S) {
+        const uint32_t target = (uint32_t)g_q4.sm_count * 6u;
+        S = (target + units - 1u) / units;
+        const uint32_t cap = (steps + DEC_WARPS - 1u) / DEC_WARPS;
+        if (S > cap) S = cap;
+    }
+    if (S > DEC_MAX_SPLIT) S = DEC_MAX_SPLIT;
+    if (S < 1) S = 1;
+
+    const uint32_t n_groups = (S + DEC_GROUP - 1u) / DEC_GROUP;
+    const size_t need_part = (size_t)units * (S + n_groups) * heads * (a.hd + 2);
+    const size_t need_ctr = (size_t)units * (1u + DEC_MAX_SPLIT / DEC_GROUP);
+    float *scratch = a.scratch_part;
+    uint32_t *counters = a.scratch_counters;
+    if (scratch) {
+        if (a.scratch_part_floats < need_part || a.scratch_n_counters < need_ctr)
+            return q4i_fail(Q4E_SCRATCH, "decode: caller scratch too small");
+    } else {
+        if (!q4i_scratch(S > 1 ? need_part : 0, need_ctr)) return false;
+        scratch = g_q4.part;
+        counters = g_q4.counters;
+    }
+
+    DecParams p;
+    p.one = a.one;
+    p.many = a.many;
+    p.layer = a.layer;
+    p.n_head = a.n_head;
+    p.n_kvh = a.n_kvh;
+    p.gqa = gqa;
+    p.q = a.q;
+    p.q_bf16 = a.q_bf16;
+    p.gate = a.gate;
+    p.out = a.out;
+    p.part_out = a.part_out;
+    p.idx = a.idx;
+    p.width = a.width;
+    p.idx_kvh_stride = a.idx_kvh_stride;
+    p.idx_unit_stride = a.idx_unit_stride;
+    p.pos = a.pos;
+    p.kv_base = a.kv_base;
+    p.scale_log2e = a.scale * 1.4426950408889634f;
+    p.S = S;
+    p.scratch = scratch;
+    p.counters = counters;
+    p.err = g_q4.err_d;
+    dim3 grid(S, a.n_kvh, a.n_units);
+    switch (a.layout) {
+    case LAY_F32: return launch_hd<LAY_F32>(p, grid, a.hd);
+    case LAY_F16: return launch_hd<LAY_F16>(p, grid, a.hd);
+    case LAY_Q8P: return launch_hd<LAY_Q8P>(p, grid, a.hd);
+    case LAY_Q8R: return launch_hd<LAY_Q8R>(p, grid, a.hd);
+    }
+    return q4i_fail(Q4E_ARG, "decode: bad layout");
+}
+
+extern "C" bool q4_gpu_lse_merge(const float *parts, uint32_t n_parts, uint32_t n_head, uint32_t hd,
+                                 const float *gate, float *out) {
+    if (!g_q4.ok) return q4i_fail(Q4E_INIT, "lse_merge: library not initialised");
+    Q4_REQUIRE(parts && out && n_parts && n_head && hd, "lse_merge: null/zero argument");
+    q4_lse_merge_k<<<n_head, 128, 0, g_q4.stream>>>(parts, n_parts, n_head, hd, gate, out);
+    return q4i_check(cudaGetLastError(), "lse_merge launch");
+}

@@ -1,0 +1,91 @@
+/* Internal declarations shared by the libq4gpu translation units (not installed). */
+#ifndef Q4_INTERNAL_H
+#define Q4_INTERNAL_H
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/q4_gpu.h"
+
+/* KV kinds of the public ABI, plus the two q8_0 layouts the kernels distinguish. */
+enum { Q4K_F32 = 0, Q4K_F16 = 1, Q4K_Q8 = 2 };
+enum { LAY_F32 = 0, LAY_F16 = 1, LAY_Q8P = 2 /* planar store */, LAY_Q8R = 3 /* reference 34-byte blocks */ };
+
+enum {
+    Q4E_ARG = 1, Q4E_CUDA = 2, Q4E_RANGE = 4, Q4E_SCRATCH = 8, Q4E_INIT = 16,
+};
+
+/* One cache as the kernels see it.  Row (layer, kv head kh, token p) of the K plane lives at
+ * k + layer*layer_stride + kh*kvh_stride + p*tok_stride (same for v); for the planar q8_0 store the
+ * scale row is at s + layer*s_layer_stride + kh*s_kvh_stride + p*s_tok_stride and holds the K block
+ * scales followed by the V block scales (fp16). */
+struct Q4Cache {
+    const uint8_t *k, *v, *s;
+    uint64_t layer_stride, kvh_stride, s_layer_stride, s_kvh_stride;
+    uint32_t tok_stride, s_tok_stride;
+    uint32_t max_kv, pad;
+};
+
+struct q4_gpu_kv {
+    uint32_t n_layers, n_kvh, hd, max_kv;
+    int kind;
+    uint8_t *k, *v, *s;          /* device planes (s only for q8_0) */
+    uint64_t plane_bytes, s_bytes;
+    Q4Cache view;                /* host copy of the kernel view */
+    Q4Cache *d_view;             /* same, in device memory (for batched launches) */
+};
+
+/* runtime state (q4_runtime.cu) */
+struct Q4State {
+    bool ok;
+    int device, sm_count;
+    cudaStream_t own_stream, stream, copy_stream;
+    int capturing;
+    int32_t *pos_d, *pos_h;
+    uint32_t *err_d;             /* device-side sticky error bits */
+    uint32_t err_h;
+    uint32_t last_graph_nodes;
+    /* attention scratch: split-KV partial records + per-unit arrival counters */
+    float *part;
+    size_t part_floats;
+    uint32_t *counters;
+    size_t n_counters;
+};
+extern Q4State g_q4;
+
+bool q4i_fail(uint32_t bit, const char *what);
+bool q4i_check(cudaError_t e, const char *what);
+bool q4i_scratch(size_t part_floats, size_t n_counters); /* grows outside capture, fails inside */
+
+#define Q4_REQUIRE(cond, what)                    \
+    do {                                          \
+        if (!(cond)) return q4i_fail(Q4E_ARG, what); \
+    } while (0)
+
+/* decode attention launcher (q4_decode.cu) */
+struct Q4DecodeArgs {
+    Q4Cache one;                 /* used when many == nullptr */
+    const Q4Cache *const *many;  /* device array of device Q4Cache pointers, one per session */
+    int layout;                  /* LAY_* */
+    uint32_t layer, n_units;     /* units = sessions (many) or tokens (one) */
+    uint32_t n_head, n_kvh, hd;
+    const void *q;
+    int q_bf16;
+    const float *gate;
+    float *out, *part_out;
+    const int32_t *idx;
+    uint32_t width, idx_kvh_stride, idx_unit_stride;
+    const int32_t *pos;          /* device positions: per session (many) or one word (one); may be null */
+    uint32_t kv_base;            /* used when pos == nullptr: unit u attends kv_base + u + 1 rows */
+    uint32_t hint_rows;          /* host's estimate of rows per unit, to size the split */
+    float scale;
+    /* optional caller-provided scratch (no-allocation entry point); null = library scratch */
+    float *scratch_part;
+    uint32_t *scratch_counters;
+    size_t scratch_part_floats, scratch_n_counters;
+};
+bool q4i_decode(const Q4DecodeArgs &a);
+
+#endif

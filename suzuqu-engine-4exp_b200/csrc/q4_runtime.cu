@@ -1,0 +1,256 @@
+/*
+ * Runtime glue behind the reference's device ABI: one device, one compute stream, allocation,
+ * copies, the decode position word, stream capture, scratch.  Restates the conventions of
+ * src/q4_rocm.cu:20-120,202-322,5656-5670,6218-6227,8156-8246,8417-8432 on the CUDA runtime.
+ */
+#include <stdlib.h>
+#include <string.h>
+
+#include "q4_internal.h"
+
+Q4State g_q4 = {};
+
+bool q4i_fail(uint32_t bit, const char *what) {
+    g_q4.err_h |= bit;
+    fprintf(stderr, "q4 gpu: %s\n", what);
+    return false;
+}
+bool q4i_check(cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return true;
+    g_q4.err_h |= Q4E_CUDA;
+    fprintf(stderr, "q4 gpu: %s: %s\n", what, cudaGetErrorString(e));
+    return false;
+}
+
+/* Scratch for the split-KV records and arrival counters.  Grows only outside capture (an
+ * allocation would invalidate the capture, src/q4_rocm.cu:55-57); counters start at zero and every
+ * kernel leaves them at zero. */
+bool q4i_scratch(size_t part_floats, size_t n_counters) {
+    if (part_floats > g_q4.part_floats) {
+        if (g_q4.capturing) return q4i_fail(Q4E_SCRATCH, "attention scratch too small inside a capture");
+        if (!q4i_check(cudaStreamSynchronize(g_q4.stream), "scratch sync")) return false;
+        if (g_q4.part) cudaFree(g_q4.part);
+        g_q4.part = nullptr;
+        g_q4.part_floats = 0;
+        size_t want = part_floats + part_floats / 4;
+        if (!q4i_check(cudaMalloc(&g_q4.part, want * sizeof(float)), "scratch alloc")) return false;
+        g_q4.part_floats = want;
+    }
+    if (n_counters > g_q4.n_counters) {
+        if (g_q4.capturing) return q4i_fail(Q4E_SCRATCH, "attention counters too small inside a capture");
+        if (!q4i_check(cudaStreamSynchronize(g_q4.stream), "scratch sync")) return false;
+        if (g_q4.counters) cudaFree(g_q4.counters);
+        g_q4.counters = nullptr;
+        g_q4.n_counters = 0;
+        size_t want = n_counters * 2;
+        if (!q4i_check(cudaMalloc(&g_q4.counters, want * sizeof(uint32_t)), "counter alloc")) return false;
+        if (!q4i_check(cudaMemset(g_q4.counters, 0, want * sizeof(uint32_t)), "counter clear")) return false;
+        g_q4.n_counters = want;
+    }
+    return true;
+}
+
+extern "C" bool q4_hip_init(void) {
+    if (g_q4.ok) return true;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    int dev = 0;
+    const char *e = getenv("Q4_GPU_DEVICE");
+    if (!e) e = getenv("LOCAL_RANK");
+    if (e) dev = atoi(e);
+    if (dev < 0 || dev >= n) dev = 0;
+    if (cudaSetDevice(dev) != cudaSuccess) return false;
+    g_q4.device = dev;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return false;
+    if (prop.major < 10) {
+        fprintf(stderr, "q4 gpu: device %d is sm_%d%d; this library is built for sm_100a only\n", dev,
+                prop.major, prop.minor);
+        return false;
+    }
+    g_q4.sm_count = prop.multiProcessorCount;
+    if (cudaStreamCreateWithFlags(&g_q4.own_stream, cudaStreamNonBlocking) != cudaSuccess) return false;
+    g_q4.stream = g_q4.own_stream;
+    if (cudaStreamCreateWithFlags(&g_q4.copy_stream, cudaStreamNonBlocking) != cudaSuccess)
+        g_q4.copy_stream = nullptr;
+    if (cudaMalloc(&g_q4.pos_d, sizeof(int32_t)) != cudaSuccess) return false;
+    if (cudaMemset(g_q4.pos_d, 0, sizeof(int32_t)) != cudaSuccess) return false;
+    if (cudaMallocHost(&g_q4.pos_h, sizeof(int32_t) * 64) != cudaSuccess) return false;
+    if (cudaMalloc(&g_q4.err_d, sizeof(uint32_t)) != cudaSuccess) return false;
+    if (cudaMemset(g_q4.err_d, 0, sizeof(uint32_t)) != cudaSuccess) return false;
+    g_q4.ok = true;
+    return true;
+}
+
+extern "C" void q4_hip_shutdown(void) {
+    if (!g_q4.ok) return;
+    cudaDeviceSynchronize();
+    if (g_q4.part) cudaFree(g_q4.part);
+    if (g_q4.counters) cudaFree(g_q4.counters);
+    if (g_q4.pos_d) cudaFree(g_q4.pos_d);
+    if (g_q4.pos_h) cudaFreeHost(g_q4.pos_h);
+    if (g_q4.err_d) cudaFree(g_q4.err_d);
+    if (g_q4.own_stream) cudaStreamDestroy(g_q4.own_stream);
+    if (g_q4.copy_stream) cudaStreamDestroy(g_q4.copy_stream);
+    memset(&g_q4, 0, sizeof(g_q4));
+}
+
+extern "C" bool q4_hip_ok(void) { return g_q4.ok; }
+extern "C" int q4_gpu_device(void) { return g_q4.ok ? g_q4.device : -1; }
+extern "C" void *q4_gpu_stream(void) { return g_q4.ok ? (void *)g_q4.stream : nullptr; }
+extern "C" bool q4_gpu_set_stream(void *s) {
+    if (!g_q4.ok) return q4i_fail(Q4E_INIT, "set_stream: library not initialised");
+    if (g_q4.capturing) return q4i_fail(Q4E_ARG, "set_stream: a capture is open");
+    g_q4.stream = s ? (cudaStream_t)s : g_q4.own_stream;
+    return true;
+}
+extern "C" const int32_t *q4_gpu_pos_word(void) { return g_q4.pos_d; }
+
+extern "C" uint32_t q4_gpu_last_error(void) {
+    uint32_t e = g_q4.err_h;
+    g_q4.err_h = 0;
+    if (g_q4.ok && !g_q4.capturing) {
+        uint32_t d = 0;
+        if (cudaMemcpyAsync(&d, g_q4.err_d, sizeof(d), cudaMemcpyDeviceToHost, g_q4.stream) == cudaSuccess &&
+            cudaStreamSynchronize(g_q4.stream) == cudaSuccess) {
+            if (d) (void)cudaMemsetAsync(g_q4.err_d, 0, sizeof(d), g_q4.stream);
+            e |= d;
+        } else {
+            e |= Q4E_CUDA;
+        }
+    }
+    return e;
+}
+
+extern "C" void *q4_hip_malloc(size_t n) {
+    if (!g_q4.ok || n == 0) return nullptr;
+    void *p = nullptr;
+    if (cudaMalloc(&p, n) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    return p;
+}
+extern "C" void q4_hip_free(void *p) {
+    if (p) (void)cudaFree(p);
+}
+
+/* Copy ordered after the compute stream's work; waited for unless a capture is open, in which case
+ * it becomes a memcpy node (src/q4_rocm.cu:202-214). */
+static bool sync_copy(void *dst, const void *src, size_t n, cudaMemcpyKind kind) {
+    if (!g_q4.ok) return q4i_fail(Q4E_INIT, "copy: library not initialised");
+    if (!q4i_check(cudaMemcpyAsync(dst, src, n, kind, g_q4.stream), "copy")) return false;
+    if (g_q4.capturing) return true;
+    return q4i_check(cudaStreamSynchronize(g_q4.stream), "copy sync");
+}
+extern "C" bool q4_hip_h2d(void *d, const void *h, size_t n) {
+    if (!d || !h || n == 0) return false;
+    return sync_copy(d, h, n, cudaMemcpyHostToDevice);
+}
+extern "C" bool q4_hip_d2h(void *h, const void *d, size_t n) {
+    if (!d || !h || n == 0) return false;
+    return sync_copy(h, d, n, cudaMemcpyDeviceToHost);
+}
+extern "C" bool q4_hip_d2h_async(void *h, const void *d, uint64_t n) {
+    if (!g_q4.ok || !h || !d || !n) return false;
+    return q4i_check(cudaMemcpyAsync(h, d, (size_t)n, cudaMemcpyDeviceToHost, g_q4.stream), "d2h_async");
+}
+extern "C" bool q4_hip_h2d_async(void *d, const void *h, uint64_t n) {
+    if (!g_q4.ok || !d || !h || !n) return false;
+    return q4i_check(cudaMemcpyAsync(d, h, (size_t)n, cudaMemcpyHostToDevice, g_q4.stream), "h2d_async");
+}
+extern "C" bool q4_hip_stream_sync(void) {
+    if (!g_q4.ok) return false;
+    return q4i_check(cudaStreamSynchronize(g_q4.stream), "stream_sync");
+}
+extern "C" void q4_hip_sync(void) {
+    if (g_q4.ok) (void)cudaDeviceSynchronize();
+}
+extern "C" void q4_hip_clear(void) { (void)cudaGetLastError(); }
+
+/* Device-to-device copy of n floats, stream-ordered.  The reference also waits for it outside
+ * capture (sync_copy); a stream-ordered consumer never needs that wait, so it is not reproduced. */
+extern "C" bool q4_hip_copy(float *d, const float *s, uint64_t n) {
+    if (!g_q4.ok || !d || !s || n == 0) return false;
+    return q4i_check(cudaMemcpyAsync(d, s, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, g_q4.stream),
+                     "copy d2d");
+}
+__global__ static void q4_fill_k(float *d, float v, uint64_t n) {
+    uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) d[i] = v;
+}
+extern "C" bool q4_hip_fill(float *d, float v, uint64_t n) {
+    if (!g_q4.ok || !d || n == 0) return false;
+    if (v == 0.f)
+        return q4i_check(cudaMemsetAsync(d, 0, (size_t)n * sizeof(float), g_q4.stream), "fill");
+    uint64_t blocks = (n + 255) / 256;
+    uint64_t cap = (uint64_t)g_q4.sm_count * 16;
+    q4_fill_k<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, g_q4.stream>>>(d, v, n);
+    return q4i_check(cudaGetLastError(), "fill launch");
+}
+
+/* Decode position for graph-captured kernels: stream-ordered 4-byte upload from pinned memory.
+ * A ring of staging words keeps an upload that has not executed yet from being overwritten by the
+ * next push. */
+extern "C" void q4_hip_pos_push(int32_t pos) {
+    if (!g_q4.ok) return;
+    static unsigned slot = 0;
+    int32_t *h = g_q4.pos_h + (slot++ & 63u);
+    *h = pos;
+    (void)cudaMemcpyAsync(g_q4.pos_d, h, sizeof(int32_t), cudaMemcpyHostToDevice, g_q4.stream);
+}
+extern "C" int q4_hip_capturing(void) { return g_q4.capturing; }
+extern "C" int q4_hip_pos_dev_ok(void) { return g_q4.ok && g_q4.pos_d && g_q4.pos_h; }
+
+extern "C" int q4_hip_graph_begin(void) {
+    if (!g_q4.ok || g_q4.capturing) return 0;
+    if (cudaStreamBeginCapture(g_q4.stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    g_q4.capturing = 1;
+    return 1;
+}
+extern "C" void *q4_hip_graph_end(void) {
+    if (!g_q4.ok || !g_q4.capturing) return nullptr;
+    g_q4.capturing = 0;
+    cudaGraph_t g = nullptr;
+    if (cudaStreamEndCapture(g_q4.stream, &g) != cudaSuccess || !g) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    size_t nn = 0;
+    (void)cudaGraphGetNodes(g, nullptr, &nn);
+    g_q4.last_graph_nodes = (uint32_t)nn;
+    cudaGraphExec_t ex = nullptr;
+    cudaError_t e = cudaGraphInstantiate(&ex, g, 0);
+    (void)cudaGraphDestroy(g);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    (void)cudaGraphUpload(ex, g_q4.stream);
+    return (void *)ex;
+}
+extern "C" uint32_t q4_hip_graph_nodes(void *exec) {
+    (void)exec;
+    return g_q4.last_graph_nodes;
+}
+extern "C" bool q4_hip_graph_launch(void *exec) {
+    if (!g_q4.ok || !exec) return false;
+    return q4i_check(cudaGraphLaunch((cudaGraphExec_t)exec, g_q4.stream), "graph launch");
+}
+extern "C" void q4_hip_graph_free(void *exec) {
+    if (exec) (void)cudaGraphExecDestroy((cudaGraphExec_t)exec);
+}
+
+extern "C" bool q4_hip_qsa_topk_alloc(void) {
+    if (!g_q4.ok) return false;
+    /* room for one session at the largest supported shape: 4 kv heads x 256 splits (+16 group
+     * records) x 16 heads x (256 + 2) floats, the same role as g_attn_part, src/q4_rocm.cu:7705-7706 */
+    return q4i_scratch((size_t)4 * (256 + 16) * 16 * 258, (size_t)4 * 17);
+}
