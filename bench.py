@@ -1,0 +1,520 @@
+#!/usr/bin/env python
+"""Benchmark of the KV-cache + decode-attention hot path.
+
+Headline workload (`config.workload`): multi-session batched QSA decode -- 64 concurrent sessions
+with seeded context lengths uniform in [1024, 131072], q8_0 KV, 12 attention layers, 16 query / 2
+kv heads, head_dim 128, 2051 selected positions per session, layer and kv head (4 sink + 1024
+recent + 1023 random).  One step = one decoded token for every session: for each layer the fused
+K/V append (quantise + scatter) and the sparse decode attention, as one CUDA graph.  Sessions are
+sharded round-robin over the ranks with no collective (strong scaling: 64 sessions in total).
+
+`value` = sessions x tokens / s with every input resident in HBM; `e2e` = the same step with q, new
+K/V rows, selection lists and positions copied from pinned host memory and the outputs copied back
+inside the timed region.  L2 is defeated by rotation: consecutive steps run on different replicas
+of the session group (own caches, own lists), sized so that >= 512 MB of distinct rows pass between
+two uses of the same row.
+
+Extra objects on the same JSON line (rank 0, 1 GPU): `single_session_ctx262144` (QSA decode, batch
+1, us per layer under graph replay), `dense_ctx262144` (full attention over 262144 rows for q8_0 /
+f16 / f32), `roofline` for the dominant kernel and `cpu_baseline` (the CPU oracle on host cores).
+
+`--impl reference` times the reference's own CPU arithmetic for the same step (the oracle port:
+q8_0 quantise of the new rows + scalar attention over the dequantised selected rows) on all host
+threads, on a bounded sample of the sessions.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "suzuqu-engine-4exp_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+N_LAYERS, N_HEAD, N_KVH, HD, WIDTH = 12, 16, 2, 128, 2051
+SINK, RECENT, NRAND = 4, 1024, 1023
+KVW = N_KVH * HD
+ROW_BYTES = 136                       # one (token, kv head) q8_0 row: 128 codes + 4 fp16 scales
+SCALE = 1.0 / math.sqrt(HD)
+SEED = 20261125
+PAD = 64                              # token slots appended during the run
+L2_BYTES = 126e6
+# dram bytes per algorithmic byte of the batched decode kernel, from the ncu capture summarised in
+# profiles/ (None until a capture exists)
+DECODE_TRAFFIC_RATIO = None
+
+
+def draw_contexts(n, lo=1024, hi=131072, seed=SEED + 4):
+    return np.random.default_rng(seed).integers(lo, hi + 1, n).astype(np.int64)
+
+
+def selection(rng, ctx):
+    """sorted unique {0..3} + 1023 random of [4, ctx-1024) + the last 1024; everything when ctx <= 2051"""
+    out = np.full(WIDTH, -1, np.int32)
+    if ctx <= WIDTH:
+        out[:ctx] = np.arange(ctx)
+        return out
+    mid = rng.choice(ctx - RECENT - SINK, NRAND, replace=False) + SINK
+    out[:] = np.sort(np.concatenate([np.arange(SINK), mid, np.arange(ctx - RECENT, ctx)]))
+    return out
+
+
+def gathered_bytes(ctx):
+    """algorithmic bytes one layer's decode reads for one session: rows x kv heads x (K + V)"""
+    return min(int(ctx), WIDTH) * N_KVH * ROW_BYTES * 2
+
+
+class ClockSampler:
+    def __init__(self, gpu_index):
+        self.proc = None
+        self.path = "/tmp/q4_bench_clocks_%d.csv" % os.getpid()
+        q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+        try:
+            self.f = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(gpu_index), "--query-gpu=" + q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=self.f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if not self.proc:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.f.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        try:
+            os.remove(self.path)
+        except OSError:
+            pass
+        if sm:
+            out["sm_mhz"] = float(np.median(sm))
+            out["sm_max_mhz"] = float(max(mx))
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+# ------------------------------------------------------------------------------------------ CPU arm
+def cpu_sample_problem(ctxs, n_sessions, seed):
+    """Host-side copy of the step for the first n_sessions sessions: per (session, layer) the selected
+    rows only, quantised by the oracle into a compact cache with the lists remapped onto it (same rows
+    dequantised and dotted as on the full cache; the full 27 GB of caches is not materialised)."""
+    from oracle import q4_oracle as oracle
+    rng = np.random.default_rng(seed)
+    items, news = [], []
+    for s in range(n_sessions):
+        ctx = int(ctxs[s])
+        for layer in range(N_LAYERS):
+            idx = np.stack([selection(rng, ctx) for _ in range(N_KVH)])
+            live = np.unique(idx[idx >= 0])
+            remap = np.full(ctx, -1, np.int32)
+            remap[live] = np.arange(len(live), dtype=np.int32)
+            cidx = np.where(idx >= 0, remap[np.maximum(idx, 0)], -1).astype(np.int32)
+            rows = rng.standard_normal((2, len(live), KVW), dtype=np.float32)
+            kc, vc = oracle.kv_write(rows[0], 2), oracle.kv_write(rows[1], 2)
+            q = oracle.bf16_to_f32(oracle.f32_to_bf16(rng.standard_normal(N_HEAD * HD, dtype=np.float32)))
+            items.append(dict(q=q, kc=kc, vc=vc, out=np.empty(N_HEAD * HD, np.float32), idx=cidx, width=WIDTH,
+                              idx_kvh_stride=WIDTH, kv_base=0, max_kv=len(live)))
+            news.append(rng.standard_normal((2, KVW), dtype=np.float32))
+    return items, news
+
+
+def cpu_step(items, news, threads):
+    """one decoded token for the sampled sessions: quantise the new K and V rows of every layer
+    (kv_write), then sparse attention of every (session, layer) on `threads` host threads"""
+    from oracle import q4_oracle as oracle
+    for nw in news:
+        oracle.kv_write(nw[0], 2)
+        oracle.kv_write(nw[1], 2)
+    oracle.attn_items(items, N_HEAD, N_KVH, HD, SCALE, 2, threads)
+
+
+def cpu_baseline(ctxs, budget_s, n_sessions=4):
+    from oracle import q4_oracle as oracle
+    threads = max(1, min(oracle.max_threads(), os.cpu_count() or 1))
+    items, news = cpu_sample_problem(ctxs, n_sessions, SEED + 9)
+    cpu_step(items, news, threads)            # warm-up
+    t0 = time.perf_counter()
+    reps = 0
+    while reps < 3 or time.perf_counter() - t0 < budget_s:
+        cpu_step(items, news, threads)
+        reps += 1
+        if time.perf_counter() - t0 > 3 * budget_s:
+            break
+    dt = time.perf_counter() - t0
+    return {"value": n_sessions * reps / dt, "unit": "session*tok/s", "cores": threads, "kind": "port",
+            "sample": "%d of the 64 sessions x 12 layers x %d reps (%.1f s); compact caches of the selected rows"
+                      % (n_sessions, reps, dt)}
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    from oracle import q4_oracle as oracle
+    ctxs = draw_contexts(args.sessions)
+    n_s = 4
+    threads = max(1, min(oracle.max_threads(), os.cpu_count() or 1))
+    items, news = cpu_sample_problem(ctxs, n_s, SEED + 9)
+    for _ in range(args.warmup):
+        cpu_step(items, news, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_step(items, news, threads)
+    dt = time.perf_counter() - t0
+    v = n_s * args.steps / dt
+    line = {"impl": "reference", "metric": "decode_attn_session_tok_per_s", "value": v, "unit": "session*tok/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "q8_0+f32",
+            "data": "synthetic", "config": workload_config(args.sessions, 1),
+            "cpu_baseline": {"value": v, "unit": "session*tok/s", "cores": threads, "kind": "port",
+                             "sample": "each step = %d of the 64 sessions x 12 layers (compact caches of the "
+                                       "selected rows), all host threads" % n_s},
+            "e2e": {"value": v, "unit": "session*tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(sessions, groups):
+    return {"workload": "configs[3]: multi-session batched QSA decode, %d sessions, ctx ~ U[1024,131072], "
+                        "q8_0 KV, 12 layers x (fused K/V append + sparse decode attention), 16 Q / 2 KV heads, "
+                        "hd 128, 2051 selected positions per kv head" % sessions,
+            "sessions": sessions, "layers": N_LAYERS, "selected_positions": WIDTH, "kv": "q8_0", "q": "bf16",
+            "parallelism": "sessions sharded round-robin, no collective",
+            "l2": "rotation over %d replicas of the session group (>=512 MB of distinct rows between reuse)" % groups}
+
+
+# ------------------------------------------------------------------------------------------ GPU arm
+class Group:
+    """One replica of this rank's session group: caches, selection lists, per-step inputs, graph."""
+
+    def __init__(self, q4gpu, torch, ctxs, seed, fill=True):
+        self.torch, self.q4gpu = torch, q4gpu
+        self.ctxs = [int(c) for c in ctxs]
+        n = len(self.ctxs)
+        self.n = n
+        rng = np.random.default_rng(seed)
+        self.stores = [q4gpu.KVStore(N_LAYERS, N_KVH, HD, c + PAD, q4gpu.KIND_Q8) for c in self.ctxs]
+        if fill:
+            for st, c in zip(self.stores, self.ctxs):
+                fill_store(torch, st, c)
+        self.batch = q4gpu.Batch(self.stores)
+        idx = np.empty((N_LAYERS, n, N_KVH, WIDTH), np.int32)
+        for layer in range(N_LAYERS):
+            for s, c in enumerate(self.ctxs):
+                for kh in range(N_KVH):
+                    idx[layer, s, kh] = selection(rng, c)
+        self.idx_h = torch.from_numpy(idx).pin_memory()
+        self.q_h = torch.randn(N_LAYERS, n, N_HEAD, HD).to(torch.bfloat16).pin_memory()
+        self.k_h = torch.randn(N_LAYERS, n, KVW).pin_memory()
+        self.v_h = torch.randn(N_LAYERS, n, KVW).pin_memory()
+        self.out_h = torch.empty(N_LAYERS, n, N_HEAD, HD).pin_memory()
+        self.idx, self.q, self.k, self.v = self.idx_h.cuda(), self.q_h.cuda(), self.k_h.cuda(), self.v_h.cuda()
+        self.out = torch.empty(N_LAYERS, n, N_HEAD, HD, device="cuda")
+        self.t = 0
+        self.graph = None
+
+    def enqueue_layers(self):
+        for layer in range(N_LAYERS):
+            self.batch.append(layer, self.k[layer], self.v[layer])
+            self.batch.decode(layer, self.q[layer], self.out[layer], N_HEAD, SCALE, idx=self.idx[layer],
+                              width=WIDTH, idx_kvh_stride=WIDTH, idx_sess_stride=N_KVH * WIDTH, q_bf16=True)
+
+    def capture(self, L):
+        assert L.q4_hip_graph_begin() == 1
+        self.enqueue_layers()
+        self.graph = L.q4_hip_graph_end()
+        assert self.graph, "graph capture failed"
+
+    def step(self, L):
+        """the token at slot ctx + t of every session (slots wrap inside the PAD region)"""
+        self.batch.set_pos([c + (self.t % PAD) for c in self.ctxs])
+        self.t += 1
+        assert L.q4_hip_graph_launch(self.graph)
+
+    def step_e2e(self, L):
+        for d, h in ((self.q, self.q_h), (self.k, self.k_h), (self.v, self.v_h), (self.idx, self.idx_h)):
+            assert L.q4_hip_h2d_async(d.data_ptr(), h.data_ptr(), h.numel() * h.element_size())
+        self.step(L)
+        assert L.q4_hip_d2h_async(self.out_h.data_ptr(), self.out.data_ptr(), self.out.numel() * 4)
+
+    def e2e_bytes(self):
+        h2d = sum(h.numel() * h.element_size() for h in (self.q_h, self.k_h, self.v_h, self.idx_h)) + 4 * self.n
+        return h2d, self.out_h.numel() * 4
+
+    def algorithmic_bytes_per_layer(self):
+        return sum(gathered_bytes(c) for c in self.ctxs)
+
+
+def fill_store(torch, st, rows, chunk=32768):
+    """cache contents N(0,1) before quantisation: rows generated on the device and appended (quantised)
+    through the library"""
+    for layer in range(st.n_layers):
+        for p0 in range(0, rows, chunk):
+            n = min(chunk, rows - p0)
+            k = torch.randn(n, st.n_kvh * st.hd, device="cuda")
+            v = torch.randn(n, st.n_kvh * st.hd, device="cuda")
+            st.append(layer, k, v, p0, n)
+
+
+def timed(torch, ext, fn, reps):
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(ext)
+    for i in range(reps):
+        fn(i)
+    ev1.record(ext)
+    ev1.synchronize()
+    return ev0.elapsed_time(ev1) * 1e-3
+
+
+def extras_single_session(torch, q4gpu, L, ext, peak_gbs):
+    """configs[1]: one session at ctx 262144, batch 1, 12 layers; us per layer under graph replay"""
+    ctx, R = 262144, 24
+    g = []
+    st = q4gpu.KVStore(N_LAYERS, N_KVH, HD, ctx + PAD, q4gpu.KIND_Q8)
+    q4gpu.use_torch_stream()
+    fill_store(torch, st, ctx)
+    torch.cuda.synchronize()
+    L.q4_gpu_set_stream(None)
+    rng = np.random.default_rng(SEED + 2)
+    idx = np.empty((R, N_LAYERS, N_KVH, WIDTH), np.int32)
+    for r in range(R):                      # every replica selects around a different virtual end
+        for layer in range(N_LAYERS):
+            for kh in range(N_KVH):
+                idx[r, layer, kh] = selection(rng, ctx - r * 2048)
+    idx_d = torch.from_numpy(idx).cuda()
+    q = torch.randn(R, N_LAYERS, N_HEAD, HD, device="cuda").to(torch.bfloat16)
+    k = torch.randn(N_LAYERS, KVW, device="cuda")
+    v = torch.randn(N_LAYERS, KVW, device="cuda")
+    out = torch.empty(N_LAYERS, N_HEAD, HD, device="cuda")
+    torch.cuda.synchronize()
+    graphs, graphs_attn = [], []
+    for with_append, dst in ((True, graphs), (False, graphs_attn)):
+        for r in range(R):
+            assert L.q4_hip_graph_begin() == 1
+            for layer in range(N_LAYERS):
+                if with_append:
+                    st.append_d(layer, k[layer], v[layer])
+                st.decode(layer, q[r, layer], out[layer], N_HEAD, SCALE, idx=idx_d[r, layer], width=WIDTH,
+                          idx_kvh_stride=WIDTH, n_kv=0, q_bf16=True)
+            gr = L.q4_hip_graph_end()
+            assert gr
+            dst.append(gr)
+    res = {}
+    for name, gl in (("us_per_layer", graphs), ("us_per_layer_attn_only", graphs_attn)):
+        def one(i, gl=gl):
+            L.q4_hip_pos_push(ctx + (i % PAD))
+            assert L.q4_hip_graph_launch(gl[i % R])
+        timed(torch, ext, one, R)
+        n = 10 * R
+        dt = timed(torch, ext, one, n)
+        res[name] = 1e6 * dt / (n * N_LAYERS)
+    by = gathered_bytes(ctx)
+    gbs = by / (res["us_per_layer"] * 1e-6) / 1e9
+    res.update({"workload": "configs[1]: single-session QSA decode, ctx 262144, batch 1, 12 layers, graph replay, "
+                            "%d rotating selections" % R,
+                "gathered_bytes_per_layer": by, "achieved_gbs": gbs, "frac_of_measured_hbm": gbs / peak_gbs,
+                "tok_per_s": 1e6 / (res["us_per_layer"] * N_LAYERS),
+                "note": "latency-bound: 1.1 MB per dependent layer is 0.17 us of HBM time"})
+    for gr in graphs + graphs_attn:
+        L.q4_hip_graph_free(gr)
+    st.close()
+    return res
+
+
+def extras_dense(torch, q4gpu, L, ext, peak_gbs):
+    """configs[4] on one GPU: full attention over 262144 rows, q8_0 / f16 / f32 KV, 12 layers"""
+    ctx = 262144
+    res = {}
+    for name, kind, rowb in (("q8_0", 2, 136), ("f16", 1, 256), ("f32", 0, 512)):
+        st = q4gpu.KVStore(N_LAYERS, N_KVH, HD, ctx, kind)
+        q4gpu.use_torch_stream()
+        fill_store(torch, st, ctx)
+        torch.cuda.synchronize()
+        L.q4_gpu_set_stream(None)
+        q = torch.randn(N_LAYERS, N_HEAD, HD, device="cuda").to(torch.bfloat16)
+        out = torch.empty(N_LAYERS, N_HEAD, HD, device="cuda")
+        torch.cuda.synchronize()
+
+        def one(i):
+            layer = i % N_LAYERS
+            st.decode(layer, q[layer], out[layer], N_HEAD, SCALE, n_kv=ctx, q_bf16=True)
+        timed(torch, ext, one, N_LAYERS)
+        n = 4 * N_LAYERS
+        dt = timed(torch, ext, one, n)
+        by = ctx * N_KVH * rowb * 2
+        us = 1e6 * dt / n
+        res[name] = {"us_per_layer": us, "bytes_per_layer": by, "achieved_gbs": by / us / 1e3,
+                     "frac_of_measured_hbm": by / us / 1e3 / peak_gbs}
+        st.close()
+    res["workload"] = "configs[4] on 1 GPU: dense decode over ctx 262144, 12 layers, inputs 12 x bytes_per_layer >> L2"
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--sessions", type=int, default=64)
+    ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import q4gpu
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: libq4gpu has no CPU path")
+    torch.cuda.set_device(local)
+    os.environ.setdefault("Q4_GPU_DEVICE", str(local))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    L = q4gpu.init()
+    assert L.q4_hip_qsa_topk_alloc()
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
+    peak_src = "measured (MEASURED_PEAKS.json)" if "hbm_gbs" in peaks else "fallback 6.65 TB/s"
+
+    ctxs = draw_contexts(args.sessions)
+    mine = [int(c) for i, c in enumerate(ctxs) if i % world == rank]
+    step_bytes = N_LAYERS * sum(gathered_bytes(c) for c in mine)
+    groups_n = max(2, int(math.ceil(512e6 / max(step_bytes, 1))))
+    torch.manual_seed(SEED + rank)
+    q4gpu.use_torch_stream()
+    groups = [Group(q4gpu, torch, mine, SEED + 100 * rank + g) for g in range(groups_n)]
+    torch.cuda.synchronize()
+    L.q4_gpu_set_stream(None)                 # capture and timing on the library's own stream
+    ext = torch.cuda.ExternalStream(L.q4_gpu_stream())
+    for g in groups:
+        g.batch.set_pos(g.ctxs)
+        g.enqueue_layers()                    # eager once: scratch grows outside the capture
+        g.capture(L)
+    assert L.q4_hip_stream_sync()
+
+    def barrier():
+        L.q4_hip_stream_sync()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if dist is None:
+            return x
+        t = torch.tensor([x], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing
+    for i in range(args.warmup):
+        groups[i % groups_n].step(L)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    dt = timed(torch, ext, lambda i: groups[i % groups_n].step(L), args.steps)
+    barrier()
+    dt = max_over_ranks(dt)
+    # ---- end to end: host buffers in, outputs out, every step
+    for i in range(3):
+        groups[i % groups_n].step_e2e(L)
+    barrier()
+    dt_e2e = timed(torch, ext, lambda i: groups[i % groups_n].step_e2e(L), args.steps)
+    barrier()
+    dt_e2e = max_over_ranks(dt_e2e)
+    clocks = sampler.stop() if sampler else None
+
+    status = L.q4_gpu_last_error()
+    assert status == 0, "device status %#x" % status
+    if rank != 0:
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the dominant kernel: the batched decode launch, timed alone
+    def dec(i):
+        g = groups[i % groups_n]
+        layer = (i // groups_n) % N_LAYERS
+        g.batch.decode(layer, g.q[layer], g.out[layer], N_HEAD, SCALE, idx=g.idx[layer], width=WIDTH,
+                       idx_kvh_stride=WIDTH, idx_sess_stride=N_KVH * WIDTH, q_bf16=True)
+    n_dec = groups_n * N_LAYERS
+    timed(torch, ext, dec, n_dec)
+    dt_dec = timed(torch, ext, dec, 3 * n_dec) / (3 * n_dec)
+    alg = groups[0].algorithmic_bytes_per_layer()
+    achieved = alg / dt_dec / 1e9
+    roofline = {"kernel": "q4_decode_k<q8_0 planar, hd 128> (batched sparse decode, %d sessions per launch)" % len(mine),
+                "bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
+                "peak_source": peak_src, "algorithmic_bytes_per_launch": alg, "us_per_launch": dt_dec * 1e6,
+                "traffic": (alg * DECODE_TRAFFIC_RATIO) if DECODE_TRAFFIC_RATIO else None}
+    h2d, d2h = groups[0].e2e_bytes()
+    line = {"metric": "decode_attn_session_tok_per_s", "value": args.sessions * args.steps / dt,
+            "unit": "session*tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "q8_0 KV, f16 tensor-core products, f32 accumulate", "data": "synthetic",
+            "config": workload_config(args.sessions, groups_n),
+            "e2e": {"value": args.sessions * args.steps / dt_e2e, "unit": "session*tok/s",
+                    "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
+                    "ms_per_step": 1e3 * dt_e2e / args.steps},
+            "gpu_launches": args.steps * N_LAYERS * 2 * world, "clocks": clocks, "roofline": roofline,
+            "us_per_layer": 1e6 * dt / (args.steps * N_LAYERS),
+            "attn_roofline_session_tok_per_s": args.sessions / (N_LAYERS * sum(gathered_bytes(c) for c in ctxs)
+                                                                / world / (peak_gbs * 1e9))}
+    for g in groups:
+        L.q4_hip_graph_free(g.graph)
+        g.batch.close()
+        for st in g.stores:
+            st.close()
+    groups.clear()
+    torch.cuda.empty_cache()
+    if world == 1 and not args.no_extras:
+        line["single_session_ctx262144"] = extras_single_session(torch, q4gpu, L, ext, peak_gbs)
+        line["dense_ctx262144"] = extras_dense(torch, q4gpu, L, ext, peak_gbs)
+        line["cpu_baseline"] = cpu_baseline(ctxs, args.cpu_seconds)
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -459,6 +459,53 @@ Q4O_API void q4o_lse_merge(const float *parts, uint32_t n_parts, uint32_t n_head
     }
 }
 
+/* Many independent decode-attention problems in one call, OpenMP over (item, head): the CPU
+ * baseline of the batched multi-session decode.  Each item is one q4o_attn call with n_tok = 1. */
+typedef struct {
+    const float *q;
+    const void *kcache, *vcache;
+    const float *gate;
+    float *out;
+    const int32_t *idx;
+    uint32_t width, idx_kvh_stride, kv_base, max_kv;
+} q4o_item;
+Q4O_API int q4o_attn_items(const q4o_item *items, uint32_t n_items, uint32_t n_head, uint32_t n_kvh,
+                           uint32_t hd, float scale, int kind, int threads) {
+    if (!items || !n_items || !n_head || !n_kvh || !hd || n_head % n_kvh) return 1;
+    const uint32_t gqa = n_head / n_kvh;
+    const long total = (long)n_items * n_head;
+    uint32_t maxn = 1;
+    for (uint32_t i = 0; i < n_items; i++) {
+        uint32_t n = items[i].idx ? items[i].width : items[i].kv_base + 1;
+        if (n > maxn) maxn = n;
+    }
+#ifdef _OPENMP
+    if (threads < 1) threads = 1;
+#pragma omp parallel num_threads(threads)
+#endif
+    {
+        float *sc = (float *)malloc(sizeof(float) * maxn);
+        float *row = (float *)malloc(sizeof(float) * hd);
+#ifdef _OPENMP
+#pragma omp for schedule(dynamic, 1)
+#endif
+        for (long w = 0; w < total; w++) {
+            const q4o_item *it = items + w / n_head;
+            uint32_t h = (uint32_t)(w % n_head), kh = h / gqa;
+            uint32_t n_kv = it->kv_base + 1 > it->max_kv ? it->max_kv : it->kv_base + 1;
+            const int32_t *pos = NULL;
+            if (it->idx) pos = it->idx_kvh_stride ? it->idx + (size_t)kh * it->idx_kvh_stride : it->idx;
+            attn_one(it->q + (size_t)h * hd, (const uint8_t *)it->kcache, (const uint8_t *)it->vcache,
+                     it->gate ? it->gate + (size_t)h * hd : NULL, it->out + (size_t)h * hd, n_kvh, hd, kind,
+                     kh, scale, pos, it->width, n_kv, 0, sc, row);
+        }
+        free(sc);
+        free(row);
+    }
+    (void)threads;
+    return 0;
+}
+
 Q4O_API int q4o_max_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -68,6 +68,9 @@ def lib():
         L.q4o_lse_merge.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p,
                                     C.c_void_p]
         L.q4o_max_threads.restype = C.c_int
+        L.q4o_attn_items.restype = C.c_int
+        L.q4o_attn_items.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float,
+                                     C.c_int, C.c_int]
         _LIB = L
     return _LIB
 
@@ -237,3 +240,22 @@ def lse_merge(parts, n_head, hd, gate=None):
 
 def max_threads():
     return int(lib().q4o_max_threads())
+
+
+class Item(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("kcache", C.c_void_p), ("vcache", C.c_void_p), ("gate", C.c_void_p),
+                ("out", C.c_void_p), ("idx", C.c_void_p), ("width", C.c_uint32),
+                ("idx_kvh_stride", C.c_uint32), ("kv_base", C.c_uint32), ("max_kv", C.c_uint32)]
+
+
+def attn_items(items, n_head, n_kvh, hd, scale, kind, threads):
+    """items: list of dicts with numpy arrays q, kc, vc, out and optional gate, idx (+ width,
+    idx_kvh_stride, kv_base, max_kv); one decode token each; parallel over (item, head)."""
+    arr = (Item * len(items))()
+    for a, it in zip(arr, items):
+        a.q, a.kcache, a.vcache, a.out = _p(it["q"]), _p(it["kc"]), _p(it["vc"]), _p(it["out"])
+        a.gate, a.idx = _p(it.get("gate")), _p(it.get("idx"))
+        a.width, a.idx_kvh_stride = it.get("width", 0), it.get("idx_kvh_stride", 0)
+        a.kv_base, a.max_kv = it.get("kv_base", 0), it.get("max_kv", 0xFFFFFFFF)
+    rc = lib().q4o_attn_items(arr, len(items), n_head, n_kvh, hd, scale, kind, threads)
+    assert rc == 0

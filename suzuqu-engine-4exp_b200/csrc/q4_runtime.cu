@@ -250,7 +250,8 @@ extern "C" void q4_hip_graph_free(void *exec) {
 
 extern "C" bool q4_hip_qsa_topk_alloc(void) {
     if (!g_q4.ok) return false;
-    /* room for one session at the largest supported shape: 4 kv heads x 256 splits (+16 group
-     * records) x 16 heads x (256 + 2) floats, the same role as g_attn_part, src/q4_rocm.cu:7705-7706 */
-    return q4i_scratch((size_t)4 * (256 + 16) * 16 * 258, (size_t)4 * 17);
+    /* 32 MB of records + 64 Ki counters: one session at the largest supported shape (4 kv heads x
+     * 272 records x 16 heads x 258 floats) or a batch of a few hundred sessions at the usual one;
+     * the same role as g_attn_part, src/q4_rocm.cu:7705-7706 */
+    return q4i_scratch((size_t)8 << 20, (size_t)64 << 10);
 }
