@@ -348,11 +348,13 @@ def extras_single_session(torch, q4gpu, L, ext, peak_gbs):
     return res
 
 
-def extras_dense(torch, q4gpu, L, ext, peak_gbs):
+def extras_dense(torch, q4gpu, L, ext, peak_gbs, kinds=("q8_0", "f16", "f32")):
     """configs[4] on one GPU: full attention over 262144 rows, q8_0 / f16 / f32 KV, 12 layers"""
     ctx = 262144
     res = {}
     for name, kind, rowb in (("q8_0", 2, 136), ("f16", 1, 256), ("f32", 0, 512)):
+        if name not in kinds:
+            continue
         st = q4gpu.KVStore(N_LAYERS, N_KVH, HD, ctx, kind)
         q4gpu.use_torch_stream()
         fill_store(torch, st, ctx)
@@ -386,6 +388,11 @@ def main():
     ap.add_argument("--sessions", type=int, default=64)
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--groups", type=int, default=0, help="replicas of the session group (0 = enough to defeat L2)")
+    ap.add_argument("--ctx-max", type=int, default=131072, help="upper end of the context-length draw (profiling: small)")
+    ap.add_argument("--only", default="", choices=["", "single", "dense"],
+                    help="run just one of the ctx-262144 extras (for profiler captures)")
+    ap.add_argument("--dense-kinds", default="q8_0,f16,f32")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -416,10 +423,17 @@ def main():
     peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
     peak_src = "measured (MEASURED_PEAKS.json)" if "hbm_gbs" in peaks else "fallback 6.65 TB/s"
 
-    ctxs = draw_contexts(args.sessions)
+    if args.only:
+        ext = torch.cuda.ExternalStream(L.q4_gpu_stream())
+        torch.manual_seed(SEED)
+        res = (extras_single_session(torch, q4gpu, L, ext, peak_gbs) if args.only == "single"
+               else extras_dense(torch, q4gpu, L, ext, peak_gbs, args.dense_kinds.split(",")))
+        print(json.dumps({"only": args.only, "result": res}), flush=True)
+        return
+    ctxs = draw_contexts(args.sessions, hi=args.ctx_max)
     mine = [int(c) for i, c in enumerate(ctxs) if i % world == rank]
     step_bytes = N_LAYERS * sum(gathered_bytes(c) for c in mine)
-    groups_n = max(2, int(math.ceil(512e6 / max(step_bytes, 1))))
+    groups_n = args.groups or max(2, int(math.ceil(512e6 / max(step_bytes, 1))))
     torch.manual_seed(SEED + rank)
     q4gpu.use_torch_stream()
     groups = [Group(q4gpu, torch, mine, SEED + 100 * rank + g) for g in range(groups_n)]

@@ -219,6 +219,14 @@ bool q4_gpu_batch_decode(q4_gpu_batch *b, uint32_t layer, const void *q, int q_b
                          uint32_t idx_kvh_stride, uint32_t idx_sess_stride, uint32_t n_head,
                          float scale);
 
+/* ---- dense causal prefill attention on the tensor cores (tcgen05 / TMEM): query t of the chunk
+ * attends rows [0, kv_base + t + 1) of the store.  q, out: [n_tok][n_head][hd] bf16; gate: fp32 or
+ * NULL.  Replaces q4_hip_qsa_decode_n with n_tok > 1 (gqa_prefill_k, src/q4_rocm.cu:7019-7206; host
+ * slicing src/q4_fwd.c:1745-1753 is not needed). */
+bool q4_gpu_kv_prefill(const q4_gpu_kv *kv, uint32_t layer, const void *q_bf16, const float *gate,
+                       void *out_bf16, uint32_t n_head, uint32_t n_tok, uint32_t kv_base,
+                       float scale);
+
 #ifdef __cplusplus
 }
 #endif

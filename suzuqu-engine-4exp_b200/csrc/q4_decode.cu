@@ -10,9 +10,13 @@
  * Shape of the kernel.  The path is bound by HBM, and with 8 query heads sharing each K/V byte the
  * scalar FMA pipe cannot keep up with B200's memory system (8 FMA per int8 byte at ~23 B/clk/SM
  * is more than the 128 FMA/clk an SM has), so the two contractions run on the tensor cores with
- * warp-level MMA while every byte of the cache goes straight from global memory into registers,
- * once, with sector-aligned 4/8/16-byte loads -- no shared-memory staging, no block barrier in
- * the main loop, so warps stream independently.
+ * warp-level MMA.  Every byte of the cache is read from global memory once.  For the planar q8_0
+ * store at hd 128 each warp owns a 3-stage ring in shared memory that it fills with 16-byte
+ * cp.async copies (whole 128-byte rows, gathered by position) two steps ahead of the step it is
+ * computing, so the gather latency of HBM is hidden behind the arithmetic without spending
+ * registers; there is no block barrier in the main loop, warps stream independently.  The rings are
+ * swizzled so that the fragment reads are bank-conflict free.  The other layouts load fragments
+ * straight into registers with sector-aligned 4/8/16-byte loads.
  *
  *   one warp-step = 16 positions:
  *     S^T[16 pos x 8 heads]  = K[16 x hd] . Q^T        (m16n8k16, K rows are the A operand)
@@ -85,6 +89,23 @@ __device__ __forceinline__ uint4 ldg128(const void *p) {
         : "l"(p));
     return v;
 }
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void *gsrc, uint32_t src_bytes) {
+    /* src_bytes = 0 writes 16 zero bytes (used for padding positions) */
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
     asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
@@ -149,16 +170,33 @@ __device__ __forceinline__ int qk_dim(int ks, int t) {
 }
 
 /* ---- the kernel ---------------------------------------------------------------------------- */
+constexpr int RING_STAGES = 3;
+constexpr int RING_STAGE_BYTES = 2048 + 2048 + 256 + 64;   /* K rows, V rows, scale rows, positions */
+
 template <int LAY, int HD, int NHT>
-__global__ void __launch_bounds__(DEC_THREADS, (HD * NHT <= 128) ? 3 : 1)
+struct DecCfg {
+    static constexpr bool STAGED = (LAY == LAY_Q8P && HD == 128);
+    static constexpr int HEADS = 8 * NHT;
+    static constexpr int REC = HD + 4;          /* acc[HD], m, l, 2 pad: 16-byte aligned records */
+    static constexpr size_t EPI_BYTES = (size_t)DEC_WARPS * HEADS * REC * sizeof(float);
+    static constexpr size_t RING_BYTES = STAGED ? (size_t)DEC_WARPS * RING_STAGES * RING_STAGE_BYTES : 0;
+    static constexpr size_t SMEM = EPI_BYTES > RING_BYTES ? EPI_BYTES : RING_BYTES;
+    static constexpr int MIN_BLOCKS = STAGED ? (NHT == 1 ? 4 : 2) : (HD * NHT <= 128 ? 3 : 1);
+};
+
+template <int LAY, int HD, int NHT>
+__global__ void __launch_bounds__(DEC_THREADS, (DecCfg<LAY, HD, NHT>::MIN_BLOCKS))
 q4_decode_k(const DecParams P) {
+    using Cfg = DecCfg<LAY, HD, NHT>;
     constexpr int NB = HD / 32;   /* q8_0 blocks per row */
     constexpr int KS = HD / 16;   /* k-steps of the QK product */
     constexpr int MT = HD / 16;   /* 16-dim output tiles of the PV product */
-    constexpr int HEADS = 8 * NHT;
-    constexpr int REC = HD + 2;
+    constexpr int HEADS = Cfg::HEADS;
+    constexpr int REC = Cfg::REC;
     constexpr bool Q8 = (LAY == LAY_Q8P || LAY == LAY_Q8R);
+    constexpr int NBQ = Q8 ? NB : 1;
 
+    extern __shared__ __align__(16) uint8_t smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const uint32_t split = blockIdx.x, kh = blockIdx.y, u = blockIdx.z;
     const uint32_t S = P.S;
@@ -180,6 +218,19 @@ q4_decode_k(const DecParams P) {
     if (LAY == LAY_Q8P)
         sbase = C.s + (uint64_t)P.layer * C.s_layer_stride + (uint64_t)kh * C.s_kvh_stride;
     const uint32_t tok_stride = C.tok_stride, s_tok_stride = C.s_tok_stride;
+    const uint32_t max_kv = C.max_kv;
+
+    /* position j of the list / range, or -1 (padding, out of range) */
+    auto position = [&](uint32_t j) -> int32_t {
+        if (j >= n_pos) return -1;
+        if (!list) return (int32_t)j;
+        int32_t p = list[j];
+        if (p >= (int32_t)max_kv) {
+            atomicOr(P.err, (uint32_t)Q4E_RANGE);
+            p = -1;
+        }
+        return p;
+    };
 
     /* ---- Q fragments (B operand of the QK product): head nt*8+g, dims qk_dim(ks, t)..+3 */
     uint32_t qf[NHT][KS][2];
@@ -221,111 +272,12 @@ q4_decode_k(const DecParams P) {
             acc[nt][mt][0] = acc[nt][mt][1] = acc[nt][mt][2] = acc[nt][mt][3] = 0.f;
     }
 
-    for (uint32_t step = s_begin + warp; step < s_end; step += DEC_WARPS) {
-        /* ---- positions of this step: K rows are slots g, g+8; V rows are slots 2t,2t+1,2t+8,2t+9 */
-        const uint32_t j0 = step << 4;
-        int32_t pk[2], pv[4];
-        if (list) {
-            int32_t mine = -1;
-            const uint32_t j = j0 + (lane & 15);
-            if (j < n_pos) {
-                mine = list[j];
-                if (mine >= (int32_t)C.max_kv) {
-                    atomicOr(P.err, (uint32_t)Q4E_RANGE);
-                    mine = -1;
-                }
-            }
-            pk[0] = __shfl_sync(0xffffffffu, mine, g);
-            pk[1] = __shfl_sync(0xffffffffu, mine, g + 8);
-            pv[0] = __shfl_sync(0xffffffffu, mine, 2 * t);
-            pv[1] = __shfl_sync(0xffffffffu, mine, 2 * t + 1);
-            pv[2] = __shfl_sync(0xffffffffu, mine, 2 * t + 8);
-            pv[3] = __shfl_sync(0xffffffffu, mine, 2 * t + 9);
-        } else {
-            auto dense = [&](uint32_t s) -> int32_t { return j0 + s < n_pos ? (int32_t)(j0 + s) : -1; };
-            pk[0] = dense(g); pk[1] = dense(g + 8);
-            pv[0] = dense(2 * t); pv[1] = dense(2 * t + 1);
-            pv[2] = dense(2 * t + 8); pv[3] = dense(2 * t + 9);
-        }
-        const uint8_t *krow[2], *vrow[4];
-#pragma unroll
-        for (int r = 0; r < 2; r++) krow[r] = kbase + (uint64_t)(pk[r] < 0 ? 0 : pk[r]) * tok_stride;
-#pragma unroll
-        for (int r = 0; r < 4; r++) vrow[r] = vbase + (uint64_t)(pv[r] < 0 ? 0 : pv[r]) * tok_stride;
-
-        /* ---- issue the q8_0 loads of the whole step up front (memory-level parallelism) */
-        uint2 kw[Q8 ? 2 : 1][Q8 ? NB : 1];
-        uint32_t vw[Q8 ? 4 : 1][Q8 ? NB : 1];
-        float ksc[Q8 ? 2 : 1][Q8 ? NB : 1];       /* K block scales x softmax scale x log2(e) */
-        __half vsc[Q8 ? 4 : 1][Q8 ? NB : 1];
-        if constexpr (LAY == LAY_Q8P) {
-#pragma unroll
-            for (int r = 0; r < 2; r++)
-#pragma unroll
-                for (int b = 0; b < NB; b++)
-                    kw[r][b] = pk[r] >= 0 ? ldg64(krow[r] + 32 * b + 8 * t) : make_uint2(0u, 0u);
-#pragma unroll
-            for (int r = 0; r < 4; r++)
-#pragma unroll
-                for (int b = 0; b < NB; b++)
-                    vw[r][b] = pv[r] >= 0 ? ldg32(vrow[r] + 32 * b + 4 * g) : 0u;
-            /* scale row: NB fp16 for K then NB fp16 for V */
-#pragma unroll
-            for (int r = 0; r < 2; r++) {
-                const uint8_t *sp = sbase + (uint64_t)(pk[r] < 0 ? 0 : pk[r]) * s_tok_stride;
-                __half h[NB];
-                if constexpr (NB == 4) { uint2 w = ldg64(sp); *reinterpret_cast<uint2 *>(h) = w; }
-                else if constexpr (NB == 8) { uint4 w = ldg128(sp); *reinterpret_cast<uint4 *>(h) = w; }
-                else if constexpr (NB == 2) { uint32_t w = ldg32(sp); *reinterpret_cast<uint32_t *>(h) = w; }
-                else { uint16_t w = (uint16_t)ldg16(sp); *reinterpret_cast<uint16_t *>(h) = w; }
-#pragma unroll
-                for (int b = 0; b < NB; b++)
-                    ksc[r][b] = pk[r] >= 0 ? __half2float(h[b]) * P.scale_log2e : 0.f;
-            }
-#pragma unroll
-            for (int r = 0; r < 4; r++) {
-                const uint8_t *sp = sbase + (uint64_t)(pv[r] < 0 ? 0 : pv[r]) * s_tok_stride + 2 * NB;
-                __half h[NB];
-                if constexpr (NB == 4) { uint2 w = ldg64(sp); *reinterpret_cast<uint2 *>(h) = w; }
-                else if constexpr (NB == 8) { uint4 w = ldg128(sp); *reinterpret_cast<uint4 *>(h) = w; }
-                else if constexpr (NB == 2) { uint32_t w = ldg32(sp); *reinterpret_cast<uint32_t *>(h) = w; }
-                else { uint16_t w = (uint16_t)ldg16(sp); *reinterpret_cast<uint16_t *>(h) = w; }
-#pragma unroll
-                for (int b = 0; b < NB; b++) vsc[r][b] = pv[r] >= 0 ? h[b] : __ushort_as_half(0);
-            }
-        } else if constexpr (LAY == LAY_Q8R) {
-            /* reference layout: 34-byte blocks {fp16 scale, 32 x int8}, only 2-byte aligned */
-#pragma unroll
-            for (int r = 0; r < 2; r++)
-#pragma unroll
-                for (int b = 0; b < NB; b++) {
-                    const uint8_t *bp = krow[r] + 34 * b;
-                    if (pk[r] >= 0) {
-                        const uint8_t *cp = bp + 2 + 8 * t;
-                        kw[r][b].x = ldg16(cp) | (ldg16(cp + 2) << 16);
-                        kw[r][b].y = ldg16(cp + 4) | (ldg16(cp + 6) << 16);
-                        ksc[r][b] = __half2float(__ushort_as_half((uint16_t)ldg16(bp))) * P.scale_log2e;
-                    } else {
-                        kw[r][b] = make_uint2(0u, 0u);
-                        ksc[r][b] = 0.f;
-                    }
-                }
-#pragma unroll
-            for (int r = 0; r < 4; r++)
-#pragma unroll
-                for (int b = 0; b < NB; b++) {
-                    const uint8_t *bp = vrow[r] + 34 * b;
-                    if (pv[r] >= 0) {
-                        const uint8_t *cp = bp + 2 + 4 * g;
-                        vw[r][b] = ldg16(cp) | (ldg16(cp + 2) << 16);
-                        vsc[r][b] = __ushort_as_half((uint16_t)ldg16(bp));
-                    } else {
-                        vw[r][b] = 0u;
-                        vsc[r][b] = __ushort_as_half(0);
-                    }
-                }
-        }
-
+    /* One warp-step: 16 positions.  K rows are slots g, g+8 (pk); V rows are slots 2t, 2t+1, 2t+8,
+     * 2t+9 (pv).  q8 layouts pass their codes and scales in registers; fp16 / fp32 rows are loaded
+     * here from krow / vrow. */
+    auto compute = [&](const int32_t (&pk)[2], const int32_t (&pv)[4], const uint2 (&kw)[2][NBQ],
+                       const uint32_t (&vw)[4][NBQ], const float (&ksc)[2][NBQ], const __half (&vsc)[4][NBQ],
+                       const uint8_t *const (&krow)[2], const uint8_t *const (&vrow)[4]) {
         /* ---- S^T = K . Q^T (log2 domain: scale * log2(e) folded in) */
         float sc[NHT][4];
 #pragma unroll
@@ -466,24 +418,214 @@ q4_decode_k(const DecParams P) {
                 for (int nt = 0; nt < NHT; nt++) mma16816(acc[nt][mt], a0, a1, a2, a3, pb0[nt], pb1[nt]);
             }
         }
+    };
+
+    if constexpr (Cfg::STAGED) {
+        /* ---- planar q8_0, hd 128: per-warp cp.async ring.  Lanes 0-15 hold the step's positions and
+         * copy the 16-byte scale rows; the K and V rows are copied 4 rows per instruction.  16-byte
+         * chunk c of row r lands at chunk c ^ ((r & 3) << 1) in the K tile and c ^ (((r >> 1) & 3) << 1)
+         * in the V tile, which makes the 8-byte K reads (rows g) and the 4-byte V reads (rows 2t..)
+         * below hit 32 distinct banks. */
+        const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem_raw) +
+                              (uint32_t)warp * RING_STAGES * RING_STAGE_BYTES;
+        const uint32_t n_my = s_begin + warp < s_end ? (s_end - s_begin - warp + DEC_WARPS - 1u) / DEC_WARPS : 0u;
+        const uint32_t r16 = lane & 15, half = lane >> 4;
+        auto my_pos = [&](uint32_t it) -> int32_t {
+            return it < n_my ? position(((s_begin + warp + it * DEC_WARPS) << 4) + r16) : -1;
+        };
+        auto issue = [&](uint32_t it, int32_t p) {
+            if (it < n_my) {
+                const uint32_t st = ring + (it % RING_STAGES) * RING_STAGE_BYTES;
+                /* copy j moves rows 4j .. 4j+3: 8 lanes x 16 bytes per row, so one instruction touches
+                 * four whole 128-byte lines instead of 32 scattered sectors */
+                const uint32_t c = lane & 7;
+#pragma unroll
+                for (uint32_t j = 0; j < 4; j++) {
+                    const uint32_t row = 4 * j + (lane >> 3);
+                    const int32_t pr = __shfl_sync(0xffffffffu, p, row);
+                    const uint32_t bytes = pr >= 0 ? 16u : 0u;
+                    const uint64_t off = (uint64_t)(pr < 0 ? 0 : pr) * tok_stride + c * 16;
+                    cp_async16(st + row * 128 + ((c ^ ((row & 3) << 1)) << 4), kbase + off, bytes);
+                    cp_async16(st + 2048 + row * 128 + ((c ^ (((row >> 1) & 3) << 1)) << 4), vbase + off, bytes);
+                }
+                if (half == 0) {
+                    cp_async16(st + 4096 + r16 * 16, sbase + (uint64_t)(p < 0 ? 0 : p) * s_tok_stride, p >= 0 ? 16u : 0u);
+                    asm volatile("st.shared.s32 [%0], %1;" ::"r"(st + 4352 + r16 * 4), "r"(p) : "memory");
+                }
+            }
+            cp_async_commit();   /* one group per step, empty or not, keeps the wait count uniform */
+        };
+        int32_t p_next[RING_STAGES];
+#pragma unroll
+        for (int i = 0; i < RING_STAGES; i++) p_next[i] = my_pos(i);
+#pragma unroll
+        for (int i = 0; i < RING_STAGES - 1; i++) issue(i, p_next[i]);
+        int32_t p_ahead = p_next[RING_STAGES - 1];
+        for (uint32_t it = 0; it < n_my; it++) {
+            const int32_t p_issue = p_ahead;
+            p_ahead = my_pos(it + RING_STAGES);          /* consumed by the next iteration's issue */
+            issue(it + RING_STAGES - 1, p_issue);
+            cp_async_wait<RING_STAGES - 1>();
+            __syncwarp();
+            const uint32_t st = ring + (it % RING_STAGES) * RING_STAGE_BYTES;
+            int32_t pk[2], pv[4];
+            pk[0] = (int32_t)lds32(st + 4352 + 4 * g);
+            pk[1] = (int32_t)lds32(st + 4352 + 4 * (g + 8));
+            {
+                const uint2 w0 = lds64(st + 4352 + 8 * t), w1 = lds64(st + 4352 + 32 + 8 * t);
+                pv[0] = (int32_t)w0.x; pv[1] = (int32_t)w0.y; pv[2] = (int32_t)w1.x; pv[3] = (int32_t)w1.y;
+            }
+            uint2 kw[2][NBQ];
+            uint32_t vw[4][NBQ];
+            float ksc[2][NBQ];
+            __half vsc[4][NBQ];
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                const uint32_t row = g + 8 * r;
+#pragma unroll
+                for (int b = 0; b < NB; b++)
+                    kw[r][b] = lds64(st + row * 128 + (((2 * b + (t >> 1)) ^ ((g & 3) << 1)) << 4) + 8 * (t & 1));
+                const uint2 w = lds64(st + 4096 + row * 16);
+                const __half2 h01 = u2h(w.x), h23 = u2h(w.y);
+                ksc[r][0] = pk[r] >= 0 ? __low2float(h01) * P.scale_log2e : 0.f;
+                ksc[r][1] = pk[r] >= 0 ? __high2float(h01) * P.scale_log2e : 0.f;
+                ksc[r][2] = pk[r] >= 0 ? __low2float(h23) * P.scale_log2e : 0.f;
+                ksc[r][3] = pk[r] >= 0 ? __high2float(h23) * P.scale_log2e : 0.f;
+            }
+#pragma unroll
+            for (int r = 0; r < 4; r++) {
+                const uint32_t row = 2 * t + (r & 1) + 8 * (r >> 1);
+#pragma unroll
+                for (int b = 0; b < NB; b++)
+                    vw[r][b] = lds32(st + 2048 + row * 128 + (((2 * b + (g >> 2)) ^ (t << 1)) << 4) + 4 * (g & 3));
+                const uint2 w = lds64(st + 4096 + row * 16 + 8);
+                const __half2 h01 = u2h(w.x), h23 = u2h(w.y);
+                const __half z = __ushort_as_half(0);
+                vsc[r][0] = pv[r] >= 0 ? __low2half(h01) : z;
+                vsc[r][1] = pv[r] >= 0 ? __high2half(h01) : z;
+                vsc[r][2] = pv[r] >= 0 ? __low2half(h23) : z;
+                vsc[r][3] = pv[r] >= 0 ? __high2half(h23) : z;
+            }
+            const uint8_t *const krow[2] = {nullptr, nullptr};
+            const uint8_t *const vrow[4] = {nullptr, nullptr, nullptr, nullptr};
+            compute(pk, pv, kw, vw, ksc, vsc, krow, vrow);
+            __syncwarp();   /* every lane is done with this stage before a later issue overwrites it */
+        }
+        cp_async_wait<0>();
+        __syncthreads();    /* the epilogue below reuses the ring memory of all warps */
+    } else {
+        for (uint32_t step = s_begin + warp; step < s_end; step += DEC_WARPS) {
+            const uint32_t j0 = step << 4;
+            int32_t pk[2], pv[4];
+            if (list) {
+                const int32_t mine = position(j0 + (lane & 15));
+                pk[0] = __shfl_sync(0xffffffffu, mine, g);
+                pk[1] = __shfl_sync(0xffffffffu, mine, g + 8);
+                pv[0] = __shfl_sync(0xffffffffu, mine, 2 * t);
+                pv[1] = __shfl_sync(0xffffffffu, mine, 2 * t + 1);
+                pv[2] = __shfl_sync(0xffffffffu, mine, 2 * t + 8);
+                pv[3] = __shfl_sync(0xffffffffu, mine, 2 * t + 9);
+            } else {
+                pk[0] = position(j0 + g); pk[1] = position(j0 + g + 8);
+                pv[0] = position(j0 + 2 * t); pv[1] = position(j0 + 2 * t + 1);
+                pv[2] = position(j0 + 2 * t + 8); pv[3] = position(j0 + 2 * t + 9);
+            }
+            const uint8_t *krow[2], *vrow[4];
+#pragma unroll
+            for (int r = 0; r < 2; r++) krow[r] = kbase + (uint64_t)(pk[r] < 0 ? 0 : pk[r]) * tok_stride;
+#pragma unroll
+            for (int r = 0; r < 4; r++) vrow[r] = vbase + (uint64_t)(pv[r] < 0 ? 0 : pv[r]) * tok_stride;
+            uint2 kw[2][NBQ];
+            uint32_t vw[4][NBQ];
+            float ksc[2][NBQ];
+            __half vsc[4][NBQ];
+            if constexpr (LAY == LAY_Q8P) {
+#pragma unroll
+                for (int r = 0; r < 2; r++)
+#pragma unroll
+                    for (int b = 0; b < NB; b++)
+                        kw[r][b] = pk[r] >= 0 ? ldg64(krow[r] + 32 * b + 8 * t) : make_uint2(0u, 0u);
+#pragma unroll
+                for (int r = 0; r < 4; r++)
+#pragma unroll
+                    for (int b = 0; b < NB; b++)
+                        vw[r][b] = pv[r] >= 0 ? ldg32(vrow[r] + 32 * b + 4 * g) : 0u;
+                /* scale row: NB fp16 for K then NB fp16 for V */
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                    const uint8_t *sp = sbase + (uint64_t)(pk[r] < 0 ? 0 : pk[r]) * s_tok_stride;
+                    __align__(16) __half h[NB];
+                    if constexpr (NB == 4) { uint2 w = ldg64(sp); *reinterpret_cast<uint2 *>(h) = w; }
+                    else if constexpr (NB == 8) { uint4 w = ldg128(sp); *reinterpret_cast<uint4 *>(h) = w; }
+                    else if constexpr (NB == 2) { uint32_t w = ldg32(sp); *reinterpret_cast<uint32_t *>(h) = w; }
+                    else { uint16_t w = (uint16_t)ldg16(sp); *reinterpret_cast<uint16_t *>(h) = w; }
+#pragma unroll
+                    for (int b = 0; b < NB; b++)
+                        ksc[r][b] = pk[r] >= 0 ? __half2float(h[b]) * P.scale_log2e : 0.f;
+                }
+#pragma unroll
+                for (int r = 0; r < 4; r++) {
+                    const uint8_t *sp = sbase + (uint64_t)(pv[r] < 0 ? 0 : pv[r]) * s_tok_stride + 2 * NB;
+                    __align__(16) __half h[NB];
+                    if constexpr (NB == 4) { uint2 w = ldg64(sp); *reinterpret_cast<uint2 *>(h) = w; }
+                    else if constexpr (NB == 8) { uint4 w = ldg128(sp); *reinterpret_cast<uint4 *>(h) = w; }
+                    else if constexpr (NB == 2) { uint32_t w = ldg32(sp); *reinterpret_cast<uint32_t *>(h) = w; }
+                    else { uint16_t w = (uint16_t)ldg16(sp); *reinterpret_cast<uint16_t *>(h) = w; }
+#pragma unroll
+                    for (int b = 0; b < NB; b++) vsc[r][b] = pv[r] >= 0 ? h[b] : __ushort_as_half(0);
+                }
+            } else if constexpr (LAY == LAY_Q8R) {
+                /* reference layout: 34-byte blocks {fp16 scale, 32 x int8}, only 2-byte aligned */
+#pragma unroll
+                for (int r = 0; r < 2; r++)
+#pragma unroll
+                    for (int b = 0; b < NB; b++) {
+                        const uint8_t *bp = krow[r] + 34 * b;
+                        if (pk[r] >= 0) {
+                            const uint8_t *cp = bp + 2 + 8 * t;
+                            kw[r][b].x = ldg16(cp) | (ldg16(cp + 2) << 16);
+                            kw[r][b].y = ldg16(cp + 4) | (ldg16(cp + 6) << 16);
+                            ksc[r][b] = __half2float(__ushort_as_half((uint16_t)ldg16(bp))) * P.scale_log2e;
+                        } else {
+                            kw[r][b] = make_uint2(0u, 0u);
+                            ksc[r][b] = 0.f;
+                        }
+                    }
+#pragma unroll
+                for (int r = 0; r < 4; r++)
+#pragma unroll
+                    for (int b = 0; b < NB; b++) {
+                        const uint8_t *bp = vrow[r] + 34 * b;
+                        if (pv[r] >= 0) {
+                            const uint8_t *cp = bp + 2 + 4 * g;
+                            vw[r][b] = ldg16(cp) | (ldg16(cp + 2) << 16);
+                            vsc[r][b] = __ushort_as_half((uint16_t)ldg16(bp));
+                        } else {
+                            vw[r][b] = 0u;
+                            vsc[r][b] = __ushort_as_half(0);
+                        }
+                    }
+            }
+            compute(pk, pv, kw, vw, ksc, vsc, krow, vrow);
+        }
     }
 
     /* ---- block reduction of the warps' partials ------------------------------------------- */
-    extern __shared__ float sm[];   /* [DEC_WARPS][HEADS][REC] : m, l, acc[HD] */
+    float *sm = reinterpret_cast<float *>(smem_raw);   /* [DEC_WARPS][HEADS][REC] : acc[HD], m, l */
 #pragma unroll
     for (int nt = 0; nt < NHT; nt++) {
         const float l0 = warp_sum_over_g(l_run[nt][0]), l1 = warp_sum_over_g(l_run[nt][1]);
         float *r0 = sm + ((size_t)warp * HEADS + nt * 8 + 2 * t) * REC;
         float *r1 = r0 + REC;
         if (g == 0) {
-            r0[0] = m_run[nt][0]; r0[1] = l0;
-            r1[0] = m_run[nt][1]; r1[1] = l1;
+            r0[HD] = m_run[nt][0]; r0[HD + 1] = l0;
+            r1[HD] = m_run[nt][1]; r1[HD + 1] = l1;
         }
 #pragma unroll
         for (int mt = 0; mt < MT; mt++) {
             const int d0 = out_dim<LAY>(mt, g, 0), d1 = out_dim<LAY>(mt, g, 1);
-            r0[2 + d0] = acc[nt][mt][0]; r1[2 + d0] = acc[nt][mt][1];
-            r0[2 + d1] = acc[nt][mt][2]; r1[2 + d1] = acc[nt][mt][3];
+            r0[d0] = acc[nt][mt][0]; r1[d0] = acc[nt][mt][1];
+            r0[d1] = acc[nt][mt][2]; r1[d1] = acc[nt][mt][3];
         }
     }
     __syncthreads();
@@ -491,52 +633,73 @@ q4_decode_k(const DecParams P) {
     const uint32_t gqa = P.gqa;
     const size_t unit = (size_t)u * P.n_kvh + kh;
     __shared__ uint32_t s_last;
+    __shared__ float s_w[DEC_GROUP * 16], s_M[16], s_L[16];
 
-    auto finish = [&](uint32_t h, uint32_t d, float M, float L, float A) {
-        const uint32_t head = kh * gqa + h;
-        if (P.part_out) {
-            float *pr = P.part_out + ((size_t)u * P.n_head + head) * REC;
-            if (d == 0) {
-                pr[0] = L > 0.f ? M * 0.6931471805599453f : 0.f;   /* back to natural-log units */
-                pr[1] = L;
-            }
-            pr[2 + d] = A;
-        } else {
-            float o = L > 0.f ? A / L : 0.f;
-            if (P.gate) o *= 1.f / (1.f + __expf(-P.gate[((size_t)u * P.n_head + head) * HD + d]));
-            P.out[((size_t)u * P.n_head + head) * HD + d] = o;
+    /* Merge `count` (<= DEC_GROUP) records spaced HEADS*REC floats apart.  Weights are computed once
+     * per (record, head) by separate threads; then every thread owns 4 output dims of some heads and
+     * streams the accumulators with independent 16-byte loads.  dst_rec != null stores a merged record
+     * for the next level, otherwise the result is finalised. */
+    auto merge = [&](const float *recs, uint32_t count, bool global, float *dst_rec) {
+        for (uint32_t i = threadIdx.x; i < count * HEADS; i += DEC_THREADS) {
+            const float *r = recs + (size_t)i * REC + HD;
+            s_w[i] = global ? __ldcg(r) : r[0];
         }
-    };
-    /* store a merged record (log2-domain max) for a later merge level */
-    auto store_rec = [&](float *rec, uint32_t h, uint32_t d, float M, float L, float A) {
-        if (d == 0) { rec[(size_t)h * REC] = M; rec[(size_t)h * REC + 1] = L; }
-        rec[(size_t)h * REC + 2 + d] = A;
-    };
-    /* merge `count` records spaced HEADS*REC floats apart; thread d owns output dim d */
-    auto merge = [&](const float *recs, uint32_t count, bool from_smem, float *dst_rec) {
-        for (uint32_t h = 0; h < gqa; h++) {
+        __syncthreads();
+        if (threadIdx.x < gqa) {
+            const uint32_t h = threadIdx.x;
             float M = -CUDART_INF_F;
-            for (uint32_t s = 0; s < count; s++) {
-                const float *r = recs + ((size_t)s * HEADS + h) * REC;
-                M = fmaxf(M, from_smem ? r[0] : __ldcg(r));
-            }
+            for (uint32_t s = 0; s < count; s++) M = fmaxf(M, s_w[s * HEADS + h]);
             const float Mu = M == -CUDART_INF_F ? 0.f : M;
             float L = 0.f;
             for (uint32_t s = 0; s < count; s++) {
-                const float *r = recs + ((size_t)s * HEADS + h) * REC;
-                L = from_smem ? fmaf(ex2(r[0] - Mu), r[1], L) : fmaf(ex2(__ldcg(r) - Mu), __ldcg(r + 1), L);
+                const float *r = recs + ((size_t)s * HEADS + h) * REC + HD + 1;
+                const float w = ex2(s_w[s * HEADS + h] - Mu);
+                s_w[s * HEADS + h] = w;
+                L = fmaf(w, global ? __ldcg(r) : r[0], L);
             }
-            for (uint32_t d = threadIdx.x; d < (uint32_t)HD; d += DEC_THREADS) {
-                float A = 0.f;
-                for (uint32_t s = 0; s < count; s++) {
-                    const float *r = recs + ((size_t)s * HEADS + h) * REC;
-                    A = from_smem ? fmaf(ex2(r[0] - Mu), r[2 + d], A)
-                                  : fmaf(ex2(__ldcg(r) - Mu), __ldcg(r + 2 + d), A);
+            s_M[h] = M;
+            s_L[h] = L;
+        }
+        __syncthreads();
+        for (uint32_t i = threadIdx.x; i < gqa * (HD / 4); i += DEC_THREADS) {
+            const uint32_t h = i / (HD / 4), d = (i % (HD / 4)) * 4;
+            float4 A = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+            for (uint32_t s = 0; s < count; s++) {
+                const float4 *r = reinterpret_cast<const float4 *>(recs + ((size_t)s * HEADS + h) * REC + d);
+                const float4 x = global ? __ldcg(r) : *r;
+                const float w = s_w[s * HEADS + h];
+                A.x = fmaf(w, x.x, A.x); A.y = fmaf(w, x.y, A.y);
+                A.z = fmaf(w, x.z, A.z); A.w = fmaf(w, x.w, A.w);
+            }
+            const float M = s_M[h], L = s_L[h];
+            if (dst_rec) {
+                float *o = dst_rec + (size_t)h * REC;
+                *reinterpret_cast<float4 *>(o + d) = A;
+                if (d == 0) { o[HD] = M; o[HD + 1] = L; }
+            } else {
+                const uint32_t head = kh * gqa + h;
+                if (P.part_out) {   /* public record: {m (natural log units), l, acc[HD]} */
+                    float *pr = P.part_out + ((size_t)u * P.n_head + head) * (HD + 2);
+                    if (d == 0) {
+                        pr[0] = L > 0.f ? M * 0.6931471805599453f : 0.f;
+                        pr[1] = L;
+                    }
+                    pr[2 + d] = A.x; pr[3 + d] = A.y; pr[4 + d] = A.z; pr[5 + d] = A.w;
+                } else {
+                    const float inv = L > 0.f ? 1.f / L : 0.f;
+                    float4 o = make_float4(A.x * inv, A.y * inv, A.z * inv, A.w * inv);
+                    const size_t off = ((size_t)u * P.n_head + head) * HD + d;
+                    if (P.gate) {
+                        const float4 gt = *reinterpret_cast<const float4 *>(P.gate + off);
+                        o.x *= 1.f / (1.f + __expf(-gt.x)); o.y *= 1.f / (1.f + __expf(-gt.y));
+                        o.z *= 1.f / (1.f + __expf(-gt.z)); o.w *= 1.f / (1.f + __expf(-gt.w));
+                    }
+                    *reinterpret_cast<float4 *>(P.out + off) = o;
                 }
-                if (dst_rec) store_rec(dst_rec, h, d, M, L, A);
-                else finish(h, d, M, L, A);
             }
         }
+        __syncthreads();   /* s_w is reused by the next level */
     };
     /* arrive on a counter; true for the last of `expected` arrivals (which also re-arms it) */
     auto arrive_last = [&](uint32_t *ctr, uint32_t expected) -> bool {
@@ -554,7 +717,7 @@ q4_decode_k(const DecParams P) {
     };
 
     if (S == 1) {
-        merge(sm, DEC_WARPS, true, nullptr);
+        merge(sm, DEC_WARPS, false, nullptr);
         return;
     }
     /* level 1: record per block; groups of DEC_GROUP blocks are merged by their last arrival,
@@ -565,15 +728,15 @@ q4_decode_k(const DecParams P) {
     float *rec1 = P.scratch + (unit * (size_t)(S + n_groups)) * HEADS * REC;
     float *rec2 = rec1 + (size_t)S * HEADS * REC;
     uint32_t *ctr = P.counters + unit * (1u + DEC_MAX_SPLIT / DEC_GROUP);
-    merge(sm, DEC_WARPS, true, rec1 + (size_t)split * HEADS * REC);
+    merge(sm, DEC_WARPS, false, rec1 + (size_t)split * HEADS * REC);
     if (!arrive_last(ctr + 1 + grp, grp_size)) return;
     if (n_groups == 1) {
-        merge(rec1, S, false, nullptr);
+        merge(rec1, S, true, nullptr);
         return;
     }
-    merge(rec1 + (size_t)grp * DEC_GROUP * HEADS * REC, grp_size, false, rec2 + (size_t)grp * HEADS * REC);
+    merge(rec1 + (size_t)grp * DEC_GROUP * HEADS * REC, grp_size, true, rec2 + (size_t)grp * HEADS * REC);
     if (!arrive_last(ctr, n_groups)) return;
-    merge(rec2, n_groups, false, nullptr);
+    merge(rec2, n_groups, true, nullptr);
 }
 
 /* Merge of externally produced records (sequence-sharded decode): parts [n_parts][n_head][hd+2]
@@ -605,7 +768,7 @@ __global__ void q4_lse_merge_k(const float *parts, uint32_t n_parts, uint32_t n_
 
 template <int LAY, int HD, int NHT>
 bool launch(const DecParams &p, dim3 grid) {
-    constexpr size_t smem = (size_t)DEC_WARPS * 8 * NHT * (HD + 2) * sizeof(float);
+    constexpr size_t smem = DecCfg<LAY, HD, NHT>::SMEM;
     static bool attr_done = false;
     if (!attr_done && smem > 48 * 1024) {
         if (!q4i_check(cudaFuncSetAttribute(q4_decode_k<LAY, HD, NHT>,
@@ -659,8 +822,9 @@ bool q4i_decode(const Q4DecodeArgs &a) {
     const uint32_t units = a.n_units * a.n_kvh;
     uint32_t S = split_override();
     if (!S) {
-        const uint32_t target = (uint32_t)g_q4.sm_count * 6u;
-        S = (target + units - 1u) / units;
+        /* one wave: 4 resident blocks per SM for the staged q8_0 kernel, 3 otherwise */
+        const uint32_t target = (uint32_t)g_q4.sm_count * ((a.layout == LAY_Q8P && a.hd == 128) ? 4u : 3u);
+        S = target / units;
         const uint32_t cap = (steps + DEC_WARPS - 1u) / DEC_WARPS;
         if (S > cap) S = cap;
     }
@@ -668,7 +832,7 @@ bool q4i_decode(const Q4DecodeArgs &a) {
     if (S < 1) S = 1;
 
     const uint32_t n_groups = (S + DEC_GROUP - 1u) / DEC_GROUP;
-    const size_t need_part = (size_t)units * (S + n_groups) * heads * (a.hd + 2);
+    const size_t need_part = (size_t)units * (S + n_groups) * heads * (a.hd + 4);
     const size_t need_ctr = (size_t)units * (1u + DEC_MAX_SPLIT / DEC_GROUP);
     float *scratch = a.scratch_part;
     uint32_t *counters = a.scratch_counters;

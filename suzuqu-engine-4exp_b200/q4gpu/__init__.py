@@ -56,6 +56,7 @@ SIGNATURES = {
     "q4_gpu_kv_decode": (_b, [_v, _u32, _v, _i, _v, _v, _u32, _v, _u32, _u32, _u32, _f]),
     "q4_gpu_kv_decode_partial": (_b, [_v, _u32, _v, _i, _v, _u32, _v, _u32, _u32, _u32, _f]),
     "q4_gpu_lse_merge": (_b, [_v, _u32, _u32, _u32, _v, _v]),
+    "q4_gpu_kv_prefill": (_b, [_v, _u32, _v, _v, _v, _u32, _u32, _u32, _f]),
     "q4_gpu_batch_create": (_v, [_u32]), "q4_gpu_batch_destroy": (None, [_v]),
     "q4_gpu_batch_bind": (_b, [_v, _u32, _v]), "q4_gpu_batch_set_pos": (_b, [_v, _v, _u32]),
     "q4_gpu_batch_append": (_b, [_v, _u32, _v, _v]),
@@ -169,6 +170,11 @@ class KVStore:
                n_kv=0, q_bf16=False):
         check(self.L.q4_gpu_kv_decode(self.h, layer, _ptr(q), int(q_bf16), _ptr(gate), _ptr(out), n_head,
                                       _ptr(idx), width, idx_kvh_stride, n_kv, scale), "q4_gpu_kv_decode")
+
+    def prefill(self, layer, q_bf16, out_bf16, n_head, n_tok, kv_base, scale, gate=None):
+        """causal attention of n_tok queries (bf16) over rows [0, kv_base + t + 1); bf16 output"""
+        check(self.L.q4_gpu_kv_prefill(self.h, layer, _ptr(q_bf16), _ptr(gate), _ptr(out_bf16), n_head, n_tok,
+                                       kv_base, scale), "q4_gpu_kv_prefill")
 
     def decode_partial(self, layer, q, part, n_head, scale, idx=None, width=0, idx_kvh_stride=0, n_kv=0,
                        q_bf16=False):
