@@ -170,7 +170,7 @@ __device__ __forceinline__ int qk_dim(int ks, int t) {
 }
 
 /* ---- the kernel ---------------------------------------------------------------------------- */
-constexpr int RING_STAGES = 3;
+constexpr int RING_STAGES = 4;
 constexpr int RING_STAGE_BYTES = 2048 + 2048 + 256 + 64;   /* K rows, V rows, scale rows, positions */
 
 template <int LAY, int HD, int NHT>
@@ -181,7 +181,7 @@ struct DecCfg {
     static constexpr size_t EPI_BYTES = (size_t)DEC_WARPS * HEADS * REC * sizeof(float);
     static constexpr size_t RING_BYTES = STAGED ? (size_t)DEC_WARPS * RING_STAGES * RING_STAGE_BYTES : 0;
     static constexpr size_t SMEM = EPI_BYTES > RING_BYTES ? EPI_BYTES : RING_BYTES;
-    static constexpr int MIN_BLOCKS = STAGED ? (NHT == 1 ? 4 : 2) : (HD * NHT <= 128 ? 3 : 1);
+    static constexpr int MIN_BLOCKS = STAGED ? (NHT == 1 ? 3 : 2) : (HD * NHT <= 128 ? 3 : 1);
 };
 
 template <int LAY, int HD, int NHT>
@@ -421,95 +421,232 @@ q4_decode_k(const DecParams P) {
     };
 
     if constexpr (Cfg::STAGED) {
-        /* ---- planar q8_0, hd 128: per-warp cp.async ring.  Lanes 0-15 hold the step's positions and
-         * copy the 16-byte scale rows; the K and V rows are copied 4 rows per instruction.  16-byte
-         * chunk c of row r lands at chunk c ^ ((r & 3) << 1) in the K tile and c ^ (((r >> 1) & 3) << 1)
-         * in the V tile, which makes the 8-byte K reads (rows g) and the 4-byte V reads (rows 2t..)
-         * below hit 32 distinct banks. */
+        /* ---- planar q8_0, hd 128: per-warp cp.async ring of 16-position stages; an iteration consumes
+         * two stages (32 positions, two independent MMA chains) while the next two are in flight.
+         * Lanes 0-15 hold a stage's positions and copy its 16-byte scale rows; the K and V rows are
+         * copied 4 rows per instruction (8 lanes x 16 bytes = one 128-byte line per row).  16-byte chunk
+         * c of row r lands at chunk c ^ ((r & 3) << 1) in the K tile and c ^ (((r >> 1) & 3) << 1) in the
+         * V tile, which makes the 8-byte K reads (rows g) and the 4-byte V reads (rows 2t..) below hit
+         * 32 distinct banks.  Padding positions are zero-filled (cp.async with 0 source bytes): their
+         * scales are 0, so they add nothing to P.V, and their scores are masked to -inf. */
         const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem_raw) +
                               (uint32_t)warp * RING_STAGES * RING_STAGE_BYTES;
         const uint32_t n_my = s_begin + warp < s_end ? (s_end - s_begin - warp + DEC_WARPS - 1u) / DEC_WARPS : 0u;
-        const uint32_t r16 = lane & 15, half = lane >> 4;
+        const uint32_t n_even = (n_my + 1u) & ~1u;
+        const uint32_t r16 = lane & 15, c8 = lane & 7;
+        uint32_t koff[4], voff[4];
+#pragma unroll
+        for (uint32_t j = 0; j < 4; j++) {
+            const uint32_t row = 4 * j + (lane >> 3);
+            koff[j] = row * 128 + ((c8 ^ ((row & 3) << 1)) << 4);
+            voff[j] = 2048 + row * 128 + ((c8 ^ (((row >> 1) & 3) << 1)) << 4);
+        }
         auto my_pos = [&](uint32_t it) -> int32_t {
             return it < n_my ? position(((s_begin + warp + it * DEC_WARPS) << 4) + r16) : -1;
         };
         auto issue = [&](uint32_t it, int32_t p) {
-            if (it < n_my) {
+            if (it < n_even) {
                 const uint32_t st = ring + (it % RING_STAGES) * RING_STAGE_BYTES;
-                /* copy j moves rows 4j .. 4j+3: 8 lanes x 16 bytes per row, so one instruction touches
-                 * four whole 128-byte lines instead of 32 scattered sectors */
-                const uint32_t c = lane & 7;
 #pragma unroll
                 for (uint32_t j = 0; j < 4; j++) {
-                    const uint32_t row = 4 * j + (lane >> 3);
-                    const int32_t pr = __shfl_sync(0xffffffffu, p, row);
+                    const int32_t pr = __shfl_sync(0xffffffffu, p, 4 * j + (lane >> 3));
                     const uint32_t bytes = pr >= 0 ? 16u : 0u;
-                    const uint64_t off = (uint64_t)(pr < 0 ? 0 : pr) * tok_stride + c * 16;
-                    cp_async16(st + row * 128 + ((c ^ ((row & 3) << 1)) << 4), kbase + off, bytes);
-                    cp_async16(st + 2048 + row * 128 + ((c ^ (((row >> 1) & 3) << 1)) << 4), vbase + off, bytes);
+                    const uint64_t off = (uint64_t)(uint32_t)max(pr, 0) * tok_stride + c8 * 16;
+                    cp_async16(st + koff[j], kbase + off, bytes);
+                    cp_async16(st + voff[j], vbase + off, bytes);
                 }
-                if (half == 0) {
-                    cp_async16(st + 4096 + r16 * 16, sbase + (uint64_t)(p < 0 ? 0 : p) * s_tok_stride, p >= 0 ? 16u : 0u);
+                if (lane < 16) {
+                    cp_async16(st + 4096 + r16 * 16, sbase + (uint64_t)(uint32_t)max(p, 0) * s_tok_stride,
+                               p >= 0 ? 16u : 0u);
                     asm volatile("st.shared.s32 [%0], %1;" ::"r"(st + 4352 + r16 * 4), "r"(p) : "memory");
                 }
             }
-            cp_async_commit();   /* one group per step, empty or not, keeps the wait count uniform */
+            cp_async_commit();   /* one group per stage, empty or not, keeps the wait count uniform */
         };
-        int32_t p_next[RING_STAGES];
+        int32_t pa = my_pos(0), pb = my_pos(1), pc = my_pos(2), pd = my_pos(3);
+        issue(0, pa);
+        issue(1, pb);
+        pa = pc;
+        pb = pd;
+
+        /* Q fragments with scale * log2(e) folded in, rounded to fp16 once; and, per 32-wide block,
+         * -1152 * sum(q): K codes enter the MMA as the fp16 numbers 1152 + code (one byte permute per
+         * pair, no subtract), so each block's partial product starts from that correction. */
+        uint32_t qs[NHT][KS][2];
+        float qcorr[NHT][NB][2];
 #pragma unroll
-        for (int i = 0; i < RING_STAGES; i++) p_next[i] = my_pos(i);
+        for (int nt = 0; nt < NHT; nt++) {
+            const uint32_t hg = nt * 8 + g;
+            const bool live = hg < P.gqa;
+            const size_t qoff = ((size_t)u * P.n_head + (size_t)kh * P.gqa + hg) * HD;
+            float bsum[NB];
 #pragma unroll
-        for (int i = 0; i < RING_STAGES - 1; i++) issue(i, p_next[i]);
-        int32_t p_ahead = p_next[RING_STAGES - 1];
-        for (uint32_t it = 0; it < n_my; it++) {
-            const int32_t p_issue = p_ahead;
-            p_ahead = my_pos(it + RING_STAGES);          /* consumed by the next iteration's issue */
-            issue(it + RING_STAGES - 1, p_issue);
-            cp_async_wait<RING_STAGES - 1>();
+            for (int ks = 0; ks < KS; ks++) {
+                float x0 = 0.f, x1 = 0.f, x2 = 0.f, x3 = 0.f;
+                if (live) {
+                    const int d = qk_dim<LAY>(ks, t);
+                    if (P.q_bf16) {
+                        const uint2 w = *reinterpret_cast<const uint2 *>(
+                            reinterpret_cast<const __nv_bfloat16 *>(P.q) + qoff + d);
+                        x0 = __uint_as_float(w.x << 16);
+                        x1 = __uint_as_float(w.x & 0xffff0000u);
+                        x2 = __uint_as_float(w.y << 16);
+                        x3 = __uint_as_float(w.y & 0xffff0000u);
+                    } else {
+                        const float4 w =
+                            *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(P.q) + qoff + d);
+                        x0 = w.x; x1 = w.y; x2 = w.z; x3 = w.w;
+                    }
+                }
+                const __half2 h0 = __floats2half2_rn(x0 * P.scale_log2e, x1 * P.scale_log2e);
+                const __half2 h1 = __floats2half2_rn(x2 * P.scale_log2e, x3 * P.scale_log2e);
+                qs[nt][ks][0] = h2u(h0);
+                qs[nt][ks][1] = h2u(h1);
+                const float part = (__low2float(h0) + __high2float(h0)) + (__low2float(h1) + __high2float(h1));
+                if (ks & 1) bsum[ks >> 1] += part; else bsum[ks >> 1] = part;
+            }
+#pragma unroll
+            for (int b = 0; b < NB; b++) {
+                float v = bsum[b];
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);     /* sum over the block for head nt*8+g */
+                qcorr[nt][b][0] = -1152.f * __shfl_sync(0xffffffffu, v, (2 * t) * 4);
+                qcorr[nt][b][1] = -1152.f * __shfl_sync(0xffffffffu, v, (2 * t + 1) * 4);
+            }
+        }
+
+        for (uint32_t it = 0; it < n_even; it += 2) {
+            issue(it + 2, pa);
+            issue(it + 3, pb);
+            pa = my_pos(it + 4);                 /* consumed by the next iteration's issue */
+            pb = my_pos(it + 5);
+            cp_async_wait<2>();                  /* all but the two newest stages have landed */
             __syncwarp();
-            const uint32_t st = ring + (it % RING_STAGES) * RING_STAGE_BYTES;
-            int32_t pk[2], pv[4];
-            pk[0] = (int32_t)lds32(st + 4352 + 4 * g);
-            pk[1] = (int32_t)lds32(st + 4352 + 4 * (g + 8));
-            {
-                const uint2 w0 = lds64(st + 4352 + 8 * t), w1 = lds64(st + 4352 + 32 + 8 * t);
-                pv[0] = (int32_t)w0.x; pv[1] = (int32_t)w0.y; pv[2] = (int32_t)w1.x; pv[3] = (int32_t)w1.y;
+            uint32_t st[2];
+            st[0] = ring + (it % RING_STAGES) * RING_STAGE_BYTES;
+            st[1] = ring + ((it + 1) % RING_STAGES) * RING_STAGE_BYTES;
+
+            /* ---- S^T = K . Q^T for both tiles */
+            float sc[2][NHT][4];
+            bool kok[2][2];
+#pragma unroll
+            for (int ti = 0; ti < 2; ti++) {
+                kok[ti][0] = (int32_t)lds32(st[ti] + 4352 + 4 * g) >= 0;
+                kok[ti][1] = (int32_t)lds32(st[ti] + 4352 + 4 * (g + 8)) >= 0;
+                float ksc[2][NB];
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                    const uint2 w = lds64(st[ti] + 4096 + (g + 8 * r) * 16);
+                    const float2 f01 = __half22float2(u2h(w.x)), f23 = __half22float2(u2h(w.y));
+                    ksc[r][0] = f01.x; ksc[r][1] = f01.y; ksc[r][2] = f23.x; ksc[r][3] = f23.y;
+                }
+#pragma unroll
+                for (int nt = 0; nt < NHT; nt++) sc[ti][nt][0] = sc[ti][nt][1] = sc[ti][nt][2] = sc[ti][nt][3] = 0.f;
+#pragma unroll
+                for (int b = 0; b < NB; b++) {
+                    const uint32_t ko = (((2 * b + (t >> 1)) ^ ((g & 3) << 1)) << 4) + 8 * (t & 1);
+                    const uint2 w0 = lds64(st[ti] + g * 128 + ko);
+                    const uint2 w1 = lds64(st[ti] + (g + 8) * 128 + ko);
+                    float cb[NHT][4];
+#pragma unroll
+                    for (int nt = 0; nt < NHT; nt++) {
+                        cb[nt][0] = cb[nt][2] = qcorr[nt][b][0];
+                        cb[nt][1] = cb[nt][3] = qcorr[nt][b][1];
+                    }
+#pragma unroll
+                    for (int jj = 0; jj < 2; jj++) {
+                        const uint32_t x0 = (jj ? w0.y : w0.x) ^ 0x80808080u, x1 = (jj ? w1.y : w1.x) ^ 0x80808080u;
+                        const uint32_t a0 = __byte_perm(x0, 0x64646464u, 0x4140), a2 = __byte_perm(x0, 0x64646464u, 0x4342);
+                        const uint32_t a1 = __byte_perm(x1, 0x64646464u, 0x4140), a3 = __byte_perm(x1, 0x64646464u, 0x4342);
+#pragma unroll
+                        for (int nt = 0; nt < NHT; nt++)
+                            mma16816(cb[nt], a0, a1, a2, a3, qs[nt][2 * b + jj][0], qs[nt][2 * b + jj][1]);
+                    }
+#pragma unroll
+                    for (int nt = 0; nt < NHT; nt++) {
+                        sc[ti][nt][0] = fmaf(ksc[0][b], cb[nt][0], sc[ti][nt][0]);
+                        sc[ti][nt][1] = fmaf(ksc[0][b], cb[nt][1], sc[ti][nt][1]);
+                        sc[ti][nt][2] = fmaf(ksc[1][b], cb[nt][2], sc[ti][nt][2]);
+                        sc[ti][nt][3] = fmaf(ksc[1][b], cb[nt][3], sc[ti][nt][3]);
+                    }
+                }
             }
-            uint2 kw[2][NBQ];
-            uint32_t vw[4][NBQ];
-            float ksc[2][NBQ];
-            __half vsc[4][NBQ];
+
+            /* ---- online softmax over the 32 positions; lanes (g, t): positions g / g+8, heads 2t, 2t+1 */
+            uint32_t pb0[2][NHT], pb1[2][NHT];
 #pragma unroll
-            for (int r = 0; r < 2; r++) {
-                const uint32_t row = g + 8 * r;
+            for (int nt = 0; nt < NHT; nt++) {
 #pragma unroll
-                for (int b = 0; b < NB; b++)
-                    kw[r][b] = lds64(st + row * 128 + (((2 * b + (t >> 1)) ^ ((g & 3) << 1)) << 4) + 8 * (t & 1));
-                const uint2 w = lds64(st + 4096 + row * 16);
-                const __half2 h01 = u2h(w.x), h23 = u2h(w.y);
-                ksc[r][0] = pk[r] >= 0 ? __low2float(h01) * P.scale_log2e : 0.f;
-                ksc[r][1] = pk[r] >= 0 ? __high2float(h01) * P.scale_log2e : 0.f;
-                ksc[r][2] = pk[r] >= 0 ? __low2float(h23) * P.scale_log2e : 0.f;
-                ksc[r][3] = pk[r] >= 0 ? __high2float(h23) * P.scale_log2e : 0.f;
+                for (int ti = 0; ti < 2; ti++) {
+                    if (!kok[ti][0]) sc[ti][nt][0] = sc[ti][nt][1] = -CUDART_INF_F;
+                    if (!kok[ti][1]) sc[ti][nt][2] = sc[ti][nt][3] = -CUDART_INF_F;
+                }
+                const float mx0 = warp_max_over_g(fmaxf(fmaxf(sc[0][nt][0], sc[0][nt][2]), fmaxf(sc[1][nt][0], sc[1][nt][2])));
+                const float mx1 = warp_max_over_g(fmaxf(fmaxf(sc[0][nt][1], sc[0][nt][3]), fmaxf(sc[1][nt][1], sc[1][nt][3])));
+                const float mn0 = fmaxf(m_run[nt][0], mx0), mn1 = fmaxf(m_run[nt][1], mx1);
+                const float mu0 = mn0 == -CUDART_INF_F ? 0.f : mn0;
+                const float mu1 = mn1 == -CUDART_INF_F ? 0.f : mn1;
+                const float al0 = ex2(m_run[nt][0] - mu0), al1 = ex2(m_run[nt][1] - mu1);
+                m_run[nt][0] = mn0;
+                m_run[nt][1] = mn1;
+                float ls0 = 0.f, ls1 = 0.f;
+#pragma unroll
+                for (int ti = 0; ti < 2; ti++) {
+                    const __half2 h0 = __floats2half2_rn(ex2(sc[ti][nt][0] - mu0), ex2(sc[ti][nt][1] - mu1));
+                    const __half2 h1 = __floats2half2_rn(ex2(sc[ti][nt][2] - mu0), ex2(sc[ti][nt][3] - mu1));
+                    const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+                    ls0 += f0.x + f1.x;
+                    ls1 += f0.y + f1.y;
+                    pb0[ti][nt] = movmatrix_t(h2u(h0));   /* {P[pos 2t][head g], P[pos 2t+1][head g]} */
+                    pb1[ti][nt] = movmatrix_t(h2u(h1));   /* positions 2t+8, 2t+9 */
+                }
+                l_run[nt][0] = fmaf(l_run[nt][0], al0, ls0);
+                l_run[nt][1] = fmaf(l_run[nt][1], al1, ls1);
+                if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
+#pragma unroll
+                    for (int mt = 0; mt < MT; mt++) {
+                        acc[nt][mt][0] *= al0; acc[nt][mt][1] *= al1;
+                        acc[nt][mt][2] *= al0; acc[nt][mt][3] *= al1;
+                    }
+                }
             }
+
+            /* ---- O^T += V^T . P^T, tile after tile on the same accumulators, 8 independent chains */
 #pragma unroll
-            for (int r = 0; r < 4; r++) {
-                const uint32_t row = 2 * t + (r & 1) + 8 * (r >> 1);
+            for (int ti = 0; ti < 2; ti++) {
+                uint2 vs[4];
 #pragma unroll
-                for (int b = 0; b < NB; b++)
-                    vw[r][b] = lds32(st + 2048 + row * 128 + (((2 * b + (g >> 2)) ^ (t << 1)) << 4) + 4 * (g & 3));
-                const uint2 w = lds64(st + 4096 + row * 16 + 8);
-                const __half2 h01 = u2h(w.x), h23 = u2h(w.y);
-                const __half z = __ushort_as_half(0);
-                vsc[r][0] = pv[r] >= 0 ? __low2half(h01) : z;
-                vsc[r][1] = pv[r] >= 0 ? __high2half(h01) : z;
-                vsc[r][2] = pv[r] >= 0 ? __low2half(h23) : z;
-                vsc[r][3] = pv[r] >= 0 ? __high2half(h23) : z;
+                for (int r = 0; r < 4; r++) vs[r] = lds64(st[ti] + 4096 + (2 * t + (r & 1) + 8 * (r >> 1)) * 16 + 8);
+#pragma unroll
+                for (int b = 0; b < NB; b++) {
+                    /* fp16 scale of block b: halves 0,1 in .x, halves 2,3 in .y */
+                    const uint32_t sel = (b & 1) ? 0x7632 : 0x5410;
+                    const uint32_t s01 = __byte_perm(b < 2 ? vs[0].x : vs[0].y, b < 2 ? vs[1].x : vs[1].y, sel);
+                    const uint32_t s23 = __byte_perm(b < 2 ? vs[2].x : vs[2].y, b < 2 ? vs[3].x : vs[3].y, sel);
+                    uint32_t bb0[NHT], bb1[NHT];
+#pragma unroll
+                    for (int nt = 0; nt < NHT; nt++) {
+                        bb0[nt] = h2u(__hmul2(u2h(pb0[ti][nt]), u2h(s01)));
+                        bb1[nt] = h2u(__hmul2(u2h(pb1[ti][nt]), u2h(s23)));
+                    }
+                    const uint32_t vo = 2048 + (((2 * b + (g >> 2)) ^ (t << 1)) << 4) + 4 * (g & 3);
+                    const uint32_t v0 = lds32(st[ti] + vo + (2 * t) * 128), v1 = lds32(st[ti] + vo + (2 * t + 1) * 128);
+                    const uint32_t v2 = lds32(st[ti] + vo + (2 * t + 8) * 128), v3 = lds32(st[ti] + vo + (2 * t + 9) * 128);
+                    {
+                        const uint32_t a0 = cvt_i8_pair<0>(v0, v1), a1 = cvt_i8_pair<1>(v0, v1);
+                        const uint32_t a2 = cvt_i8_pair<0>(v2, v3), a3 = cvt_i8_pair<1>(v2, v3);
+#pragma unroll
+                        for (int nt = 0; nt < NHT; nt++) mma16816(acc[nt][2 * b], a0, a1, a2, a3, bb0[nt], bb1[nt]);
+                    }
+                    {
+                        const uint32_t a0 = cvt_i8_pair<2>(v0, v1), a1 = cvt_i8_pair<3>(v0, v1);
+                        const uint32_t a2 = cvt_i8_pair<2>(v2, v3), a3 = cvt_i8_pair<3>(v2, v3);
+#pragma unroll
+                        for (int nt = 0; nt < NHT; nt++) mma16816(acc[nt][2 * b + 1], a0, a1, a2, a3, bb0[nt], bb1[nt]);
+                    }
+                }
             }
-            const uint8_t *const krow[2] = {nullptr, nullptr};
-            const uint8_t *const vrow[4] = {nullptr, nullptr, nullptr, nullptr};
-            compute(pk, pv, kw, vw, ksc, vsc, krow, vrow);
-            __syncwarp();   /* every lane is done with this stage before a later issue overwrites it */
+            __syncwarp();   /* every lane is done with both stages before a later issue overwrites them */
         }
         cp_async_wait<0>();
         __syncthreads();    /* the epilogue below reuses the ring memory of all warps */
@@ -633,7 +770,7 @@ q4_decode_k(const DecParams P) {
     const uint32_t gqa = P.gqa;
     const size_t unit = (size_t)u * P.n_kvh + kh;
     __shared__ uint32_t s_last;
-    __shared__ float s_w[DEC_GROUP * 16], s_M[16], s_L[16];
+    __shared__ float s_w[DEC_GROUP * 16], s_l[DEC_GROUP * 16], s_M[16], s_L[16];
 
     /* Merge `count` (<= DEC_GROUP) records spaced HEADS*REC floats apart.  Weights are computed once
      * per (record, head) by separate threads; then every thread owns 4 output dims of some heads and
@@ -641,8 +778,10 @@ q4_decode_k(const DecParams P) {
      * for the next level, otherwise the result is finalised. */
     auto merge = [&](const float *recs, uint32_t count, bool global, float *dst_rec) {
         for (uint32_t i = threadIdx.x; i < count * HEADS; i += DEC_THREADS) {
-            const float *r = recs + (size_t)i * REC + HD;
-            s_w[i] = global ? __ldcg(r) : r[0];
+            const float2 *r = reinterpret_cast<const float2 *>(recs + (size_t)i * REC + HD);
+            const float2 ml = global ? __ldcg(r) : *r;   /* one round trip for every m and l */
+            s_w[i] = ml.x;
+            s_l[i] = ml.y;
         }
         __syncthreads();
         if (threadIdx.x < gqa) {
@@ -652,10 +791,9 @@ q4_decode_k(const DecParams P) {
             const float Mu = M == -CUDART_INF_F ? 0.f : M;
             float L = 0.f;
             for (uint32_t s = 0; s < count; s++) {
-                const float *r = recs + ((size_t)s * HEADS + h) * REC + HD + 1;
                 const float w = ex2(s_w[s * HEADS + h] - Mu);
                 s_w[s * HEADS + h] = w;
-                L = fmaf(w, global ? __ldcg(r) : r[0], L);
+                L = fmaf(w, s_l[s * HEADS + h], L);
             }
             s_M[h] = M;
             s_L[h] = L;
@@ -664,13 +802,20 @@ q4_decode_k(const DecParams P) {
         for (uint32_t i = threadIdx.x; i < gqa * (HD / 4); i += DEC_THREADS) {
             const uint32_t h = i / (HD / 4), d = (i % (HD / 4)) * 4;
             float4 A = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-            for (uint32_t s = 0; s < count; s++) {
-                const float4 *r = reinterpret_cast<const float4 *>(recs + ((size_t)s * HEADS + h) * REC + d);
-                const float4 x = global ? __ldcg(r) : *r;
-                const float w = s_w[s * HEADS + h];
-                A.x = fmaf(w, x.x, A.x); A.y = fmaf(w, x.y, A.y);
-                A.z = fmaf(w, x.z, A.z); A.w = fmaf(w, x.w, A.w);
+            for (uint32_t s0 = 0; s0 < count; s0 += 8) {   /* 8 independent 16-byte loads in flight */
+                float4 x[8];
+#pragma unroll
+                for (uint32_t k = 0; k < 8; k++) {
+                    const uint32_t sidx = min(s0 + k, count - 1u);
+                    const float4 *r = reinterpret_cast<const float4 *>(recs + ((size_t)sidx * HEADS + h) * REC + d);
+                    x[k] = global ? __ldcg(r) : *r;
+                }
+#pragma unroll
+                for (uint32_t k = 0; k < 8; k++) {
+                    const float w = s0 + k < count ? s_w[(s0 + k) * HEADS + h] : 0.f;
+                    A.x = fmaf(w, x[k].x, A.x); A.y = fmaf(w, x[k].y, A.y);
+                    A.z = fmaf(w, x[k].z, A.z); A.w = fmaf(w, x[k].w, A.w);
+                }
             }
             const float M = s_M[h], L = s_L[h];
             if (dst_rec) {
@@ -822,8 +967,8 @@ bool q4i_decode(const Q4DecodeArgs &a) {
     const uint32_t units = a.n_units * a.n_kvh;
     uint32_t S = split_override();
     if (!S) {
-        /* one wave: 4 resident blocks per SM for the staged q8_0 kernel, 3 otherwise */
-        const uint32_t target = (uint32_t)g_q4.sm_count * ((a.layout == LAY_Q8P && a.hd == 128) ? 4u : 3u);
+        /* one wave of 3 resident blocks per SM */
+        const uint32_t target = (uint32_t)g_q4.sm_count * 3u;
         S = target / units;
         const uint32_t cap = (steps + DEC_WARPS - 1u) / DEC_WARPS;
         if (S > cap) S = cap;
