@@ -379,6 +379,66 @@ def extras_dense(torch, q4gpu, L, ext, peak_gbs, kinds=("q8_0", "f16", "f32")):
     return res
 
 
+def run_seqshard(args, torch, q4gpu, L, dist, rank, world, peak_gbs):
+    """configs[4]: one session at ctx 262144, dense attention; rank r owns an even contiguous slice of the
+    rows, computes (m, l, acc) records over it, the records are all-gathered over NCCL and merged on every
+    rank.  One step = 12 layers; time = max over ranks, on the device."""
+    from q4gpu import shard
+    ctx = 262144
+    b, e = shard.rows_for_rank(ctx, rank, world)
+    rows = e - b
+    res = {}
+    stream = torch.cuda.Stream()
+    for name, kind, rowb in (("q8_0", 2, 136), ("f16", 1, 256), ("f32", 0, 512)):
+        if name not in args.dense_kinds.split(","):
+            continue
+        st = q4gpu.KVStore(N_LAYERS, N_KVH, HD, rows, kind)
+        with torch.cuda.stream(stream):
+            q4gpu.use_torch_stream()
+            torch.manual_seed(SEED + rank)
+            fill_store(torch, st, rows)
+            q = torch.randn(N_LAYERS, N_HEAD, HD, device="cuda").to(torch.bfloat16)
+            part = torch.empty(N_LAYERS, N_HEAD, HD + 2, device="cuda")
+            out = torch.empty(N_LAYERS, N_HEAD, HD, device="cuda")
+
+            def step():
+                for layer in range(N_LAYERS):
+                    st.decode_partial(layer, q[layer], part[layer], N_HEAD, SCALE, n_kv=rows, q_bf16=True)
+                    if world > 1:
+                        allp = shard.exchange_records(part[layer])
+                    else:
+                        allp = part[layer:layer + 1]
+                    q4gpu.check(L.q4_gpu_lse_merge(allp.data_ptr(), world, N_HEAD, HD, None, out[layer].data_ptr()),
+                                "q4_gpu_lse_merge")
+            for _ in range(max(args.warmup, 3)):
+                step()
+            stream.synchronize()
+            if dist is not None:
+                dist.barrier()
+            torch.cuda.synchronize()
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record(stream)
+            for _ in range(args.steps):
+                step()
+            ev1.record(stream)
+            ev1.synchronize()
+            dt = ev0.elapsed_time(ev1) * 1e-3
+        if dist is not None:
+            t = torch.tensor([dt], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t.item())
+        us = 1e6 * dt / (args.steps * N_LAYERS)
+        by = ctx * N_KVH * rowb * 2
+        res[name] = {"us_per_layer": us, "bytes_per_layer_all_ranks": by, "achieved_gbs_all_ranks": by / us / 1e3,
+                     "frac_of_measured_hbm_x_ranks": by / us / 1e3 / (peak_gbs * world)}
+        st.close()
+    L.q4_gpu_set_stream(None)
+    if rank == 0:
+        print(json.dumps({"metric": "dense_decode_us_per_layer_ctx262144", "mode": "seqshard", "n_gpus": world,
+                          "steps": args.steps, "exchange": "NCCL all-gather of %d B per rank per layer" % (N_HEAD * (HD + 2) * 4),
+                          "result": res}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -393,6 +453,9 @@ def main():
     ap.add_argument("--only", default="", choices=["", "single", "dense"],
                     help="run just one of the ctx-262144 extras (for profiler captures)")
     ap.add_argument("--dense-kinds", default="q8_0,f16,f32")
+    ap.add_argument("--mode", default="sessions", choices=["sessions", "seqshard"],
+                    help="sessions: the headline (sessions sharded over ranks); seqshard: one ctx-262144 "
+                         "session, dense attention, rows sharded over ranks, records all-gathered (configs[4])")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -423,6 +486,12 @@ def main():
     peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
     peak_src = "measured (MEASURED_PEAKS.json)" if "hbm_gbs" in peaks else "fallback 6.65 TB/s"
 
+    if args.mode == "seqshard":
+        run_seqshard(args, torch, q4gpu, L, dist, rank, world, peak_gbs)
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     if args.only:
         ext = torch.cuda.ExternalStream(L.q4_gpu_stream())
         torch.manual_seed(SEED)

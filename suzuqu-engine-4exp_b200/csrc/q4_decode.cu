@@ -37,6 +37,7 @@
 #include <cuda_bf16.h>
 #include <math_constants.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include "q4_internal.h"
 
@@ -61,6 +62,7 @@ struct DecParams {
     uint32_t kv_base;
     float scale_log2e;
     uint32_t S;
+    uint32_t debug;   /* measurement aid: 1 = copy the tiles but skip the arithmetic */
     float *scratch;
     uint32_t *counters;
     uint32_t *err;
@@ -167,6 +169,110 @@ template <int LAY>
 __device__ __forceinline__ int qk_dim(int ks, int t) {
     if (LAY == LAY_Q8P || LAY == LAY_Q8R) return 32 * (ks >> 1) + 8 * t + 4 * (ks & 1);
     return 16 * ks + 4 * t;
+}
+
+/* ---- merge of (acc, m, l) records ------------------------------------------------------------- */
+struct MergeOut {
+    float *out, *part_out;
+    const float *gate;
+    size_t row0;       /* index of the group's first head in [unit][head] order */
+    uint32_t gqa;
+};
+
+/* arrive on a counter; true for the last of `expected` arrivals (which also re-arms it) */
+__device__ __noinline__ bool arrive_last(uint32_t *ctr, uint32_t expected) {
+    __shared__ uint32_t s_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t prev = atomicAdd(ctr, 1u);
+        s_last = (prev == expected - 1u);
+        if (s_last) *ctr = 0u;   /* ready for the next launch / graph replay */
+    }
+    __syncthreads();
+    const bool last = s_last != 0u;
+    if (last) __threadfence();
+    return last;
+}
+
+/* Merge `count` (<= DEC_GROUP) records spaced HEADS*REC floats apart (log2-domain max).  Weights are
+ * computed once per (record, head); then every thread owns 4 output dims of some heads and streams
+ * the accumulators with 8 independent 16-byte loads in flight.  dst_rec != null stores a merged
+ * record for the next level, otherwise the result is finalised: out = acc / l * sigmoid(gate), or the
+ * public record {m (natural-log units), l, acc[HD]}.  Deliberately not inlined: the kernel calls it
+ * from one place for every merge level, and a small kernel image matters for launches that run each
+ * instruction once. */
+template <int HD, int HEADS>
+__device__ __noinline__ void merge_records(const float *recs, uint32_t count, bool global, float *dst_rec,
+                                           const MergeOut mo) {
+    constexpr int REC = HD + 4;
+    __shared__ float s_w[DEC_GROUP * 16], s_l[DEC_GROUP * 16], s_M[16], s_L[16];
+    const uint32_t gqa = mo.gqa;
+    for (uint32_t i = threadIdx.x; i < count * HEADS; i += DEC_THREADS) {
+        const float2 *r = reinterpret_cast<const float2 *>(recs + (size_t)i * REC + HD);
+        const float2 ml = global ? __ldcg(r) : *r;   /* one round trip for every m and l */
+        s_w[i] = ml.x;
+        s_l[i] = ml.y;
+    }
+    __syncthreads();
+    if (threadIdx.x < gqa) {
+        const uint32_t h = threadIdx.x;
+        float M = -CUDART_INF_F;
+        for (uint32_t s = 0; s < count; s++) M = fmaxf(M, s_w[s * HEADS + h]);
+        const float Mu = M == -CUDART_INF_F ? 0.f : M;
+        float L = 0.f;
+        for (uint32_t s = 0; s < count; s++) {
+            const float w = ex2(s_w[s * HEADS + h] - Mu);
+            s_w[s * HEADS + h] = w;
+            L = fmaf(w, s_l[s * HEADS + h], L);
+        }
+        s_M[h] = M;
+        s_L[h] = L;
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < gqa * (HD / 4); i += DEC_THREADS) {
+        const uint32_t h = i / (HD / 4), d = (i % (HD / 4)) * 4;
+        float4 A = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t s0 = 0; s0 < count; s0 += 8) {
+            float4 x[8];
+#pragma unroll
+            for (uint32_t k = 0; k < 8; k++) {
+                const uint32_t sidx = min(s0 + k, count - 1u);
+                const float4 *r = reinterpret_cast<const float4 *>(recs + ((size_t)sidx * HEADS + h) * REC + d);
+                x[k] = global ? __ldcg(r) : *r;
+            }
+#pragma unroll
+            for (uint32_t k = 0; k < 8; k++) {
+                const float w = s0 + k < count ? s_w[(s0 + k) * HEADS + h] : 0.f;
+                A.x = fmaf(w, x[k].x, A.x); A.y = fmaf(w, x[k].y, A.y);
+                A.z = fmaf(w, x[k].z, A.z); A.w = fmaf(w, x[k].w, A.w);
+            }
+        }
+        const float M = s_M[h], L = s_L[h];
+        if (dst_rec) {
+            float *o = dst_rec + (size_t)h * REC;
+            *reinterpret_cast<float4 *>(o + d) = A;
+            if (d == 0) { o[HD] = M; o[HD + 1] = L; }
+        } else if (mo.part_out) {
+            float *pr = mo.part_out + (mo.row0 + h) * (HD + 2);
+            if (d == 0) {
+                pr[0] = L > 0.f ? M * 0.6931471805599453f : 0.f;
+                pr[1] = L;
+            }
+            pr[2 + d] = A.x; pr[3 + d] = A.y; pr[4 + d] = A.z; pr[5 + d] = A.w;
+        } else {
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            float4 o = make_float4(A.x * inv, A.y * inv, A.z * inv, A.w * inv);
+            const size_t off = (mo.row0 + h) * HD + d;
+            if (mo.gate) {
+                const float4 gt = *reinterpret_cast<const float4 *>(mo.gate + off);
+                o.x *= 1.f / (1.f + __expf(-gt.x)); o.y *= 1.f / (1.f + __expf(-gt.y));
+                o.z *= 1.f / (1.f + __expf(-gt.z)); o.w *= 1.f / (1.f + __expf(-gt.w));
+            }
+            *reinterpret_cast<float4 *>(mo.out + off) = o;
+        }
+    }
+    __syncthreads();   /* s_w is reused by the next level */
 }
 
 /* ---- the kernel ---------------------------------------------------------------------------- */
@@ -441,11 +547,19 @@ q4_decode_k(const DecParams P) {
             koff[j] = row * 128 + ((c8 ^ ((row & 3) << 1)) << 4);
             voff[j] = 2048 + row * 128 + ((c8 ^ (((row >> 1) & 3) << 1)) << 4);
         }
+        /* The list entry is only loaded here; its range check waits until issue() needs the value one
+         * or two iterations later, so the load latency stays off the critical path. */
         auto my_pos = [&](uint32_t it) -> int32_t {
-            return it < n_my ? position(((s_begin + warp + it * DEC_WARPS) << 4) + r16) : -1;
+            const uint32_t j = ((s_begin + warp + it * DEC_WARPS) << 4) + r16;
+            if (it >= n_my || j >= n_pos) return -1;
+            return list ? list[j] : (int32_t)j;
         };
         auto issue = [&](uint32_t it, int32_t p) {
             if (it < n_even) {
+                if (p >= (int32_t)max_kv) {
+                    atomicOr(P.err, (uint32_t)Q4E_RANGE);
+                    p = -1;
+                }
                 const uint32_t st = ring + (it % RING_STAGES) * RING_STAGE_BYTES;
 #pragma unroll
                 for (uint32_t j = 0; j < 4; j++) {
@@ -463,11 +577,11 @@ q4_decode_k(const DecParams P) {
             }
             cp_async_commit();   /* one group per stage, empty or not, keeps the wait count uniform */
         };
-        int32_t pa = my_pos(0), pb = my_pos(1), pc = my_pos(2), pd = my_pos(3);
+        int32_t pa = my_pos(0), pb = my_pos(1), pc = my_pos(2), pd = my_pos(3), pe = my_pos(4), pf = my_pos(5);
         issue(0, pa);
         issue(1, pb);
-        pa = pc;
-        pb = pd;
+        pa = pc; pb = pd;      /* next iteration's stages */
+        pc = pe; pd = pf;      /* the ones after: list entries are fetched two iterations ahead */
 
         /* Q fragments with scale * log2(e) folded in, rounded to fp16 once; and, per 32-wide block,
          * -1152 * sum(q): K codes enter the MMA as the fp16 numbers 1152 + code (one byte permute per
@@ -518,13 +632,19 @@ q4_decode_k(const DecParams P) {
         for (uint32_t it = 0; it < n_even; it += 2) {
             issue(it + 2, pa);
             issue(it + 3, pb);
-            pa = my_pos(it + 4);                 /* consumed by the next iteration's issue */
-            pb = my_pos(it + 5);
+            pa = pc; pb = pd;
+            pc = my_pos(it + 6);                 /* consumed by the issue two iterations from now */
+            pd = my_pos(it + 7);
             cp_async_wait<2>();                  /* all but the two newest stages have landed */
             __syncwarp();
             uint32_t st[2];
             st[0] = ring + (it % RING_STAGES) * RING_STAGE_BYTES;
             st[1] = ring + ((it + 1) % RING_STAGES) * RING_STAGE_BYTES;
+            if (P.debug) {
+                acc[0][0][0] += __uint_as_float(lds32(st[0] + 4 * lane) ^ lds32(st[1] + 2048 + 4 * lane));
+                __syncwarp();
+                continue;
+            }
 
             /* ---- S^T = K . Q^T for both tiles */
             float sc[2][NHT][4];
@@ -767,102 +887,13 @@ q4_decode_k(const DecParams P) {
     }
     __syncthreads();
 
-    const uint32_t gqa = P.gqa;
     const size_t unit = (size_t)u * P.n_kvh + kh;
-    __shared__ uint32_t s_last;
-    __shared__ float s_w[DEC_GROUP * 16], s_l[DEC_GROUP * 16], s_M[16], s_L[16];
-
-    /* Merge `count` (<= DEC_GROUP) records spaced HEADS*REC floats apart.  Weights are computed once
-     * per (record, head) by separate threads; then every thread owns 4 output dims of some heads and
-     * streams the accumulators with independent 16-byte loads.  dst_rec != null stores a merged record
-     * for the next level, otherwise the result is finalised. */
-    auto merge = [&](const float *recs, uint32_t count, bool global, float *dst_rec) {
-        for (uint32_t i = threadIdx.x; i < count * HEADS; i += DEC_THREADS) {
-            const float2 *r = reinterpret_cast<const float2 *>(recs + (size_t)i * REC + HD);
-            const float2 ml = global ? __ldcg(r) : *r;   /* one round trip for every m and l */
-            s_w[i] = ml.x;
-            s_l[i] = ml.y;
-        }
-        __syncthreads();
-        if (threadIdx.x < gqa) {
-            const uint32_t h = threadIdx.x;
-            float M = -CUDART_INF_F;
-            for (uint32_t s = 0; s < count; s++) M = fmaxf(M, s_w[s * HEADS + h]);
-            const float Mu = M == -CUDART_INF_F ? 0.f : M;
-            float L = 0.f;
-            for (uint32_t s = 0; s < count; s++) {
-                const float w = ex2(s_w[s * HEADS + h] - Mu);
-                s_w[s * HEADS + h] = w;
-                L = fmaf(w, s_l[s * HEADS + h], L);
-            }
-            s_M[h] = M;
-            s_L[h] = L;
-        }
-        __syncthreads();
-        for (uint32_t i = threadIdx.x; i < gqa * (HD / 4); i += DEC_THREADS) {
-            const uint32_t h = i / (HD / 4), d = (i % (HD / 4)) * 4;
-            float4 A = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (uint32_t s0 = 0; s0 < count; s0 += 8) {   /* 8 independent 16-byte loads in flight */
-                float4 x[8];
-#pragma unroll
-                for (uint32_t k = 0; k < 8; k++) {
-                    const uint32_t sidx = min(s0 + k, count - 1u);
-                    const float4 *r = reinterpret_cast<const float4 *>(recs + ((size_t)sidx * HEADS + h) * REC + d);
-                    x[k] = global ? __ldcg(r) : *r;
-                }
-#pragma unroll
-                for (uint32_t k = 0; k < 8; k++) {
-                    const float w = s0 + k < count ? s_w[(s0 + k) * HEADS + h] : 0.f;
-                    A.x = fmaf(w, x[k].x, A.x); A.y = fmaf(w, x[k].y, A.y);
-                    A.z = fmaf(w, x[k].z, A.z); A.w = fmaf(w, x[k].w, A.w);
-                }
-            }
-            const float M = s_M[h], L = s_L[h];
-            if (dst_rec) {
-                float *o = dst_rec + (size_t)h * REC;
-                *reinterpret_cast<float4 *>(o + d) = A;
-                if (d == 0) { o[HD] = M; o[HD + 1] = L; }
-            } else {
-                const uint32_t head = kh * gqa + h;
-                if (P.part_out) {   /* public record: {m (natural log units), l, acc[HD]} */
-                    float *pr = P.part_out + ((size_t)u * P.n_head + head) * (HD + 2);
-                    if (d == 0) {
-                        pr[0] = L > 0.f ? M * 0.6931471805599453f : 0.f;
-                        pr[1] = L;
-                    }
-                    pr[2 + d] = A.x; pr[3 + d] = A.y; pr[4 + d] = A.z; pr[5 + d] = A.w;
-                } else {
-                    const float inv = L > 0.f ? 1.f / L : 0.f;
-                    float4 o = make_float4(A.x * inv, A.y * inv, A.z * inv, A.w * inv);
-                    const size_t off = ((size_t)u * P.n_head + head) * HD + d;
-                    if (P.gate) {
-                        const float4 gt = *reinterpret_cast<const float4 *>(P.gate + off);
-                        o.x *= 1.f / (1.f + __expf(-gt.x)); o.y *= 1.f / (1.f + __expf(-gt.y));
-                        o.z *= 1.f / (1.f + __expf(-gt.z)); o.w *= 1.f / (1.f + __expf(-gt.w));
-                    }
-                    *reinterpret_cast<float4 *>(P.out + off) = o;
-                }
-            }
-        }
-        __syncthreads();   /* s_w is reused by the next level */
-    };
-    /* arrive on a counter; true for the last of `expected` arrivals (which also re-arms it) */
-    auto arrive_last = [&](uint32_t *ctr, uint32_t expected) -> bool {
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            const uint32_t prev = atomicAdd(ctr, 1u);
-            s_last = (prev == expected - 1u);
-            if (s_last) *ctr = 0u;   /* ready for the next launch / graph replay */
-        }
-        __syncthreads();
-        const bool last = s_last != 0u;
-        if (last) __threadfence();
-        return last;
-    };
-
+    MergeOut mo;
+    mo.out = P.out; mo.part_out = P.part_out; mo.gate = P.gate;
+    mo.row0 = (size_t)u * P.n_head + (size_t)kh * P.gqa;
+    mo.gqa = P.gqa;
     if (S == 1) {
-        merge(sm, DEC_WARPS, false, nullptr);
+        merge_records<HD, HEADS>(sm, DEC_WARPS, false, nullptr, mo);
         return;
     }
     /* level 1: record per block; groups of DEC_GROUP blocks are merged by their last arrival,
@@ -873,15 +904,30 @@ q4_decode_k(const DecParams P) {
     float *rec1 = P.scratch + (unit * (size_t)(S + n_groups)) * HEADS * REC;
     float *rec2 = rec1 + (size_t)S * HEADS * REC;
     uint32_t *ctr = P.counters + unit * (1u + DEC_MAX_SPLIT / DEC_GROUP);
-    merge(sm, DEC_WARPS, false, rec1 + (size_t)split * HEADS * REC);
-    if (!arrive_last(ctr + 1 + grp, grp_size)) return;
-    if (n_groups == 1) {
-        merge(rec1, S, true, nullptr);
-        return;
+    /* one call site for every level keeps a single copy of the merge code in the kernel */
+    const float *src = sm;
+    uint32_t count = DEC_WARPS;
+    bool global = false;
+    float *dst = rec1 + (size_t)split * HEADS * REC;
+    uint32_t *arrive = ctr + 1 + grp;
+    uint32_t expected = grp_size;
+    for (int level = 0;; level++) {
+        merge_records<HD, HEADS>(src, count, global, dst, mo);
+        if (!dst) return;                                  /* finalised */
+        if (!arrive_last(arrive, expected)) return;        /* someone else carries on */
+        global = true;
+        if (level == 0) {
+            src = rec1 + (size_t)grp * DEC_GROUP * HEADS * REC;
+            count = grp_size;
+            dst = n_groups == 1 ? nullptr : rec2 + (size_t)grp * HEADS * REC;
+            arrive = ctr;
+            expected = n_groups;
+        } else {
+            src = rec2;
+            count = n_groups;
+            dst = nullptr;
+        }
     }
-    merge(rec1 + (size_t)grp * DEC_GROUP * HEADS * REC, grp_size, true, rec2 + (size_t)grp * HEADS * REC);
-    if (!arrive_last(ctr, n_groups)) return;
-    merge(rec2, n_groups, true, nullptr);
 }
 
 /* Merge of externally produced records (sequence-sharded decode): parts [n_parts][n_head][hd+2]
@@ -970,19 +1016,27 @@ bool q4i_decode(const Q4DecodeArgs &a) {
         /* one wave of 3 resident blocks per SM */
         const uint32_t target = (uint32_t)g_q4.sm_count * 3u;
         S = target / units;
+        /* dense scans of unequal length balance better with slices of ~64 steps */
+        if (!a.idx) S = S > (steps + 63u) / 64u ? S : (steps + 63u) / 64u;
         const uint32_t cap = (steps + DEC_WARPS - 1u) / DEC_WARPS;
         if (S > cap) S = cap;
     }
     if (S > DEC_MAX_SPLIT) S = DEC_MAX_SPLIT;
+    if (S > DEC_GROUP && S < 2 * DEC_GROUP) S = DEC_GROUP;   /* one merge level instead of two */
     if (S < 1) S = 1;
 
+    if (a.scratch_part && a.scratch_clamp) {
+        /* fixed-size caller scratch: fewer splits until the records fit */
+        while (S > 1 && (size_t)units * (S + (S + DEC_GROUP - 1u) / DEC_GROUP) * heads * (a.hd + 4) > a.scratch_part_floats)
+            S--;
+    }
     const uint32_t n_groups = (S + DEC_GROUP - 1u) / DEC_GROUP;
     const size_t need_part = (size_t)units * (S + n_groups) * heads * (a.hd + 4);
     const size_t need_ctr = (size_t)units * (1u + DEC_MAX_SPLIT / DEC_GROUP);
     float *scratch = a.scratch_part;
     uint32_t *counters = a.scratch_counters;
     if (scratch) {
-        if (a.scratch_part_floats < need_part || a.scratch_n_counters < need_ctr)
+        if ((S > 1 && a.scratch_part_floats < need_part) || a.scratch_n_counters < need_ctr)
             return q4i_fail(Q4E_SCRATCH, "decode: caller scratch too small");
     } else {
         if (!q4i_scratch(S > 1 ? need_part : 0, need_ctr)) return false;
@@ -1010,6 +1064,11 @@ bool q4i_decode(const Q4DecodeArgs &a) {
     p.kv_base = a.kv_base;
     p.scale_log2e = a.scale * 1.4426950408889634f;
     p.S = S;
+    {
+        static int dbg = -1;
+        if (dbg < 0) { const char *e = getenv("Q4_DEC_DEBUG"); dbg = e ? atoi(e) : 0; }
+        p.debug = (uint32_t)dbg;
+    }
     p.scratch = scratch;
     p.counters = counters;
     p.err = g_q4.err_d;
@@ -1030,3 +1089,4 @@ extern "C" bool q4_gpu_lse_merge(const float *parts, uint32_t n_parts, uint32_t 
     q4_lse_merge_k<<<n_head, 128, 0, g_q4.stream>>>(parts, n_parts, n_head, hd, gate, out);
     return q4i_check(cudaGetLastError(), "lse_merge launch");
 }
+

@@ -85,6 +85,7 @@ struct Q4DecodeArgs {
     float *scratch_part;
     uint32_t *scratch_counters;
     size_t scratch_part_floats, scratch_n_counters;
+    int scratch_clamp;           /* reduce the split count until the records fit the caller's scratch */
 };
 bool q4i_decode(const Q4DecodeArgs &a);
 
