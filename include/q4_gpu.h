@@ -190,6 +190,24 @@ bool q4_gpu_kv_restore(q4_gpu_kv *kv, uint32_t n_kv, const void *buf, int host);
 bool q4_gpu_kv_decode(const q4_gpu_kv *kv, uint32_t layer, const void *q, int q_bf16,
                       const float *gate, float *out, uint32_t n_head, const int32_t *idx,
                       uint32_t width, uint32_t idx_kvh_stride, uint32_t n_kv, float scale);
+/* ---- decode with no allocation at all.  Has no counterpart in the reference.  Same arguments and
+ * result as q4_gpu_kv_decode, for hosts that may not allocate device memory once they are running: an
+ * engine whose placement planner has already handed every byte of device memory to weights, expert
+ * slots and KV (a late cudaMalloc can fail, and it synchronises the device), or a serving loop that
+ * must never enter the allocator.  The split-KV records live in a 4 MB array inside the library
+ * image (held by every GPU that loads the library until the process exits), so:
+ *  - shapes are limited to 4 kv heads and 16 query heads per kv head; anything larger returns false
+ *    with status bit 8; the number of splits shrinks automatically until the records fit;
+ *  - the first call on a device looks up the array's device address (cudaGetSymbolAddress); make that
+ *    first call during start-up, before any stream capture is opened;
+ *  - every call shares the one array and keeps the previous call's contents: the arrival counters are
+ *    cleared on the stream before each launch, and two calls that overlap on the GPU (different
+ *    streams, or another process thread) race on it -- keep calls stream-ordered.
+ * Calls no cudaMalloc / cudaFree and no allocating library routine. */
+bool q4_gpu_kv_decode_noalloc(const q4_gpu_kv *kv, uint32_t layer, const void *q, int q_bf16,
+                              const float *gate, float *out, uint32_t n_head, const int32_t *idx,
+                              uint32_t width, uint32_t idx_kvh_stride, uint32_t n_kv, float scale);
+
 /* Same, but stops before normalisation: part[n_head][hd+2] = {m, l, acc[hd]} over this store's
  * rows, the record of src/q4_rocm.cu:6780,6957-6963 -- the payload exchanged between GPUs when one
  * sequence is sharded by position. */

@@ -1090,3 +1090,73 @@ extern "C" bool q4_gpu_lse_merge(const float *parts, uint32_t n_parts, uint32_t 
     return q4i_check(cudaGetLastError(), "lse_merge launch");
 }
 
+/* ---- decode without any allocation ------------------------------------------------------------
+ * Scratch for the split-KV records lives in the library image itself: every GPU that loads the
+ * library holds these 4 MB + 272 B until the process exits.  The names below are host-side stand-ins
+ * in host code; the device addresses come from cudaGetSymbolAddress, once per device. */
+constexpr size_t Q4_STATIC_PART_FLOATS = (size_t)1 << 20;   /* 4 MB of records */
+constexpr size_t Q4_STATIC_COUNTERS = 4 * (1 + DEC_MAX_SPLIT / DEC_GROUP);   /* up to 4 kv heads */
+static __device__ __align__(256) float q4_static_part[Q4_STATIC_PART_FLOATS];
+static __device__ __align__(256) uint32_t q4_static_counters[Q4_STATIC_COUNTERS];
+
+extern "C" bool q4_gpu_kv_decode_noalloc(const q4_gpu_kv *kv, uint32_t layer, const void *q, int q_bf16,
+                                         const float *gate, float *out, uint32_t n_head, const int32_t *idx,
+                                         uint32_t width, uint32_t idx_kvh_stride, uint32_t n_kv, float scale) {
+    if (!g_q4.ok) return q4i_fail(Q4E_INIT, "kv_decode_noalloc: library not initialised");
+    Q4_REQUIRE(kv && q && out && layer < kv->n_layers && n_head, "kv_decode_noalloc: bad argument");
+    Q4_REQUIRE(n_kv <= kv->max_kv, "kv_decode_noalloc: n_kv beyond max_kv");
+    if (kv->n_kvh > 4 || n_head % kv->n_kvh || n_head / kv->n_kvh > 16)
+        return q4i_fail(Q4E_SCRATCH, "kv_decode_noalloc: shape beyond the built-in scratch (at most 4 kv heads, "
+                                     "16 query heads per kv head)");
+    /* set-up, once per device, with that device current: resolve the arrays' device addresses */
+    static float *part_dev[64];
+    static uint32_t *ctr_dev[64];
+    int dev = -1;
+    if (!q4i_check(cudaGetDevice(&dev), "kv_decode_noalloc: cudaGetDevice")) return false;
+    if (dev < 0 || dev >= 64) return q4i_fail(Q4E_ARG, "kv_decode_noalloc: device index out of range");
+    if (!part_dev[dev]) {
+        float *p = nullptr;
+        uint32_t *c = nullptr;
+        if (!q4i_check(cudaGetSymbolAddress((void **)&p, q4_static_part), "kv_decode_noalloc: symbol address (records)"))
+            return false;
+        if (!q4i_check(cudaGetSymbolAddress((void **)&c, q4_static_counters), "kv_decode_noalloc: symbol address (counters)"))
+            return false;
+        part_dev[dev] = p;
+        ctr_dev[dev] = c;
+    }
+    /* the arrival counters must start at zero; the records need no clearing (every record that is
+     * read has been written by this launch) */
+    if (!q4i_check(cudaMemsetAsync(ctr_dev[dev], 0, Q4_STATIC_COUNTERS * sizeof(uint32_t), g_q4.stream),
+                   "kv_decode_noalloc: counter clear"))
+        return false;
+    Q4DecodeArgs a;
+    memset(&a, 0, sizeof(a));
+    a.one = kv->view;
+    a.layout = kv->kind == Q4K_Q8 ? LAY_Q8P : kv->kind == Q4K_F16 ? LAY_F16 : LAY_F32;
+    a.layer = layer;
+    a.n_units = 1;
+    a.n_head = n_head;
+    a.n_kvh = kv->n_kvh;
+    a.hd = kv->hd;
+    a.q = q;
+    a.q_bf16 = q_bf16;
+    a.gate = gate;
+    a.out = out;
+    a.idx = idx;
+    a.width = width;
+    a.idx_kvh_stride = idx_kvh_stride;
+    if (n_kv) {
+        a.kv_base = n_kv - 1;
+        a.hint_rows = n_kv;
+    } else {
+        a.pos = g_q4.pos_d;
+        a.hint_rows = kv->max_kv;
+    }
+    a.scale = scale;
+    a.scratch_part = part_dev[dev];
+    a.scratch_counters = ctr_dev[dev];
+    a.scratch_part_floats = Q4_STATIC_PART_FLOATS;
+    a.scratch_n_counters = Q4_STATIC_COUNTERS;
+    a.scratch_clamp = 1;
+    return q4i_decode(a);
+}

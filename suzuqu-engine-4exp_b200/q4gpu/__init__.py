@@ -54,6 +54,7 @@ SIGNATURES = {
     "q4_gpu_kv_snapshot_bytes": (_u64, [_v, _u32]),
     "q4_gpu_kv_save": (_b, [_v, _u32, _v, _i]), "q4_gpu_kv_restore": (_b, [_v, _u32, _v, _i]),
     "q4_gpu_kv_decode": (_b, [_v, _u32, _v, _i, _v, _v, _u32, _v, _u32, _u32, _u32, _f]),
+    "q4_gpu_kv_decode_noalloc": (_b, [_v, _u32, _v, _i, _v, _v, _u32, _v, _u32, _u32, _u32, _f]),
     "q4_gpu_kv_decode_partial": (_b, [_v, _u32, _v, _i, _v, _u32, _v, _u32, _u32, _u32, _f]),
     "q4_gpu_lse_merge": (_b, [_v, _u32, _u32, _u32, _v, _v]),
     "q4_gpu_kv_prefill": (_b, [_v, _u32, _v, _v, _v, _u32, _u32, _u32, _f]),
