@@ -91,9 +91,13 @@ __device__ __forceinline__ uint4 ldg128(const void *p) {
         : "l"(p));
     return v;
 }
-__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void *gsrc, uint32_t src_bytes) {
-    /* src_bytes = 0 writes 16 zero bytes (used for padding positions) */
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(src_bytes) : "memory");
+/* 16-byte asynchronous copy, or 16 zero bytes for a padding position.  The copy uses the plain form
+ * without a source-size operand so that neighbouring lanes coalesce into whole sectors. */
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void *gsrc, bool live) {
+    if (live)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
+    else
+        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(smem_dst), "r"(0u) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -564,14 +568,12 @@ q4_decode_k(const DecParams P) {
 #pragma unroll
                 for (uint32_t j = 0; j < 4; j++) {
                     const int32_t pr = __shfl_sync(0xffffffffu, p, 4 * j + (lane >> 3));
-                    const uint32_t bytes = pr >= 0 ? 16u : 0u;
                     const uint64_t off = (uint64_t)(uint32_t)max(pr, 0) * tok_stride + c8 * 16;
-                    cp_async16(st + koff[j], kbase + off, bytes);
-                    cp_async16(st + voff[j], vbase + off, bytes);
+                    cp_async16(st + koff[j], kbase + off, pr >= 0);
+                    cp_async16(st + voff[j], vbase + off, pr >= 0);
                 }
                 if (lane < 16) {
-                    cp_async16(st + 4096 + r16 * 16, sbase + (uint64_t)(uint32_t)max(p, 0) * s_tok_stride,
-                               p >= 0 ? 16u : 0u);
+                    cp_async16(st + 4096 + r16 * 16, sbase + (uint64_t)(uint32_t)max(p, 0) * s_tok_stride, p >= 0);
                     asm volatile("st.shared.s32 [%0], %1;" ::"r"(st + 4352 + r16 * 4), "r"(p) : "memory");
                 }
             }
@@ -1016,8 +1018,8 @@ bool q4i_decode(const Q4DecodeArgs &a) {
         /* one wave of 3 resident blocks per SM */
         const uint32_t target = (uint32_t)g_q4.sm_count * 3u;
         S = target / units;
-        /* dense scans of unequal length balance better with slices of ~64 steps */
-        if (!a.idx) S = S > (steps + 63u) / 64u ? S : (steps + 63u) / 64u;
+        /* several units of unequal length (dense batch): finer slices so the block scheduler can balance */
+        if (!a.idx && a.n_units > 1) S = S > (steps + 63u) / 64u ? S : (steps + 63u) / 64u;
         const uint32_t cap = (steps + DEC_WARPS - 1u) / DEC_WARPS;
         if (S > cap) S = cap;
     }
