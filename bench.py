@@ -348,6 +348,41 @@ def extras_single_session(torch, q4gpu, L, ext, peak_gbs):
     return res
 
 
+def extras_prefill(torch, q4gpu, L, ext, peaks):
+    """configs[2]: append 8192 new tokens (fp32 N(0,1), quantised to q8_0) into a 16384-token q8_0 cache, then
+    causal dense attention of the 8192 bf16 queries over all 24576 keys on the tensor cores, bf16 out"""
+    base, n_tok, n_layers = 16384, 8192, 4       # 4 layers rotate so Q/out (67 MB per layer) do not sit in L2
+    st = q4gpu.KVStore(n_layers, N_KVH, HD, base + n_tok, q4gpu.KIND_Q8)
+    q4gpu.use_torch_stream()
+    fill_store(torch, st, base)
+    knew = torch.randn(n_tok, KVW, device="cuda")
+    vnew = torch.randn(n_tok, KVW, device="cuda")
+    q = torch.randn(n_layers, n_tok, N_HEAD, HD, device="cuda").to(torch.bfloat16)
+    out = torch.empty(n_layers, n_tok, N_HEAD, HD, device="cuda", dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    L.q4_gpu_set_stream(None)
+
+    def app(i):
+        st.append(i % n_layers, knew, vnew, base, n_tok)
+
+    def att(i):
+        st.prefill(i % n_layers, q[i % n_layers], out[i % n_layers], N_HEAD, n_tok, base, SCALE)
+    timed(torch, ext, app, n_layers)
+    t_app = timed(torch, ext, app, 4 * n_layers) / (4 * n_layers)
+    timed(torch, ext, att, n_layers)
+    t_att = timed(torch, ext, att, 2 * n_layers) / (2 * n_layers)
+    pairs = sum(base + t + 1 for t in range(n_tok))
+    flop = pairs * 4 * HD * N_HEAD
+    peak_tf = float(peaks.get("bf16_tflops", 1590.0))
+    st.close()
+    return {"workload": "configs[2]: chunked prefill, 8192 new tokens over a 16384-token q8_0 cache, 16 Q / 2 KV heads, "
+                        "hd 128, bf16 Q and out",
+            "append_us": t_app * 1e6, "append_gbs": 2 * n_tok * (KVW * 4 + N_KVH * ROW_BYTES) / t_app / 1e9,
+            "attn_ms_per_layer": t_att * 1e3, "flop_per_layer": flop, "achieved_tflops": flop / t_att / 1e12,
+            "peak_tflops_measured_bf16": peak_tf, "frac_of_measured_tensor": flop / t_att / 1e12 / peak_tf,
+            "queries_per_s": n_tok / (t_app + t_att)}
+
+
 def extras_dense(torch, q4gpu, L, ext, peak_gbs, kinds=("q8_0", "f16", "f32")):
     """configs[4] on one GPU: full attention over 262144 rows, q8_0 / f16 / f32 KV, 12 layers"""
     ctx = 262144
@@ -450,7 +485,7 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--groups", type=int, default=0, help="replicas of the session group (0 = enough to defeat L2)")
     ap.add_argument("--ctx-max", type=int, default=131072, help="upper end of the context-length draw (profiling: small)")
-    ap.add_argument("--only", default="", choices=["", "single", "dense"],
+    ap.add_argument("--only", default="", choices=["", "single", "dense", "prefill"],
                     help="run just one of the ctx-262144 extras (for profiler captures)")
     ap.add_argument("--dense-kinds", default="q8_0,f16,f32")
     ap.add_argument("--mode", default="sessions", choices=["sessions", "seqshard"],
@@ -495,8 +530,12 @@ def main():
     if args.only:
         ext = torch.cuda.ExternalStream(L.q4_gpu_stream())
         torch.manual_seed(SEED)
-        res = (extras_single_session(torch, q4gpu, L, ext, peak_gbs) if args.only == "single"
-               else extras_dense(torch, q4gpu, L, ext, peak_gbs, args.dense_kinds.split(",")))
+        if args.only == "single":
+            res = extras_single_session(torch, q4gpu, L, ext, peak_gbs)
+        elif args.only == "prefill":
+            res = extras_prefill(torch, q4gpu, L, ext, peaks)
+        else:
+            res = extras_dense(torch, q4gpu, L, ext, peak_gbs, args.dense_kinds.split(","))
         print(json.dumps({"only": args.only, "result": res}), flush=True)
         return
     ctxs = draw_contexts(args.sessions, hi=args.ctx_max)
@@ -592,6 +631,7 @@ def main():
     if world == 1 and not args.no_extras:
         line["single_session_ctx262144"] = extras_single_session(torch, q4gpu, L, ext, peak_gbs)
         line["dense_ctx262144"] = extras_dense(torch, q4gpu, L, ext, peak_gbs)
+        line["prefill_8192_over_16384"] = extras_prefill(torch, q4gpu, L, ext, peaks)
         line["cpu_baseline"] = cpu_baseline(ctxs, args.cpu_seconds)
     print(json.dumps(line), flush=True)
     if dist is not None:
