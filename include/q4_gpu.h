@@ -11,7 +11,7 @@
  *     operate on caller-owned caches in the reference layout
  *     [token][kv_head][hd/32 x {fp16 scale, 32 x int8}] (q8_0), or fp16 / fp32 rows.
  *
- *  2. `q4_gpu_*` -- additive entry points: a library-owned KV store with a B200-native planar
+ *  2. `q4_gpu_*` -- additive entry points: a library-owned KV store with a B200-native record
  *     layout, fused K+V append, batched multi-session decode, bf16 queries, per-kv-head
  *     selection lists, partial (m, l, acc) output + merge for sequence-sharded decode,
  *     tensor-core prefill, and bulk prefix save/restore.
@@ -146,9 +146,10 @@ const int32_t *q4_gpu_pos_word(void);
 
 /* ---- KV store: allocator + layout (replaces q4_sess KV fields, kv_at, kv_token_bytes,
  * kv_write: src/q4_fwd.c:26-57,637-665,1944-1950; sizing q4_qsa_kv_bytes src/q4_place.c:92-105).
- * One store per session.  q8_0 layout, per layer and kv head: quants [max_kv][hd] int8 for K and
- * for V (one 128-byte line per row at hd 128) and one scale row [max_kv][2][hd/32] fp16 (K block
- * scales then V block scales; 16 bytes at hd 128).  fp16 / fp32 kinds: [max_kv][hd] rows. */
+ * One store per session.  q8_0 layout: one record per (layer, kv head, position) holding the K codes,
+ * the V codes, the K block scales and the V block scales (128 + 128 + 8 + 8 = 272 bytes at hd 128),
+ * so a gathered position is one contiguous, 16-byte aligned read.  fp16 / fp32 kinds: K and V planes
+ * of [layer][kv head][max_kv][hd] rows. */
 typedef struct q4_gpu_kv q4_gpu_kv;
 uint64_t q4_gpu_kv_bytes(uint32_t n_layers, uint32_t n_kvh, uint32_t hd, uint32_t max_kv, int kind);
 q4_gpu_kv *q4_gpu_kv_create(uint32_t n_layers, uint32_t n_kvh, uint32_t hd, uint32_t max_kv,

@@ -10,11 +10,12 @@
  * Shape of the kernel.  The path is bound by HBM, and with 8 query heads sharing each K/V byte the
  * scalar FMA pipe cannot keep up with B200's memory system (8 FMA per int8 byte at ~23 B/clk/SM
  * is more than the 128 FMA/clk an SM has), so the two contractions run on the tensor cores with
- * warp-level MMA.  Every byte of the cache is read from global memory once.  For the planar q8_0
- * store at hd 128 each warp owns a 3-stage ring in shared memory that it fills with 16-byte
- * cp.async copies (whole 128-byte rows, gathered by position) two steps ahead of the step it is
- * computing, so the gather latency of HBM is hidden behind the arithmetic without spending
- * registers; there is no block barrier in the main loop, warps stream independently.  The rings are
+ * warp-level MMA.  Every byte of the cache is read from global memory once.  For the native q8_0
+ * store at hd 128 each warp owns a 4-stage ring of 16-position tiles in shared memory that it fills
+ * with 16-byte cp.async copies (whole 128-byte rows, gathered by position); an iteration computes two
+ * tiles while the next two are in flight, so the gather latency of HBM is hidden behind the
+ * arithmetic without spending registers; there is no block barrier in the main loop, warps stream
+ * independently.  The rings are
  * swizzled so that the fragment reads are bank-conflict free.  The other layouts load fragments
  * straight into registers with sector-aligned 4/8/16-byte loads.
  *
@@ -29,10 +30,10 @@
  *   scales are folded into P^T per 32-wide block of hd.  Nothing is rounded except Q (to fp16 once)
  *   and the softmax weights (fp16, and the denominator sums the same rounded weights).
  *
- * grid = (splits, kv heads, units).  Every block reduces its warps' partials in shared memory; with
- * more than one split it writes an (m, l, acc) record to scratch and the last block to arrive
- * (atomic counter per unit and kv head) merges the records and writes the output, so the whole
- * layer is one launch.
+ * grid = (splits, kv heads, units).  Every block reduces its warps' partials in shared memory.  Up to
+ * 8 splits form one thread-block cluster and merge through distributed shared memory (no scratch, no
+ * atomics); more splits write (acc, m, l) records to scratch and the last block to arrive per group
+ * of 16 (atomic counter) merges them, two levels at most.  Either way the layer is one launch.
  */
 #include <cuda_bf16.h>
 #include <math_constants.h>
@@ -62,6 +63,7 @@ struct DecParams {
     uint32_t kv_base;
     float scale_log2e;
     uint32_t S;
+    uint32_t cluster; /* 1: the splits of a unit form one thread-block cluster and merge through DSMEM */
     uint32_t debug;   /* measurement aid: 1 = copy the tiles but skip the arithmetic */
     float *scratch;
     uint32_t *counters;
@@ -279,6 +281,78 @@ __device__ __noinline__ void merge_records(const float *recs, uint32_t count, bo
     __syncthreads();   /* s_w is reused by the next level */
 }
 
+/* ---- merge inside a thread-block cluster (distributed shared memory) -------------------------- */
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t saddr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float ld_cluster(uint32_t a) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(a) : "memory");
+    return v;
+}
+/* When the splits of a unit are the blocks of one cluster (at most 8), every block leaves its record
+ * in its own shared memory and block r merges heads r, r+S, .. by reading all S records through
+ * distributed shared memory: no scratch, no atomics, no global round trips.  Called between two
+ * cluster barriers (records complete before, nobody exits while peers still read after). */
+template <int HD, int HEADS>
+__device__ __noinline__ void cluster_merge(uint32_t rec_saddr, uint32_t S, uint32_t rank, const MergeOut mo) {
+    constexpr int REC = HD + 4;
+    for (uint32_t h = rank; h < mo.gqa; h += S) {
+        float m[8], l[8];
+        float M = -CUDART_INF_F;
+#pragma unroll
+        for (uint32_t s = 0; s < 8; s++) {
+            m[s] = -CUDART_INF_F;
+            l[s] = 0.f;
+            if (s < S) {
+                const uint32_t b = map_to_rank(rec_saddr + (h * REC + HD) * 4, s);
+                m[s] = ld_cluster(b);
+                l[s] = ld_cluster(b + 4);
+            }
+            M = fmaxf(M, m[s]);
+        }
+        const float Mu = M == -CUDART_INF_F ? 0.f : M;
+        float L = 0.f;
+#pragma unroll
+        for (uint32_t s = 0; s < 8; s++) {
+            m[s] = ex2(m[s] - Mu);
+            L = fmaf(m[s], l[s], L);
+        }
+        for (uint32_t d = threadIdx.x; d < (uint32_t)HD; d += DEC_THREADS) {
+            float a[8];
+#pragma unroll
+            for (uint32_t s = 0; s < 8; s++)
+                a[s] = s < S ? ld_cluster(map_to_rank(rec_saddr + (h * REC + d) * 4, s)) : 0.f;
+            float A = 0.f;
+#pragma unroll
+            for (uint32_t s = 0; s < 8; s++) A = fmaf(m[s], a[s], A);
+            if (mo.part_out) {
+                float *pr = mo.part_out + (mo.row0 + h) * (HD + 2);
+                if (d == 0) {
+                    pr[0] = L > 0.f ? M * 0.6931471805599453f : 0.f;
+                    pr[1] = L;
+                }
+                pr[2 + d] = A;
+            } else {
+                float o = L > 0.f ? A / L : 0.f;
+                const size_t off = (mo.row0 + h) * HD + d;
+                if (mo.gate) o *= 1.f / (1.f + __expf(-mo.gate[off]));
+                mo.out[off] = o;
+            }
+        }
+    }
+}
+
 /* ---- the kernel ---------------------------------------------------------------------------- */
 constexpr int RING_STAGES = 4;
 constexpr int RING_STAGE_BYTES = 2048 + 2048 + 256 + 64;   /* K rows, V rows, scale rows, positions */
@@ -290,7 +364,8 @@ struct DecCfg {
     static constexpr int REC = HD + 4;          /* acc[HD], m, l, 2 pad: 16-byte aligned records */
     static constexpr size_t EPI_BYTES = (size_t)DEC_WARPS * HEADS * REC * sizeof(float);
     static constexpr size_t RING_BYTES = STAGED ? (size_t)DEC_WARPS * RING_STAGES * RING_STAGE_BYTES : 0;
-    static constexpr size_t SMEM = EPI_BYTES > RING_BYTES ? EPI_BYTES : RING_BYTES;
+    static constexpr size_t REC_BYTES = (size_t)HEADS * REC * sizeof(float);   /* the block's merged record */
+    static constexpr size_t SMEM = EPI_BYTES + REC_BYTES > RING_BYTES ? EPI_BYTES + REC_BYTES : RING_BYTES;
     static constexpr int MIN_BLOCKS = STAGED ? (NHT == 1 ? 3 : 2) : (HD * NHT <= 128 ? 3 : 1);
 };
 
@@ -531,7 +606,7 @@ q4_decode_k(const DecParams P) {
     };
 
     if constexpr (Cfg::STAGED) {
-        /* ---- planar q8_0, hd 128: per-warp cp.async ring of 16-position stages; an iteration consumes
+        /* ---- native q8_0 store, hd 128: per-warp cp.async ring of 16-position stages; an iteration consumes
          * two stages (32 positions, two independent MMA chains) while the next two are in flight.
          * Lanes 0-15 hold a stage's positions and copy its 16-byte scale rows; the K and V rows are
          * copied 4 rows per instruction (8 lanes x 16 bytes = one 128-byte line per row).  16-byte chunk
@@ -898,6 +973,14 @@ q4_decode_k(const DecParams P) {
         merge_records<HD, HEADS>(sm, DEC_WARPS, false, nullptr, mo);
         return;
     }
+    if (P.cluster) {
+        float *own = reinterpret_cast<float *>(smem_raw + Cfg::EPI_BYTES);
+        merge_records<HD, HEADS>(sm, DEC_WARPS, false, own, mo);
+        cluster_sync_all();
+        cluster_merge<HD, HEADS>((uint32_t)__cvta_generic_to_shared(own), S, cluster_ctarank(), mo);
+        cluster_sync_all();
+        return;
+    }
     /* level 1: record per block; groups of DEC_GROUP blocks are merged by their last arrival,
      * level 2: the group records are merged by the last group to finish. */
     const uint32_t n_groups = (S + DEC_GROUP - 1u) / DEC_GROUP;
@@ -970,6 +1053,22 @@ bool launch(const DecParams &p, dim3 grid) {
             return false;
     }
     attr_done = true;
+    if (p.cluster) {
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(DEC_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = g_q4.stream;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = grid.x;
+        at[0].val.clusterDim.y = 1;
+        at[0].val.clusterDim.z = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        return q4i_check(cudaLaunchKernelEx(&cfg, q4_decode_k<LAY, HD, NHT>, p), "decode cluster launch");
+    }
     q4_decode_k<LAY, HD, NHT><<<grid, DEC_THREADS, smem, g_q4.stream>>>(p);
     return q4i_check(cudaGetLastError(), "decode launch");
 }
@@ -1026,6 +1125,18 @@ bool q4i_decode(const Q4DecodeArgs &a) {
     if (S > DEC_MAX_SPLIT) S = DEC_MAX_SPLIT;
     if (S > DEC_GROUP && S < 2 * DEC_GROUP) S = DEC_GROUP;   /* one merge level instead of two */
     if (S < 1) S = 1;
+    /* Short lists (a few hundred tiles per unit) are bound by the latency of the merge, not by bandwidth:
+     * at most 8 splits, launched as one cluster per unit, merge through distributed shared memory. */
+    static int use_cluster = -1;
+    if (use_cluster < 0) {
+        const char *e = getenv("Q4_DEC_CLUSTER");
+        use_cluster = e ? atoi(e) : 1;
+    }
+    bool cluster = false;
+    if (use_cluster && !a.scratch_part && (S <= 8 || steps <= 512)) {
+        if (S > 8) S = 8;
+        cluster = S > 1;
+    }
 
     if (a.scratch_part && a.scratch_clamp) {
         /* fixed-size caller scratch: fewer splits until the records fit */
@@ -1041,7 +1152,7 @@ bool q4i_decode(const Q4DecodeArgs &a) {
         if ((S > 1 && a.scratch_part_floats < need_part) || a.scratch_n_counters < need_ctr)
             return q4i_fail(Q4E_SCRATCH, "decode: caller scratch too small");
     } else {
-        if (!q4i_scratch(S > 1 ? need_part : 0, need_ctr)) return false;
+        if (!q4i_scratch(S > 1 && !cluster ? need_part : 0, need_ctr)) return false;
         scratch = g_q4.part;
         counters = g_q4.counters;
     }
@@ -1066,6 +1177,7 @@ bool q4i_decode(const Q4DecodeArgs &a) {
     p.kv_base = a.kv_base;
     p.scale_log2e = a.scale * 1.4426950408889634f;
     p.S = S;
+    p.cluster = cluster ? 1u : 0u;
     {
         static int dbg = -1;
         if (dbg < 0) { const char *e = getenv("Q4_DEC_DEBUG"); dbg = e ? atoi(e) : 0; }

@@ -11,14 +11,14 @@
 
 /* KV kinds of the public ABI, plus the two q8_0 layouts the kernels distinguish. */
 enum { Q4K_F32 = 0, Q4K_F16 = 1, Q4K_Q8 = 2 };
-enum { LAY_F32 = 0, LAY_F16 = 1, LAY_Q8P = 2 /* planar store */, LAY_Q8R = 3 /* reference 34-byte blocks */ };
+enum { LAY_F32 = 0, LAY_F16 = 1, LAY_Q8P = 2 /* native store: 16-byte aligned records */, LAY_Q8R = 3 /* reference 34-byte blocks */ };
 
 enum {
     Q4E_ARG = 1, Q4E_CUDA = 2, Q4E_RANGE = 4, Q4E_SCRATCH = 8, Q4E_INIT = 16,
 };
 
 /* One cache as the kernels see it.  Row (layer, kv head kh, token p) of the K plane lives at
- * k + layer*layer_stride + kh*kvh_stride + p*tok_stride (same for v); for the planar q8_0 store the
+ * k + layer*layer_stride + kh*kvh_stride + p*tok_stride (same for v); for the native q8_0 store the
  * scale row is at s + layer*s_layer_stride + kh*s_kvh_stride + p*s_tok_stride and holds the K block
  * scales followed by the V block scales (fp16). */
 struct Q4Cache {
@@ -33,6 +33,7 @@ struct q4_gpu_kv {
     int kind;
     uint8_t *k, *v, *s;          /* device planes (s only for q8_0) */
     uint64_t plane_bytes, s_bytes;
+    uint32_t rec_bytes;          /* bytes per (kv head, position): q8_0 record, or fp16 / fp32 row */
     Q4Cache view;                /* host copy of the kernel view */
     Q4Cache *d_view;             /* same, in device memory (for batched launches) */
 };

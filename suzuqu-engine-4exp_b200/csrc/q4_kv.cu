@@ -1,5 +1,5 @@
 /*
- * KV store (allocator + planar layout), the fused K/V append with q8_0 quantisation, conversion
+ * KV store (allocator + record layout), the fused K/V append with q8_0 quantisation, conversion
  * to / from the reference layout, bulk prefix save / restore, and the host entry points of the
  * decode attention (reference ABI and store-based).
  *
@@ -168,8 +168,9 @@ __global__ void q4_relayout_k(Q4Cache C, uint32_t layer, int which, uint32_t n_k
     }
 }
 
+inline uint32_t q8_record_bytes(uint32_t hd) { return (2u * hd + hd / 8u + 15u) & ~15u; }   /* 272 at hd 128 */
 inline uint32_t row_bytes(uint32_t hd, int kind) {
-    return kind == Q4K_Q8 ? hd : hd * (kind == Q4K_F16 ? 2u : 4u);   /* planar store: codes only */
+    return kind == Q4K_Q8 ? hd : hd * (kind == Q4K_F16 ? 2u : 4u);   /* q8_0: the code part of a record */
 }
 inline int store_layout(int kind) { return kind == Q4K_Q8 ? LAY_Q8P : kind == Q4K_F16 ? LAY_F16 : LAY_F32; }
 inline bool hd_ok(uint32_t hd) { return hd == 32 || hd == 64 || hd == 128 || hd == 256; }
@@ -297,7 +298,7 @@ extern "C" bool q4_hip_qsa_decode_idx(const float *d_q, const void *d_kcache, co
 /* ======================================================================= KV store ========== */
 
 extern "C" uint64_t q4_gpu_kv_bytes(uint32_t n_layers, uint32_t n_kvh, uint32_t hd, uint32_t max_kv, int kind) {
-    /* K+V: same total as q4_qsa_kv_bytes (src/q4_place.c:92-105); the planar split moves bytes, it
+    /* K+V: same total as q4_qsa_kv_bytes (src/q4_place.c:92-105); the record layout regroups bytes, it
      * does not add any: hd codes + hd/32 fp16 scales per row = (hd/32)*34. */
     if (kind == Q4K_Q8) return (uint64_t)n_layers * max_kv * 2ull * n_kvh * (hd / 32u) * 34u;
     return (uint64_t)n_layers * max_kv * 2ull * n_kvh * hd * (kind == Q4K_F16 ? 2u : 4u);
@@ -312,11 +313,20 @@ extern "C" q4_gpu_kv *q4_gpu_kv_create(uint32_t n_layers, uint32_t n_kvh, uint32
     q4_gpu_kv *kv = (q4_gpu_kv *)calloc(1, sizeof(q4_gpu_kv));
     if (!kv) return nullptr;
     kv->n_layers = n_layers; kv->n_kvh = n_kvh; kv->hd = hd; kv->max_kv = max_kv; kv->kind = kind;
-    const uint32_t rb = row_bytes(hd, kind);
+    /* q8_0: one record per (kv head, position) = K codes | V codes | K scales | V scales, so a gathered
+     * position is one contiguous 272-byte read (hd 128) instead of three scattered ones.  fp16 / fp32:
+     * a K plane and a V plane of [kv head][position][hd] rows. */
+    const uint32_t rb = kind == Q4K_Q8 ? q8_record_bytes(hd) : row_bytes(hd, kind);
+    kv->rec_bytes = rb;
     kv->plane_bytes = (uint64_t)n_layers * n_kvh * max_kv * rb;
-    kv->s_bytes = kind == Q4K_Q8 ? (uint64_t)n_layers * n_kvh * max_kv * (hd / 32u) * 4u : 0;
-    bool ok = cudaMalloc(&kv->k, kv->plane_bytes) == cudaSuccess && cudaMalloc(&kv->v, kv->plane_bytes) == cudaSuccess;
-    if (ok && kv->s_bytes) ok = cudaMalloc(&kv->s, kv->s_bytes) == cudaSuccess;
+    kv->s_bytes = 0;
+    bool ok = cudaMalloc(&kv->k, kv->plane_bytes) == cudaSuccess;
+    if (ok && kind == Q4K_Q8) {
+        kv->v = kv->k + hd;
+        kv->s = kv->k + 2 * hd;
+    } else if (ok) {
+        ok = cudaMalloc(&kv->v, kv->plane_bytes) == cudaSuccess;
+    }
     if (ok) ok = cudaMalloc(&kv->d_view, sizeof(Q4Cache)) == cudaSuccess;
     if (!ok) {
         (void)cudaGetLastError();
@@ -329,9 +339,9 @@ extern "C" q4_gpu_kv *q4_gpu_kv_create(uint32_t n_layers, uint32_t n_kvh, uint32
     c.tok_stride = rb;
     c.kvh_stride = (uint64_t)max_kv * rb;
     c.layer_stride = (uint64_t)n_kvh * max_kv * rb;
-    c.s_tok_stride = (hd / 32u) * 4u;
-    c.s_kvh_stride = (uint64_t)max_kv * c.s_tok_stride;
-    c.s_layer_stride = (uint64_t)n_kvh * c.s_kvh_stride;
+    c.s_tok_stride = rb;                      /* the scales ride in the same record */
+    c.s_kvh_stride = c.kvh_stride;
+    c.s_layer_stride = c.layer_stride;
     c.max_kv = max_kv;
     if (cudaMemcpy(kv->d_view, &c, sizeof(c), cudaMemcpyHostToDevice) != cudaSuccess) {
         q4i_fail(Q4E_CUDA, "kv_create: view upload failed");
@@ -343,8 +353,7 @@ extern "C" q4_gpu_kv *q4_gpu_kv_create(uint32_t n_layers, uint32_t n_kvh, uint32
 extern "C" void q4_gpu_kv_destroy(q4_gpu_kv *kv) {
     if (!kv) return;
     if (kv->k) cudaFree(kv->k);
-    if (kv->v) cudaFree(kv->v);
-    if (kv->s) cudaFree(kv->s);
+    if (kv->v && kv->kind != Q4K_Q8) cudaFree(kv->v);   /* q8_0: v and s point into the k allocation */
     if (kv->d_view) cudaFree(kv->d_view);
     free(kv);
 }
@@ -397,22 +406,22 @@ extern "C" bool q4_gpu_kv_import(q4_gpu_kv *kv, uint32_t layer, int which, uint3
     return relayout<false>(kv, layer, which, tok0, n_tok, const_cast<void *>(src));
 }
 
-/* Prefix snapshot = rows [0, n_kv) of every (layer, kv head) of the K plane, then of the V plane,
- * then of the scale plane: three strided bulk copies (pitch = max_kv rows, width = n_kv rows). */
+/* Prefix snapshot = records [0, n_kv) of every (layer, kv head): one strided bulk copy for q8_0 (two
+ * for the fp16 / fp32 kinds' K and V planes); pitch = max_kv rows, width = n_kv rows. */
 extern "C" uint64_t q4_gpu_kv_snapshot_bytes(const q4_gpu_kv *kv, uint32_t n_kv) {
     if (!kv) return 0;
     const uint64_t rows = (uint64_t)kv->n_layers * kv->n_kvh * n_kv;
-    return rows * (2ull * row_bytes(kv->hd, kv->kind) + (kv->kind == Q4K_Q8 ? (kv->hd / 32u) * 4u : 0u));
+    return rows * (kv->kind == Q4K_Q8 ? (uint64_t)kv->rec_bytes : 2ull * row_bytes(kv->hd, kv->kind));
 }
 static bool snapshot(const q4_gpu_kv *kv, uint32_t n_kv, void *buf, int host, bool save) {
     if (!g_q4.ok) return q4i_fail(Q4E_INIT, "kv snapshot: library not initialised");
     Q4_REQUIRE(kv && buf && n_kv && n_kv <= kv->max_kv, "kv snapshot: bad argument");
     const size_t height = (size_t)kv->n_layers * kv->n_kvh;
-    const uint32_t rb = row_bytes(kv->hd, kv->kind), sb = (kv->hd / 32u) * 4u;
+    const uint32_t rb = kv->rec_bytes;
     uint8_t *b = (uint8_t *)buf;
     const cudaMemcpyKind kind = !host ? cudaMemcpyDeviceToDevice : save ? cudaMemcpyDeviceToHost : cudaMemcpyHostToDevice;
-    struct { uint8_t *plane; uint32_t row; } pl[3] = {{kv->k, rb}, {kv->v, rb}, {kv->s, sb}};
-    for (int i = 0; i < (kv->kind == Q4K_Q8 ? 3 : 2); i++) {
+    struct { uint8_t *plane; uint32_t row; } pl[2] = {{kv->k, rb}, {kv->v, rb}};
+    for (int i = 0; i < (kv->kind == Q4K_Q8 ? 1 : 2); i++) {
         const size_t width = (size_t)n_kv * pl[i].row, pitch = (size_t)kv->max_kv * pl[i].row;
         cudaError_t e = save ? cudaMemcpy2DAsync(b, width, pl[i].plane, pitch, width, height, kind, g_q4.stream)
                              : cudaMemcpy2DAsync(pl[i].plane, pitch, b, width, width, height, kind, g_q4.stream);

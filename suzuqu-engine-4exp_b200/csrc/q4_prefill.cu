@@ -1,5 +1,5 @@
 /*
- * Dense causal prefill attention over the planar q8_0 store on the 5th-generation tensor cores
+ * Dense causal prefill attention over the native q8_0 store on the 5th-generation tensor cores
  * (tcgen05.mma, accumulators in tensor memory).  Query t of the chunk attends rows
  * [0, min(kv_base + t + 1, max_kv)) -- the semantics of gqa_prefill_k (src/q4_rocm.cu:7019-7206) as
  * launched by q4_hip_qsa_decode_n with n_tok > 1 (:7263,7286-7298); the reference computes it with
