@@ -163,6 +163,15 @@ bool q4_gpu_kv_append(q4_gpu_kv *kv, uint32_t layer, const float *k, const float
 /* Same for one token at the slot held in the device position word (replaces q4_hip_kv_append_d,
  * src/q4_fwd.c:891). */
 bool q4_gpu_kv_append_d(q4_gpu_kv *kv, uint32_t layer, const float *k, const float *v);
+/* K prep fused into the append: RMSNorm (optional weight) + interleaved-pair RoPE of the raw K rows,
+ * then quantise / convert K and V and scatter them, one launch.  Replaces q4_hip_qsa_k_prep_{n,d}
+ * followed by the append (src/q4_fwd.c:884,891 decode; :1734,1738-1741 prefill); the cache bytes are
+ * those of that two-launch sequence.  k_raw, v: [n_tok][n_kvh*hd] fp32; k_raw is not modified. */
+bool q4_gpu_kv_prep_append(q4_gpu_kv *kv, uint32_t layer, const float *k_raw, const float *v,
+                           const float *k_norm_w, uint32_t n_rot, float rope_base, float eps,
+                           uint32_t pos0, uint32_t n_tok);
+bool q4_gpu_kv_prep_append_d(q4_gpu_kv *kv, uint32_t layer, const float *k_raw, const float *v,
+                             const float *k_norm_w, uint32_t n_rot, float rope_base, float eps);
 /* Rows [tok0, tok0+n_tok) of one layer's K (which = 0) or V (1) cache to / from the reference
  * layout (n_tok * kv_token_bytes device bytes) -- what q4_sess_save writes per layer,
  * src/q4_fwd.c:2353-2360. */
@@ -176,6 +185,14 @@ bool q4_gpu_kv_import(q4_gpu_kv *kv, uint32_t layer, int which, uint32_t tok0, u
 uint64_t q4_gpu_kv_snapshot_bytes(const q4_gpu_kv *kv, uint32_t n_kv);
 bool q4_gpu_kv_save(const q4_gpu_kv *kv, uint32_t n_kv, void *buf, int host);
 bool q4_gpu_kv_restore(q4_gpu_kv *kv, uint32_t n_kv, const void *buf, int host);
+
+/* The KV section of the reference's session file, streamed to / from a file descriptor positioned by
+ * the caller: for every layer the K rows [0, n_kv) then the V rows, in the reference layout
+ * (src/q4_fwd.c:2353-2360 save, :2437-2445 restore; the header, ids and the other state stay with the
+ * host).  Conversion on the device, double-buffered pinned staging.  Blocking; returns false on a
+ * short file or I/O error. */
+bool q4_gpu_kv_write_fd(const q4_gpu_kv *kv, uint32_t n_kv, int fd);
+bool q4_gpu_kv_read_fd(q4_gpu_kv *kv, uint32_t n_kv, int fd);
 
 /* ---- decode attention over a store.  One launch covers every kv head and query head of the
  * layer (split-KV over the position list, merged by the last block to finish).

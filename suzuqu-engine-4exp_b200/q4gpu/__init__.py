@@ -49,10 +49,13 @@ SIGNATURES = {
     "q4_gpu_kv_create": (_v, [_u32, _u32, _u32, _u32, _i]), "q4_gpu_kv_destroy": (None, [_v]),
     "q4_gpu_kv_append": (_b, [_v, _u32, _v, _v, _u32, _u32]),
     "q4_gpu_kv_append_d": (_b, [_v, _u32, _v, _v]),
+    "q4_gpu_kv_prep_append": (_b, [_v, _u32, _v, _v, _v, _u32, _f, _f, _u32, _u32]),
+    "q4_gpu_kv_prep_append_d": (_b, [_v, _u32, _v, _v, _v, _u32, _f, _f]),
     "q4_gpu_kv_export": (_b, [_v, _u32, _i, _u32, _u32, _v]),
     "q4_gpu_kv_import": (_b, [_v, _u32, _i, _u32, _u32, _v]),
     "q4_gpu_kv_snapshot_bytes": (_u64, [_v, _u32]),
     "q4_gpu_kv_save": (_b, [_v, _u32, _v, _i]), "q4_gpu_kv_restore": (_b, [_v, _u32, _v, _i]),
+    "q4_gpu_kv_write_fd": (_b, [_v, _u32, _i]), "q4_gpu_kv_read_fd": (_b, [_v, _u32, _i]),
     "q4_gpu_kv_decode": (_b, [_v, _u32, _v, _i, _v, _v, _u32, _v, _u32, _u32, _u32, _f]),
     "q4_gpu_kv_decode_noalloc": (_b, [_v, _u32, _v, _i, _v, _v, _u32, _v, _u32, _u32, _u32, _f]),
     "q4_gpu_kv_decode_partial": (_b, [_v, _u32, _v, _i, _v, _u32, _v, _u32, _u32, _u32, _f]),
@@ -166,6 +169,12 @@ class KVStore:
 
     def restore(self, n_kv, buf, host=False):
         check(self.L.q4_gpu_kv_restore(self.h, n_kv, _ptr(buf), int(host)), "q4_gpu_kv_restore")
+
+    def write_fd(self, n_kv, fd):
+        check(self.L.q4_gpu_kv_write_fd(self.h, n_kv, fd), "q4_gpu_kv_write_fd")
+
+    def read_fd(self, n_kv, fd):
+        check(self.L.q4_gpu_kv_read_fd(self.h, n_kv, fd), "q4_gpu_kv_read_fd")
 
     def decode(self, layer, q, out, n_head, scale, gate=None, idx=None, width=0, idx_kvh_stride=0,
                n_kv=0, q_bf16=False):

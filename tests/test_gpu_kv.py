@@ -233,3 +233,90 @@ def test_prep_kernels(oracle):
     dk2 = dev(kk[:n_kvh * hd])
     assert L.q4_hip_qsa_k_prep_d(dk2.data_ptr(), dev(wk).data_ptr(), n_kvh, hd, n_rot, base, eps)
     assert np.array_equal(host(dk2), host(dk)[:n_kvh * hd])
+
+
+@pytest.mark.parametrize("kind", [2, 1])
+def test_session_file_kv_section(oracle, kind, tmp_path):
+    """q4_gpu_kv_write_fd writes exactly the KV section of the reference's session file: per layer the
+    K rows then the V rows in the reference layout (src/q4_fwd.c:2353-2360); read_fd restores it; a
+    truncated file is refused."""
+    import os
+    L = lib()
+    n_layers, n_kvh, hd, max_kv, n = 3, 2, 128, 400, 333
+    kvw = n_kvh * hd
+    st = q4gpu.KVStore(n_layers, n_kvh, hd, max_kv, kind)
+    want = b""
+    for layer in range(n_layers):
+        k = oracle.normal(90, layer, n * kvw).reshape(n, kvw)
+        v = oracle.normal(91, layer, n * kvw).reshape(n, kvw)
+        st.append(layer, dev(k), dev(v), 0, n)
+        want += oracle.kv_write(k, kind).tobytes() + oracle.kv_write(v, kind).tobytes()
+    path = str(tmp_path / "kv.bin")
+    fd = os.open(path, os.O_CREAT | os.O_WRONLY | os.O_TRUNC, 0o600)
+    os.write(fd, b"HDR!")                      # the caller positions the descriptor (header, ids, ...)
+    st.write_fd(n, fd)
+    os.close(fd)
+    data = open(path, "rb").read()
+    assert data[:4] == b"HDR!" and data[4:] == want
+    other = q4gpu.KVStore(n_layers, n_kvh, hd, max_kv, kind)
+    fd = os.open(path, os.O_RDONLY)
+    os.lseek(fd, 4, os.SEEK_SET)
+    other.read_fd(n, fd)
+    os.close(fd)
+    tb = st.token_bytes
+    for layer in range(n_layers):
+        for which in (0, 1):
+            a = torch.empty(n * tb, dtype=torch.uint8, device="cuda")
+            b = torch.empty_like(a)
+            st.export(layer, which, 0, n, a)
+            other.export(layer, which, 0, n, b)
+            assert torch.equal(a, b)
+    with open(path, "r+b") as f:
+        f.truncate(len(data) - 100)
+    fd = os.open(path, os.O_RDONLY)
+    os.lseek(fd, 4, os.SEEK_SET)
+    assert not L.q4_gpu_kv_read_fd(other.h, n, fd)
+    os.close(fd)
+    L.q4_gpu_last_error()
+    st.close()
+    other.close()
+
+
+@pytest.mark.parametrize("kind,hd,n_rot", [(2, 128, 128), (2, 256, 64), (1, 128, 64), (0, 64, 64)])
+def test_fused_prep_append_equals_two_launches(oracle, kind, hd, n_rot):
+    """RMSNorm + RoPE + quantise + scatter in one launch == q4_hip_qsa_k_prep_n followed by the append,
+    byte for byte; and within the documented libm tolerance of the oracle's prep before quantisation."""
+    L = lib()
+    n_kvh, n_tok, pos0, base, eps = 2, 37, 1000, 1e7, 1e-6
+    kvw = n_kvh * hd
+    k = oracle.normal(95, hd, n_tok * kvw)
+    v = oracle.normal(96, hd, n_tok * kvw)
+    w = (1 + 0.1 * oracle.normal(97, hd, hd)).astype(np.float32)
+    a = q4gpu.KVStore(1, n_kvh, hd, 1100, kind)
+    b = q4gpu.KVStore(1, n_kvh, hd, 1100, kind)
+    dk, dv, dw = dev(k), dev(v), dev(w)
+    assert L.q4_gpu_kv_prep_append(a.h, 0, dk.data_ptr(), dv.data_ptr(), dw.data_ptr(), n_rot, base, eps, pos0, n_tok)
+    assert np.array_equal(host(dk), k)                      # the raw rows are left alone
+    dk2 = dev(k)
+    assert L.q4_hip_qsa_k_prep_n(dk2.data_ptr(), dw.data_ptr(), n_kvh, hd, n_rot, pos0, base, eps, n_tok)
+    b.append(0, dk2, dv, pos0, n_tok)
+    tb = a.token_bytes
+    for which in (0, 1):
+        xa = torch.empty(n_tok * tb, dtype=torch.uint8, device="cuda")
+        xb = torch.empty_like(xa)
+        a.export(0, which, pos0, n_tok, xa)
+        b.export(0, which, pos0, n_tok, xb)
+        assert torch.equal(xa, xb), which
+    # device-position variant writes the same bytes at the position word
+    c = q4gpu.KVStore(1, n_kvh, hd, 1100, kind)
+    L.q4_hip_pos_push(pos0 + 5)
+    assert L.q4_gpu_kv_prep_append_d(c.h, 0, dk.data_ptr() + 5 * kvw * 4, dv.data_ptr() + 5 * kvw * 4, dw.data_ptr(),
+                                     n_rot, base, eps)
+    for which in (0, 1):
+        xa = torch.empty(tb, dtype=torch.uint8, device="cuda")
+        xc = torch.empty_like(xa)
+        a.export(0, which, pos0 + 5, 1, xa)
+        c.export(0, which, pos0 + 5, 1, xc)
+        assert torch.equal(xa, xc)
+    for s in (a, b, c):
+        s.close()
