@@ -71,8 +71,42 @@ def gathered_bytes(ctx):
 
 
 class ClockSampler:
-    def __init__(self, gpu_index):
-        self.proc = None
+    """SM clock and throttle reasons while the timed steps run.  Reads NVML in a thread every ~2 ms (the
+    timed region of a default run lasts tens of milliseconds, shorter than one nvidia-smi poll); falls
+    back to an `nvidia-smi -lms` child when NVML cannot be opened.  Read-only: no setting is touched."""
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+
+    def __init__(self, gpu_index, uuid=None):
+        self.samples = []          # (t, sm_mhz, reasons bitmask)
+        self.sm_max = None
+        self.thread = self.proc = None
+        self.stop_flag = False
+        try:
+            import pynvml as nv
+            import threading
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByUUID(uuid) if uuid else nv.nvmlDeviceGetHandleByIndex(gpu_index)
+            self.sm_max = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            bits = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown,
+                    "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+                    "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown,
+                    "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
+            self.bits = bits
+
+            def poll():
+                while not self.stop_flag:
+                    try:
+                        self.samples.append((time.perf_counter(),
+                                             float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)),
+                                             int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))))
+                    except Exception:
+                        pass
+                    time.sleep(0.002)
+            self.thread = threading.Thread(target=poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         self.path = "/tmp/q4_bench_clocks_%d.csv" % os.getpid()
         q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -85,8 +119,26 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
-    def stop(self):
+    def stop(self, windows=()):
+        """windows: (t0, t1) host-clock intervals of the timed regions; samples outside them are used only
+        when fewer than three fall inside (then "window" says so)."""
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.thread:
+            self.stop_flag = True
+            self.thread.join(timeout=2)
+            inside = [s for s in self.samples if any(a <= s[0] <= b for a, b in windows)]
+            use, out["window"] = (inside, "timed regions") if len(inside) >= 3 else \
+                                 (self.samples, "warm-up through the last timed step")
+            if use:
+                out["sm_mhz"] = float(np.median([s[1] for s in use]))
+                out["sm_max_mhz"] = self.sm_max
+                out["samples"] = len(use)
+                mask = 0
+                for s in use:
+                    mask |= s[2]
+                out["reasons"] = sorted(n for n, bit in self.bits.items() if mask & bit)
+            out["source"] = "nvml"
+            return out
         if not self.proc:
             return out
         self.proc.terminate()
@@ -96,7 +148,6 @@ class ClockSampler:
             self.proc.kill()
         self.f.close()
         sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in open(self.path):
             parts = [x.strip() for x in line.split(",")]
             if len(parts) < 7:
@@ -106,7 +157,7 @@ class ClockSampler:
                 mx.append(float(parts[1]))
             except ValueError:
                 continue
-            for nm, v in zip(names, parts[3:7]):
+            for nm, v in zip(self.NAMES, parts[3:7]):
                 if v.lower().startswith("active"):
                     reasons.add(nm)
         try:
@@ -118,6 +169,7 @@ class ClockSampler:
             out["sm_max_mhz"] = float(max(mx))
             out["samples"] = len(sm)
         out["reasons"] = sorted(reasons)
+        out["source"] = "nvidia-smi"
         return out
 
 
@@ -239,6 +291,7 @@ class Group:
         self.out = torch.empty(N_LAYERS, n, N_HEAD, HD, device="cuda")
         self.t = 0
         self.graph = None
+        self.ev_in = self.ev_done = None
 
     def enqueue_layers(self):
         for layer in range(N_LAYERS):
@@ -258,11 +311,22 @@ class Group:
         self.t += 1
         assert L.q4_hip_graph_launch(self.graph)
 
-    def step_e2e(self, L):
+    def copy_in(self, L, torch, cs):
+        """this step's inputs from pinned host memory, on the library's copy stream (C ABI), after the
+        previous step that used these device buffers"""
+        if self.ev_done is not None:
+            cs.wait_event(self.ev_done)
         for d, h in ((self.q, self.q_h), (self.k, self.k_h), (self.v, self.v_h), (self.idx, self.idx_h)):
-            assert L.q4_hip_h2d_async(d.data_ptr(), h.data_ptr(), h.numel() * h.element_size())
+            assert L.q4_hip_copy_h2d(d.data_ptr(), h.data_ptr(), h.numel() * h.element_size())
+        self.ev_in = torch.cuda.Event()
+        self.ev_in.record(cs)
+
+    def run_e2e(self, L, torch, xs):
+        xs.wait_event(self.ev_in)
         self.step(L)
         assert L.q4_hip_d2h_async(self.out_h.data_ptr(), self.out.data_ptr(), self.out.numel() * 4)
+        self.ev_done = torch.cuda.Event()
+        self.ev_done.record(xs)
 
     def e2e_bytes(self):
         h2d = sum(h.numel() * h.element_size() for h in (self.q_h, self.k_h, self.v_h, self.idx_h)) + 4 * self.n
@@ -488,8 +552,8 @@ def run_seqshard(args, torch, q4gpu, L, dist, rank, world, peak_gbs):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--sessions", type=int, default=64)
     ap.add_argument("--no-extras", action="store_true")
@@ -580,23 +644,46 @@ def main():
         return float(t.item())
 
     # ---- device-resident timing
+    sampler = ClockSampler(local, "GPU-" + str(torch.cuda.get_device_properties(local).uuid)) if rank == 0 else None
     for i in range(args.warmup):
         groups[i % groups_n].step(L)
     barrier()
-    sampler = ClockSampler(local) if rank == 0 else None
+    windows = []
+    w0 = time.perf_counter()
     torch.cuda.profiler.start()               # profilers started with capture off see the timed steps only
     dt = timed(torch, ext, lambda i: groups[i % groups_n].step(L), args.steps)
     torch.cuda.profiler.stop()
+    windows.append((w0, time.perf_counter()))
     barrier()
     dt = max_over_ranks(dt)
     # ---- end to end: host buffers in, outputs out, every step
-    for i in range(3):
-        groups[i % groups_n].step_e2e(L)
+    # Uploads ride the library's copy stream (q4_hip_copy_h2d) and are ordered against the compute
+    # stream with events, so the inputs of step i+1 travel while step i computes; every step's copies in
+    # and out are inside the timed region.
+    cs = torch.cuda.ExternalStream(L.q4_gpu_copy_stream())
+
+    def e2e_loop(n):
+        groups[0].copy_in(L, torch, cs)
+        for i in range(n):
+            if i + 1 < n and groups_n > 1:
+                groups[(i + 1) % groups_n].copy_in(L, torch, cs)
+            groups[i % groups_n].run_e2e(L, torch, ext)
+            if i + 1 < n and groups_n == 1:          # one set of device buffers: no overlap possible
+                groups[0].copy_in(L, torch, cs)
+    e2e_loop(3)
     barrier()
-    dt_e2e = timed(torch, ext, lambda i: groups[i % groups_n].step_e2e(L), args.steps)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0 = time.perf_counter()
+    ev0.record(ext)
+    cs.wait_event(ev0)                     # no copy starts before the clock does
+    e2e_loop(args.steps)
+    ev1.record(ext)
+    ev1.synchronize()
+    windows.append((w0, time.perf_counter()))
+    dt_e2e = ev0.elapsed_time(ev1) * 1e-3
     barrier()
     dt_e2e = max_over_ranks(dt_e2e)
-    clocks = sampler.stop() if sampler else None
+    clocks = sampler.stop(windows) if sampler else None
 
     status = L.q4_gpu_last_error()
     assert status == 0, "device status %#x" % status

@@ -58,6 +58,10 @@ bool q4_hip_d2h(void *h, const void *d, size_t n);
 bool q4_hip_d2h_async(void *h, const void *d, uint64_t n);
 bool q4_hip_h2d_async(void *d, const void *h, uint64_t n);
 bool q4_hip_stream_sync(void);
+/* Upload on the separate copy stream and the blocking wait for it (src/q4.h:832,887,
+ * src/q4_rocm.cu:247-250,3270-3275): lets the next step's inputs travel while this step computes. */
+bool q4_hip_copy_h2d(void *dst, const void *src, size_t n);
+void q4_hip_copy_wait(void);
 /* src/q4.h:851,781, src/q4_rocm.cu:5656-5670 (n counts floats; copy is device-to-device) */
 bool q4_hip_copy(float *d, const float *s, uint64_t n);
 bool q4_hip_fill(float *d, float v, uint64_t n);
@@ -139,6 +143,7 @@ uint32_t q4_gpu_last_error(void);
 /* Internal compute stream as a cudaStream_t, and adoption of a caller's stream (NULL restores the
  * internal one).  No counterpart in the reference (its stream is private, src/q4_rocm.cu:52-54). */
 void *q4_gpu_stream(void);
+void *q4_gpu_copy_stream(void);   /* the copy stream as a cudaStream_t, for event ordering without a host wait */
 bool q4_gpu_set_stream(void *cuda_stream);
 int q4_gpu_device(void);
 /* Device address of the position word written by q4_hip_pos_push. */

@@ -488,7 +488,8 @@ struct q4_gpu_batch {
     q4_gpu_kv **kv;
     const Q4Cache **h_views;      /* pinned mirror of the device pointer table */
     const Q4Cache **d_views;
-    int32_t *pos_d, *pos_h;       /* pos_h: pinned ring of 8 uploads */
+    int32_t *pos_d, *pos_h;       /* pos_h: pinned ring of 8 uploads, each slot guarded by an event */
+    cudaEvent_t pos_ev[8];
     uint32_t ring, max_pos;
 };
 
@@ -503,6 +504,8 @@ extern "C" q4_gpu_batch *q4_gpu_batch_create(uint32_t max_sessions) {
               cudaMalloc(&b->pos_d, sizeof(int32_t) * max_sessions) == cudaSuccess &&
               cudaMallocHost(&b->pos_h, sizeof(int32_t) * max_sessions * 8) == cudaSuccess;
     if (ok) ok = cudaMemset(b->pos_d, 0, sizeof(int32_t) * max_sessions) == cudaSuccess;
+    for (int i = 0; ok && i < 8; i++)
+        ok = cudaEventCreateWithFlags(&b->pos_ev[i], cudaEventDisableTiming) == cudaSuccess;
     if (!ok) {
         (void)cudaGetLastError();
         q4i_fail(Q4E_CUDA, "batch_create: allocation failed");
@@ -518,6 +521,8 @@ extern "C" void q4_gpu_batch_destroy(q4_gpu_batch *b) {
     if (b->d_views) cudaFree(b->d_views);
     if (b->pos_d) cudaFree(b->pos_d);
     if (b->pos_h) cudaFreeHost(b->pos_h);
+    for (int i = 0; i < 8; i++)
+        if (b->pos_ev[i]) cudaEventDestroy(b->pos_ev[i]);
     free(b->kv);
     free(b);
 }
@@ -540,8 +545,11 @@ extern "C" bool q4_gpu_batch_bind(q4_gpu_batch *b, uint32_t slot, q4_gpu_kv *kv)
 }
 extern "C" bool q4_gpu_batch_set_pos(q4_gpu_batch *b, const int32_t *pos, uint32_t n_sessions) {
     if (!g_q4.ok) return q4i_fail(Q4E_INIT, "batch_set_pos: library not initialised");
-    Q4_REQUIRE(b && pos && n_sessions && n_sessions <= b->n, "batch_set_pos: bad argument");
-    int32_t *h = b->pos_h + (size_t)(b->ring++ & 7u) * b->max_sessions;
+    Q4_REQUIRE(b && pos && n_sessions && n_sessions <= b->n && !g_q4.capturing, "batch_set_pos: bad argument");
+    /* a host running more than 8 steps ahead waits here for the upload that last used this slot */
+    const uint32_t slot = b->ring++ & 7u;
+    if (!q4i_check(cudaEventSynchronize(b->pos_ev[slot]), "batch_set_pos slot")) return false;
+    int32_t *h = b->pos_h + (size_t)slot * b->max_sessions;
     uint32_t mx = 0;
     for (uint32_t i = 0; i < n_sessions; i++) {
         h[i] = pos[i];
@@ -549,7 +557,8 @@ extern "C" bool q4_gpu_batch_set_pos(q4_gpu_batch *b, const int32_t *pos, uint32
     }
     b->max_pos = mx;
     return q4i_check(cudaMemcpyAsync(b->pos_d, h, sizeof(int32_t) * n_sessions, cudaMemcpyHostToDevice, g_q4.stream),
-                     "batch_set_pos upload");
+                     "batch_set_pos upload") &&
+           q4i_check(cudaEventRecord(b->pos_ev[slot], g_q4.stream), "batch_set_pos event");
 }
 extern "C" bool q4_gpu_batch_append(q4_gpu_batch *b, uint32_t layer, const float *k, const float *v) {
     if (!g_q4.ok) return q4i_fail(Q4E_INIT, "batch_append: library not initialised");

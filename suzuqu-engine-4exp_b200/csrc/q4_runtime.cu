@@ -162,6 +162,20 @@ extern "C" bool q4_hip_h2d_async(void *d, const void *h, uint64_t n) {
     if (!g_q4.ok || !d || !h || !n) return false;
     return q4i_check(cudaMemcpyAsync(d, h, (size_t)n, cudaMemcpyHostToDevice, g_q4.stream), "h2d_async");
 }
+/* Copies on the separate copy stream, so uploads for the next step overlap the current step's
+ * kernels (src/q4.h:832,887; src/q4_rocm.cu:247-250,3270-3275).  The caller orders them against the
+ * compute stream with q4_hip_copy_wait (blocking) or with events on q4_gpu_copy_stream(). */
+extern "C" bool q4_hip_copy_h2d(void *dst, const void *src, size_t n) {
+    if (!g_q4.ok || !dst || !src || !n) return false;
+    cudaStream_t st = g_q4.copy_stream ? g_q4.copy_stream : g_q4.stream;
+    return q4i_check(cudaMemcpyAsync(dst, src, n, cudaMemcpyHostToDevice, st), "copy_h2d");
+}
+extern "C" void q4_hip_copy_wait(void) {
+    if (!g_q4.ok) return;
+    if (g_q4.copy_stream) (void)cudaStreamSynchronize(g_q4.copy_stream);
+    else (void)cudaDeviceSynchronize();
+}
+extern "C" void *q4_gpu_copy_stream(void) { return g_q4.ok ? (void *)g_q4.copy_stream : nullptr; }
 extern "C" bool q4_hip_stream_sync(void) {
     if (!g_q4.ok) return false;
     return q4i_check(cudaStreamSynchronize(g_q4.stream), "stream_sync");
@@ -193,15 +207,14 @@ extern "C" bool q4_hip_fill(float *d, float v, uint64_t n) {
     return q4i_check(cudaGetLastError(), "fill launch");
 }
 
-/* Decode position for graph-captured kernels: stream-ordered 4-byte upload from pinned memory.
- * A ring of staging words keeps an upload that has not executed yet from being overwritten by the
- * next push. */
+/* Decode position for graph-captured kernels: a stream-ordered one-word store.  The value travels
+ * as a launch argument, so a host that runs many steps ahead of the device has no staging word that
+ * a later push could overwrite before the device has read it. */
+__global__ void q4_set_word_k(int32_t *dst, int32_t v) { *dst = v; }
 extern "C" void q4_hip_pos_push(int32_t pos) {
     if (!g_q4.ok) return;
-    static unsigned slot = 0;
-    int32_t *h = g_q4.pos_h + (slot++ & 63u);
-    *h = pos;
-    (void)cudaMemcpyAsync(g_q4.pos_d, h, sizeof(int32_t), cudaMemcpyHostToDevice, g_q4.stream);
+    q4_set_word_k<<<1, 1, 0, g_q4.stream>>>(g_q4.pos_d, pos);
+    (void)q4i_check(cudaGetLastError(), "pos_push launch");
 }
 extern "C" int q4_hip_capturing(void) { return g_q4.capturing; }
 extern "C" int q4_hip_pos_dev_ok(void) { return g_q4.ok && g_q4.pos_d && g_q4.pos_h; }
