@@ -210,7 +210,7 @@ def cpu_step(items, news, threads):
 
 def cpu_baseline(ctxs, budget_s, n_sessions=4):
     from oracle import q4_oracle as oracle
-    threads = max(1, min(oracle.max_threads(), os.cpu_count() or 1))
+    threads = max(1, oracle.host_procs())
     items, news = cpu_sample_problem(ctxs, n_sessions, SEED + 9)
     cpu_step(items, news, threads)            # warm-up
     t0 = time.perf_counter()
@@ -232,7 +232,7 @@ def run_reference_arm(args, rank):
     from oracle import q4_oracle as oracle
     ctxs = draw_contexts(args.sessions)
     n_s = 4
-    threads = max(1, min(oracle.max_threads(), os.cpu_count() or 1))
+    threads = max(1, oracle.host_procs())
     items, news = cpu_sample_problem(ctxs, n_s, SEED + 9)
     for _ in range(args.warmup):
         cpu_step(items, news, threads)
@@ -480,14 +480,18 @@ def extras_dense(torch, q4gpu, L, ext, peak_gbs, kinds=("q8_0", "f16", "f32")):
 
 def run_seqshard(args, torch, q4gpu, L, dist, rank, world, peak_gbs):
     """configs[4]: one session at ctx 262144, dense attention; rank r owns an even contiguous slice of the
-    rows, computes (m, l, acc) records over it, the records are all-gathered over NCCL and merged on every
-    rank.  One step = 12 layers; time = max over ranks, on the device."""
+    rows and attends them; the (acc, m, l) records are exchanged and merged on every rank, either inside the
+    decode kernel (peer stores over NVLink, q4_gpu_kv_decode_xchg: the product) or by an NCCL all-gather
+    plus a merge kernel (timed beside it).  One step = 12 layers; time = max over ranks, on the device."""
     from q4gpu import shard
     ctx = 262144
     b, e = shard.rows_for_rank(ctx, rank, world)
     rows = e - b
     res = {}
     stream = torch.cuda.Stream()
+    xw = q4gpu.Exchange(rank, world, N_HEAD, N_KVH, HD)
+    if world > 1:
+        xw.attach_all(dist)
     for name, kind, rowb in (("q8_0", 2, 136), ("f16", 1, 256), ("f32", 0, 512)):
         if name not in args.dense_kinds.split(","):
             continue
@@ -496,11 +500,12 @@ def run_seqshard(args, torch, q4gpu, L, dist, rank, world, peak_gbs):
             q4gpu.use_torch_stream()
             torch.manual_seed(SEED + rank)
             fill_store(torch, st, rows)
+            torch.manual_seed(SEED)                       # the query is the same on every rank
             q = torch.randn(N_LAYERS, N_HEAD, HD, device="cuda").to(torch.bfloat16)
             part = torch.empty(N_LAYERS, N_HEAD, HD + 2, device="cuda")
             out = torch.empty(N_LAYERS, N_HEAD, HD, device="cuda")
 
-            def step():
+            def step_nccl():
                 for layer in range(N_LAYERS):
                     st.decode_partial(layer, q[layer], part[layer], N_HEAD, SCALE, n_kv=rows, q_bf16=True)
                     if world > 1:
@@ -509,43 +514,66 @@ def run_seqshard(args, torch, q4gpu, L, dist, rank, world, peak_gbs):
                         allp = part[layer:layer + 1]
                     q4gpu.check(L.q4_gpu_lse_merge(allp.data_ptr(), world, N_HEAD, HD, None, out[layer].data_ptr()),
                                 "q4_gpu_lse_merge")
-            for _ in range(max(args.warmup, 3)):
-                step()
-            stream.synchronize()
-            # the 12-layer step (decode, all-gather, merge per layer) as one CUDA graph: NCCL and the
-            # library's launches are all captured on this stream, so the host is out of the timed loop
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
+
+            def step_fused():
+                # one launch per layer: attend the local rows, store the record into every peer's window
+                # over NVLink, wait for theirs, merge
+                for layer in range(N_LAYERS):
+                    xw.decode(st, layer, q[layer], out_f[layer], SCALE, rows, q_bf16=True)
+
+            def time_graph(step):
+                for _ in range(max(args.warmup, 3)):
+                    step()
+                stream.synchronize()
+                # the 12-layer step as one CUDA graph (NCCL and the library's launches are all captured on
+                # this stream), so the host is out of the timed loop
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    q4gpu.use_torch_stream()
+                    step()
                 q4gpu.use_torch_stream()
-                step()
-            q4gpu.use_torch_stream()
-            for _ in range(3):
-                graph.replay()
+                for _ in range(3):
+                    graph.replay()
+                stream.synchronize()
+                if dist is not None:
+                    dist.barrier()
+                torch.cuda.synchronize()
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ev0.record(stream)
+                for _ in range(args.steps):
+                    graph.replay()
+                ev1.record(stream)
+                ev1.synchronize()
+                dt = ev0.elapsed_time(ev1) * 1e-3
+                del graph
+                if dist is not None:
+                    t = torch.tensor([dt], device="cuda", dtype=torch.float64)
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                    dt = float(t.item())
+                return 1e6 * dt / (args.steps * N_LAYERS)
+
+            out_f = torch.zeros_like(out)
+            us_nccl = time_graph(step_nccl) if world > 1 else None
+            us = time_graph(step_fused)
             stream.synchronize()
-            if dist is not None:
-                dist.barrier()
-            torch.cuda.synchronize()
-            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            ev0.record(stream)
-            for _ in range(args.steps):
-                graph.replay()
-            ev1.record(stream)
-            ev1.synchronize()
-            dt = ev0.elapsed_time(ev1) * 1e-3
-            del graph
-        if dist is not None:
-            t = torch.tensor([dt], device="cuda", dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            dt = float(t.item())
-        us = 1e6 * dt / (args.steps * N_LAYERS)
+            status = L.q4_gpu_last_error()
+            assert status == 0, "device status %#x" % status
+            if world > 1:      # the two exchanges must agree (same records, same merge arithmetic up to rounding)
+                err = float((out_f - out).abs().max())
+                assert err < 2e-3, "fused exchange differs from the all-gather path: %g" % err
         by = ctx * N_KVH * rowb * 2
-        res[name] = {"us_per_layer": us, "bytes_per_layer_all_ranks": by, "achieved_gbs_all_ranks": by / us / 1e3,
+        res[name] = {"us_per_layer": us, "us_per_layer_nccl_allgather": us_nccl, "bytes_per_layer_all_ranks": by,
+                     "achieved_gbs_all_ranks": by / us / 1e3,
                      "frac_of_measured_hbm_x_ranks": by / us / 1e3 / (peak_gbs * world)}
         st.close()
     L.q4_gpu_set_stream(None)
+    xw.close()
     if rank == 0:
         print(json.dumps({"metric": "dense_decode_us_per_layer_ctx262144", "mode": "seqshard", "n_gpus": world,
-                          "steps": args.steps, "exchange": "NCCL all-gather of %d B per rank per layer" % (N_HEAD * (HD + 2) * 4),
+                          "steps": args.steps,
+                          "exchange": "in-kernel: peer stores of %d B per peer per layer + epoch flags over NVLink; "
+                                      "us_per_layer_nccl_allgather is the same step with an NCCL all-gather + merge kernel"
+                                      % (N_HEAD * (HD + 4) * 4),
                           "result": res}), flush=True)
 
 

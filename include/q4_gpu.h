@@ -242,6 +242,33 @@ bool q4_gpu_kv_decode_partial(const q4_gpu_kv *kv, uint32_t layer, const void *q
 bool q4_gpu_lse_merge(const float *parts, uint32_t n_parts, uint32_t n_head, uint32_t hd,
                       const float *gate, float *out);
 
+/* ---- sequence-sharded decode with the exchange inside the kernel.  No counterpart in the reference
+ * (it runs one GPU); the merge is gqa_dec_comb_k's (src/q4_rocm.cu:6968-7012), taken across GPUs.
+ * Every rank of a node owns the rows [b, e) of one context in a store of its own and an exchange
+ * window; q4_gpu_kv_decode_xchg attends the local rows, stores the rank's (acc, m, l) record into
+ * every peer's window over NVLink, waits (bounded) for the peers' records and writes the merged,
+ * gated output on every rank: one launch per layer, no host round trip, no collective library.
+ *   create   : rank/world <= 16, n_kvh <= 16; allocates the window (cudaMalloc) and clears it.
+ *   handle   : the 64-byte CUDA IPC handle of the local window, to be sent to every peer once.
+ *   attach   : opens a peer's handle (another process on the same node, peer access required).
+ *   attach_ptr: a peer window that is already mapped in this process (q4_gpu_xchg_window of an
+ *              exchange object on the same device, or any mapping the host obtained itself).
+ *   phase    : 0 = attend, push, wait and merge in one kernel; 1 = attend and push only; 2 = wait
+ *              and merge only (kv, q, n_kv, scale ignored).  1 then 2 on every rank equals 0.
+ *   Every rank must make the same sequence of calls.  A wait that outlasts the limit (2 s unless
+ *   set) sets status bit 32 in q4_gpu_last_error() and the output is this rank's own part only; the
+ *   context stays usable. */
+typedef struct q4_gpu_xchg q4_gpu_xchg;
+q4_gpu_xchg *q4_gpu_xchg_create(uint32_t rank, uint32_t world, uint32_t n_head, uint32_t n_kvh, uint32_t hd);
+void q4_gpu_xchg_destroy(q4_gpu_xchg *x);
+bool q4_gpu_xchg_handle(q4_gpu_xchg *x, void *handle64);
+void *q4_gpu_xchg_window(q4_gpu_xchg *x);
+bool q4_gpu_xchg_attach(q4_gpu_xchg *x, uint32_t peer_rank, const void *handle64);
+bool q4_gpu_xchg_attach_ptr(q4_gpu_xchg *x, uint32_t peer_rank, void *peer_window);
+bool q4_gpu_xchg_set_timeout_ms(q4_gpu_xchg *x, uint32_t ms);
+bool q4_gpu_kv_decode_xchg(const q4_gpu_kv *kv, q4_gpu_xchg *x, uint32_t layer, const void *q, int q_bf16,
+                           const float *gate, float *out, uint32_t n_kv, float scale, int phase);
+
 /* ---- batched multi-session decode: one launch per layer for every session of the batch. */
 typedef struct q4_gpu_batch q4_gpu_batch;
 q4_gpu_batch *q4_gpu_batch_create(uint32_t max_sessions);

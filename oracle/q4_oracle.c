@@ -513,3 +513,13 @@ Q4O_API int q4o_max_threads(void) {
     return 1;
 #endif
 }
+
+/* Processors this process may run on, whatever OMP_NUM_THREADS says (launchers of multi-process jobs
+ * set it to 1); 1 without OpenMP.  The timed baseline passes this as its explicit thread count. */
+Q4O_API int q4o_host_procs(void) {
+#ifdef _OPENMP
+    return omp_get_num_procs();
+#else
+    return 1;
+#endif
+}

@@ -68,6 +68,7 @@ def lib():
         L.q4o_lse_merge.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p,
                                     C.c_void_p]
         L.q4o_max_threads.restype = C.c_int
+        L.q4o_host_procs.restype = C.c_int
         L.q4o_attn_items.restype = C.c_int
         L.q4o_attn_items.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float,
                                      C.c_int, C.c_int]
@@ -240,6 +241,11 @@ def lse_merge(parts, n_head, hd, gate=None):
 
 def max_threads():
     return int(lib().q4o_max_threads())
+
+
+def host_procs():
+    """processors usable by this process, independent of OMP_NUM_THREADS (1 without OpenMP)"""
+    return int(lib().q4o_host_procs())
 
 
 class Item(C.Structure):

@@ -68,6 +68,8 @@ struct DecParams {
     float *scratch;
     uint32_t *counters;
     uint32_t *err;
+    const Q4XchgDev *xchg;   /* sequence-sharded decode: exchange window (null otherwise) */
+    uint32_t xchg_phase;
 };
 
 /* ---- small device helpers ---------------------------------------------------------------- */
@@ -351,6 +353,100 @@ __device__ __noinline__ void cluster_merge(uint32_t rec_saddr, uint32_t S, uint3
             }
         }
     }
+}
+
+/* ---- exchange of the units' records between ranks (sequence-sharded decode) --------------------
+ * The block that finishes a unit's last merge leaves the record in its own window, stores it into the
+ * same slot of every peer's window (plain peer stores over NVLink), publishes it with one release
+ * store of the call's epoch per peer, waits for the peers' epochs in its own window and merges the
+ * `world` records into the output.  Slots and flags are double-buffered by the parity of the epoch:
+ * a rank can be at most one call ahead of a peer, because it cannot finish call e+1 before the peer
+ * has published e+1, which the peer does only after it finished reading call e.  Every wait is
+ * bounded; when it runs out the status bit Q4E_PEER is set and the output is the rank's own part. */
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ float *xchg_slot(const Q4XchgDev *xd, Q4XchgWin *w, uint32_t par, uint32_t unit,
+                                            uint32_t writer) {
+    float *base = reinterpret_cast<float *>(reinterpret_cast<char *>(w) + XCHG_REC_OFFSET);
+    return base + ((size_t)(par * xd->units + unit) * xd->world + writer) * xd->slot_floats;
+}
+/* where the unit's last merge leaves this rank's record for the call that is running */
+__device__ __noinline__ float *xchg_own_slot(const Q4XchgDev *xd, uint32_t unit) {
+    Q4XchgWin *w = xd->win[xd->rank];
+    const uint32_t epoch = __ldcg(&w->epoch[unit]) + 1u;
+    return xchg_slot(xd, w, epoch & 1u, unit, xd->rank);
+}
+template <int HD, int HEADS>
+__device__ __noinline__ void xchg_wait_merge(const Q4XchgDev *xd, uint32_t unit, uint32_t epoch, const MergeOut mo,
+                                             uint32_t *err) {
+    __shared__ uint32_t s_missing;
+    const uint32_t rank = xd->rank, world = xd->world, par = epoch & 1u;
+    Q4XchgWin *w = xd->win[rank];
+    if (threadIdx.x == 0) s_missing = 0u;
+    __syncthreads();
+    if (threadIdx.x < world && threadIdx.x != rank) {
+        const uint32_t *f = &w->flags[par][unit][threadIdx.x];
+        const unsigned long long t0 = global_ns(), limit = xd->timeout_ns;
+        uint32_t polls = 0;
+        while ((int32_t)(ld_acquire_sys(f) - epoch) < 0) {
+            if (++polls < 64u) continue;
+            __nanosleep(100);
+            /* time limit, plus a poll limit in case the timer does not advance */
+            if ((polls & 255u) == 0u && (global_ns() - t0 > limit || polls > (1u << 26))) {
+                atomicOr(&s_missing, 1u << threadIdx.x);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    const bool alone = s_missing != 0u;
+    if (alone && threadIdx.x == 0) atomicOr(err, (uint32_t)Q4E_PEER);
+    merge_records<HD, HEADS>(xchg_slot(xd, w, par, unit, alone ? rank : 0u), alone ? 1u : world, true, nullptr, mo);
+}
+template <int HD, int HEADS>
+__device__ __noinline__ void xchg_finish(const Q4XchgDev *xd, uint32_t phase, uint32_t unit, const MergeOut mo,
+                                         uint32_t *err) {
+    constexpr int REC = HD + 4;
+    const uint32_t rank = xd->rank, world = xd->world;
+    Q4XchgWin *w = xd->win[rank];
+    const uint32_t epoch = __ldcg(&w->epoch[unit]) + 1u, par = epoch & 1u;
+    /* the merge that wrote the record ended with a block barrier: all of it is visible here */
+    const float4 *own = reinterpret_cast<const float4 *>(xchg_slot(xd, w, par, unit, rank));
+    const uint32_t n4 = mo.gqa * REC / 4;
+    for (uint32_t p = 0; p < world; p++) {
+        if (p == rank) continue;
+        float4 *dst = reinterpret_cast<float4 *>(xchg_slot(xd, xd->win[p], par, unit, rank));
+        for (uint32_t i = threadIdx.x; i < n4; i += DEC_THREADS) dst[i] = own[i];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < world && threadIdx.x != rank)
+        st_release_sys(&xd->win[threadIdx.x]->flags[par][unit][rank], epoch);
+    if (threadIdx.x == 0) w->epoch[unit] = epoch;
+    if (phase == XCHG_PUSH) return;
+    xchg_wait_merge<HD, HEADS>(xd, unit, epoch, mo, err);
+}
+/* the wait-and-merge half as its own launch (one block per unit), after a push-only decode */
+template <int HD, int HEADS>
+__global__ void __launch_bounds__(DEC_THREADS) q4_xchg_merge_k(const Q4XchgDev *xd, uint32_t gqa, const float *gate,
+                                                               float *out, uint32_t *err) {
+    const uint32_t unit = blockIdx.x;
+    MergeOut mo;
+    mo.out = out; mo.part_out = nullptr; mo.gate = gate;
+    mo.row0 = (size_t)unit * gqa;
+    mo.gqa = gqa;
+    xchg_wait_merge<HD, HEADS>(xd, unit, __ldcg(&xd->win[xd->rank]->epoch[unit]), mo, err);
 }
 
 /* ---- the kernel ---------------------------------------------------------------------------- */
@@ -970,7 +1066,9 @@ q4_decode_k(const DecParams P) {
     mo.row0 = (size_t)u * P.n_head + (size_t)kh * P.gqa;
     mo.gqa = P.gqa;
     if (S == 1) {
-        merge_records<HD, HEADS>(sm, DEC_WARPS, false, nullptr, mo);
+        float *fin = P.xchg ? xchg_own_slot(P.xchg, (uint32_t)unit) : nullptr;
+        merge_records<HD, HEADS>(sm, DEC_WARPS, false, fin, mo);
+        if (fin) xchg_finish<HD, HEADS>(P.xchg, P.xchg_phase, (uint32_t)unit, mo, P.err);
         return;
     }
     if (P.cluster) {
@@ -996,22 +1094,29 @@ q4_decode_k(const DecParams P) {
     float *dst = rec1 + (size_t)split * HEADS * REC;
     uint32_t *arrive = ctr + 1 + grp;
     uint32_t expected = grp_size;
+    bool last = false;
     for (int level = 0;; level++) {
         merge_records<HD, HEADS>(src, count, global, dst, mo);
-        if (!dst) return;                                  /* finalised */
+        if (last) {                                        /* finalised, or this rank's record is complete */
+            if (P.xchg) xchg_finish<HD, HEADS>(P.xchg, P.xchg_phase, (uint32_t)unit, mo, P.err);
+            return;
+        }
         if (!arrive_last(arrive, expected)) return;        /* someone else carries on */
         global = true;
         if (level == 0) {
             src = rec1 + (size_t)grp * DEC_GROUP * HEADS * REC;
             count = grp_size;
-            dst = n_groups == 1 ? nullptr : rec2 + (size_t)grp * HEADS * REC;
+            last = n_groups == 1;
+            dst = last ? nullptr : rec2 + (size_t)grp * HEADS * REC;
             arrive = ctr;
             expected = n_groups;
         } else {
             src = rec2;
             count = n_groups;
+            last = true;
             dst = nullptr;
         }
+        if (last && P.xchg) dst = xchg_own_slot(P.xchg, (uint32_t)unit);
     }
 }
 
@@ -1133,7 +1238,8 @@ bool q4i_decode(const Q4DecodeArgs &a) {
         use_cluster = e ? atoi(e) : 1;
     }
     bool cluster = false;
-    if (use_cluster && !a.scratch_part && (S <= 8 || steps <= 512)) {
+    if (a.xchg) Q4_REQUIRE(a.n_units == 1 && a.out && !a.part_out && !a.many, "decode: exchange mode is for one token of one session");
+    if (use_cluster && !a.scratch_part && !a.xchg && (S <= 8 || steps <= 512)) {
         if (S > 8) S = 8;
         cluster = S > 1;
     }
@@ -1186,6 +1292,8 @@ bool q4i_decode(const Q4DecodeArgs &a) {
     p.scratch = scratch;
     p.counters = counters;
     p.err = g_q4.err_d;
+    p.xchg = a.xchg;
+    p.xchg_phase = (uint32_t)a.xchg_phase;
     dim3 grid(S, a.n_kvh, a.n_units);
     switch (a.layout) {
     case LAY_F32: return launch_hd<LAY_F32>(p, grid, a.hd);
@@ -1194,6 +1302,25 @@ bool q4i_decode(const Q4DecodeArgs &a) {
     case LAY_Q8R: return launch_hd<LAY_Q8R>(p, grid, a.hd);
     }
     return q4i_fail(Q4E_ARG, "decode: bad layout");
+}
+
+namespace {
+template <int HD>
+bool launch_xchg_merge(const q4_gpu_xchg *x, uint32_t gqa, const float *gate, float *out) {
+    if (gqa <= 8) q4_xchg_merge_k<HD, 8><<<x->n_kvh, DEC_THREADS, 0, g_q4.stream>>>(x->dev, gqa, gate, out, g_q4.err_d);
+    else q4_xchg_merge_k<HD, 16><<<x->n_kvh, DEC_THREADS, 0, g_q4.stream>>>(x->dev, gqa, gate, out, g_q4.err_d);
+    return q4i_check(cudaGetLastError(), "exchange merge launch");
+}
+}  // namespace
+bool q4i_xchg_merge(const q4_gpu_xchg *x, const float *gate, float *out) {
+    const uint32_t gqa = x->n_head / x->n_kvh;
+    switch (x->hd) {
+    case 32: return launch_xchg_merge<32>(x, gqa, gate, out);
+    case 64: return launch_xchg_merge<64>(x, gqa, gate, out);
+    case 128: return launch_xchg_merge<128>(x, gqa, gate, out);
+    case 256: return launch_xchg_merge<256>(x, gqa, gate, out);
+    }
+    return q4i_fail(Q4E_ARG, "exchange merge: hd must be 32, 64, 128 or 256");
 }
 
 extern "C" bool q4_gpu_lse_merge(const float *parts, uint32_t n_parts, uint32_t n_head, uint32_t hd,

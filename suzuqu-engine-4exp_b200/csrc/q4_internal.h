@@ -15,6 +15,7 @@ enum { LAY_F32 = 0, LAY_F16 = 1, LAY_Q8P = 2 /* native store: 16-byte aligned re
 
 enum {
     Q4E_ARG = 1, Q4E_CUDA = 2, Q4E_RANGE = 4, Q4E_SCRATCH = 8, Q4E_INIT = 16,
+    Q4E_PEER = 32,   /* a peer's record did not arrive within the time limit */
 };
 
 /* One cache as the kernels see it.  Row (layer, kv head kh, token p) of the K plane lives at
@@ -65,6 +66,34 @@ bool q4i_scratch(size_t part_floats, size_t n_counters); /* grows outside captur
         if (!(cond)) return q4i_fail(Q4E_ARG, what); \
     } while (0)
 
+/* ---- record exchange between the ranks of a sequence-sharded decode -----------------------------
+ * Every rank owns one window in its own memory that all peers can write.  It starts with this header;
+ * the records follow at XCHG_REC_OFFSET: float rec[2][units][world][slot_floats], one slot per
+ * (parity of the call count, unit = kv head, writing rank), each slot the kernel's internal record
+ * layout for the unit's heads: {acc[hd], m (log2 units, scale folded in), l, 2 pad} per head. */
+constexpr uint32_t XCHG_MAX_WORLD = 16, XCHG_MAX_UNITS = 16;
+constexpr size_t XCHG_REC_OFFSET = 4096;
+struct Q4XchgWin {
+    uint32_t epoch[XCHG_MAX_UNITS];                       /* calls completed by the owner, per unit */
+    uint32_t flags[2][XCHG_MAX_UNITS][XCHG_MAX_WORLD];    /* [parity][unit][writer] = epoch of the record in the slot */
+};
+/* who and where, in the owner's device memory (never written by peers) */
+struct Q4XchgDev {
+    uint32_t rank, world, units, slot_floats;
+    unsigned long long timeout_ns;
+    Q4XchgWin *win[XCHG_MAX_WORLD];                       /* win[rank] is the local window */
+};
+enum { XCHG_FUSED = 0, XCHG_PUSH = 1, XCHG_MERGE = 2 };
+struct q4_gpu_xchg {
+    uint32_t n_head, n_kvh, hd;
+    size_t win_bytes;
+    Q4XchgWin *win;
+    Q4XchgDev host, *dev;
+    uint8_t attached[XCHG_MAX_WORLD];                     /* 1 = opened from an IPC handle, 2 = caller's pointer */
+};
+/* wait-and-merge half alone (q4_decode.cu): the records of the latest push on every rank -> out */
+bool q4i_xchg_merge(const q4_gpu_xchg *x, const float *gate, float *out);
+
 /* decode attention launcher (q4_decode.cu) */
 struct Q4DecodeArgs {
     Q4Cache one;                 /* used when many == nullptr */
@@ -87,6 +116,10 @@ struct Q4DecodeArgs {
     uint32_t *scratch_counters;
     size_t scratch_part_floats, scratch_n_counters;
     int scratch_clamp;           /* reduce the split count until the records fit the caller's scratch */
+    /* sequence-sharded decode: leave the unit's record in the exchange window, push it to the peers and
+     * (XCHG_FUSED) wait for theirs and write the merged output; null = single-rank decode */
+    const Q4XchgDev *xchg;
+    int xchg_phase;
 };
 bool q4i_decode(const Q4DecodeArgs &a);
 

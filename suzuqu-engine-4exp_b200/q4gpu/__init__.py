@@ -61,6 +61,11 @@ SIGNATURES = {
     "q4_gpu_kv_decode_noalloc": (_b, [_v, _u32, _v, _i, _v, _v, _u32, _v, _u32, _u32, _u32, _f]),
     "q4_gpu_kv_decode_partial": (_b, [_v, _u32, _v, _i, _v, _u32, _v, _u32, _u32, _u32, _f]),
     "q4_gpu_lse_merge": (_b, [_v, _u32, _u32, _u32, _v, _v]),
+    "q4_gpu_xchg_create": (_v, [_u32, _u32, _u32, _u32, _u32]), "q4_gpu_xchg_destroy": (None, [_v]),
+    "q4_gpu_xchg_handle": (_b, [_v, _v]), "q4_gpu_xchg_window": (_v, [_v]),
+    "q4_gpu_xchg_attach": (_b, [_v, _u32, _v]), "q4_gpu_xchg_attach_ptr": (_b, [_v, _u32, _v]),
+    "q4_gpu_xchg_set_timeout_ms": (_b, [_v, _u32]),
+    "q4_gpu_kv_decode_xchg": (_b, [_v, _v, _u32, _v, _i, _v, _v, _u32, _f, _i]),
     "q4_gpu_kv_prefill": (_b, [_v, _u32, _v, _v, _v, _u32, _u32, _u32, _f]),
     "q4_gpu_batch_create": (_v, [_u32]), "q4_gpu_batch_destroy": (None, [_v]),
     "q4_gpu_batch_bind": (_b, [_v, _u32, _v]), "q4_gpu_batch_set_pos": (_b, [_v, _v, _u32]),
@@ -192,6 +197,57 @@ class KVStore:
         check(self.L.q4_gpu_kv_decode_partial(self.h, layer, _ptr(q), int(q_bf16), _ptr(part), n_head,
                                               _ptr(idx), width, idx_kvh_stride, n_kv, scale),
               "q4_gpu_kv_decode_partial")
+
+
+class Exchange:
+    """Exchange window of one rank of a sequence-sharded decode (q4_gpu_xchg_*): the decode kernel
+    pushes its record into the peers' windows and merges theirs, one launch per layer."""
+    FUSED, PUSH, MERGE = 0, 1, 2
+
+    def __init__(self, rank, world, n_head, n_kvh, hd):
+        self.L = init()
+        self.rank, self.world = rank, world
+        self.h = self.L.q4_gpu_xchg_create(rank, world, n_head, n_kvh, hd)
+        if not self.h:
+            raise RuntimeError("q4_gpu_xchg_create failed (status %#x)" % self.L.q4_gpu_last_error())
+
+    def handle(self):
+        """the 64-byte IPC handle of the local window"""
+        buf = C.create_string_buffer(64)
+        check(self.L.q4_gpu_xchg_handle(self.h, C.cast(buf, C.c_void_p)), "q4_gpu_xchg_handle")
+        return bytes(buf.raw)
+
+    def window(self):
+        return self.L.q4_gpu_xchg_window(self.h)
+
+    def attach(self, peer_rank, handle):
+        buf = C.create_string_buffer(bytes(handle), 64)
+        check(self.L.q4_gpu_xchg_attach(self.h, peer_rank, C.cast(buf, C.c_void_p)), "q4_gpu_xchg_attach")
+
+    def attach_ptr(self, peer_rank, window):
+        check(self.L.q4_gpu_xchg_attach_ptr(self.h, peer_rank, window), "q4_gpu_xchg_attach_ptr")
+
+    def attach_all(self, dist):
+        """exchange the handles over a torch.distributed process group (host side, once) and open them"""
+        handles = [None] * self.world
+        dist.all_gather_object(handles, self.handle())
+        for r, hd_ in enumerate(handles):
+            if r != self.rank:
+                self.attach(r, hd_)
+        dist.barrier()
+
+    def set_timeout_ms(self, ms):
+        check(self.L.q4_gpu_xchg_set_timeout_ms(self.h, ms), "q4_gpu_xchg_set_timeout_ms")
+
+    def decode(self, store, layer, q, out, scale, n_kv, gate=None, q_bf16=False, phase=0):
+        check(self.L.q4_gpu_kv_decode_xchg(store.h if store is not None else None, self.h, layer, _ptr(q),
+                                           int(q_bf16), _ptr(gate), _ptr(out), n_kv, scale, phase),
+              "q4_gpu_kv_decode_xchg")
+
+    def close(self):
+        if self.h:
+            self.L.q4_gpu_xchg_destroy(self.h)
+            self.h = None
 
 
 class Batch:
