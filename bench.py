@@ -291,7 +291,7 @@ class Group:
         self.out = torch.empty(N_LAYERS, n, N_HEAD, HD, device="cuda")
         self.t = 0
         self.graph = None
-        self.ev_in = self.ev_done = None
+        self.ev_in = self.ev_comp = self.ev_done = None
 
     def enqueue_layers(self):
         for layer in range(N_LAYERS):
@@ -313,20 +313,27 @@ class Group:
 
     def copy_in(self, L, torch, cs):
         """this step's inputs from pinned host memory, on the library's copy stream (C ABI), after the
-        previous step that used these device buffers"""
-        if self.ev_done is not None:
-            cs.wait_event(self.ev_done)
+        previous step that read these device buffers"""
+        if self.ev_comp is not None:
+            cs.wait_event(self.ev_comp)
         for d, h in ((self.q, self.q_h), (self.k, self.k_h), (self.v, self.v_h), (self.idx, self.idx_h)):
             assert L.q4_hip_copy_h2d(d.data_ptr(), h.data_ptr(), h.numel() * h.element_size())
         self.ev_in = torch.cuda.Event()
         self.ev_in.record(cs)
 
-    def run_e2e(self, L, torch, xs):
+    def run_e2e(self, L, torch, xs, ds):
+        """compute on the library's stream once the inputs are in and the previous result of this group is
+        out; the result goes back on the download stream"""
         xs.wait_event(self.ev_in)
+        if self.ev_done is not None:
+            xs.wait_event(self.ev_done)
         self.step(L)
-        assert L.q4_hip_d2h_async(self.out_h.data_ptr(), self.out.data_ptr(), self.out.numel() * 4)
+        self.ev_comp = torch.cuda.Event()
+        self.ev_comp.record(xs)
+        ds.wait_event(self.ev_comp)
+        assert L.q4_gpu_copy_d2h(self.out_h.data_ptr(), self.out.data_ptr(), self.out.numel() * 4)
         self.ev_done = torch.cuda.Event()
-        self.ev_done.record(xs)
+        self.ev_done.record(ds)
 
     def e2e_bytes(self):
         h2d = sum(h.numel() * h.element_size() for h in (self.q_h, self.k_h, self.v_h, self.idx_h)) + 4 * self.n
@@ -689,13 +696,14 @@ def main():
     # stream with events, so the inputs of step i+1 travel while step i computes; every step's copies in
     # and out are inside the timed region.
     cs = torch.cuda.ExternalStream(L.q4_gpu_copy_stream())
+    ds = torch.cuda.ExternalStream(L.q4_gpu_download_stream())
 
     def e2e_loop(n):
         groups[0].copy_in(L, torch, cs)
         for i in range(n):
             if i + 1 < n and groups_n > 1:
                 groups[(i + 1) % groups_n].copy_in(L, torch, cs)
-            groups[i % groups_n].run_e2e(L, torch, ext)
+            groups[i % groups_n].run_e2e(L, torch, ext, ds)
             if i + 1 < n and groups_n == 1:          # one set of device buffers: no overlap possible
                 groups[0].copy_in(L, torch, cs)
     e2e_loop(3)
@@ -705,6 +713,7 @@ def main():
     ev0.record(ext)
     cs.wait_event(ev0)                     # no copy starts before the clock does
     e2e_loop(args.steps)
+    ext.wait_stream(ds)                    # the last result is on the host before the clock stops
     ev1.record(ext)
     ev1.synchronize()
     windows.append((w0, time.perf_counter()))

@@ -144,6 +144,10 @@ uint32_t q4_gpu_last_error(void);
  * internal one).  No counterpart in the reference (its stream is private, src/q4_rocm.cu:52-54). */
 void *q4_gpu_stream(void);
 void *q4_gpu_copy_stream(void);   /* the copy stream as a cudaStream_t, for event ordering without a host wait */
+/* Download on a third stream (no counterpart in the reference, which reads results back on its compute
+ * stream): device-to-host copies overlap the next step's kernels and uploads.  Order it with events. */
+bool q4_gpu_copy_d2h(void *dst, const void *src, size_t n);
+void *q4_gpu_download_stream(void);
 bool q4_gpu_set_stream(void *cuda_stream);
 int q4_gpu_device(void);
 /* Device address of the position word written by q4_hip_pos_push. */

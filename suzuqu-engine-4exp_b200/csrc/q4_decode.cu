@@ -449,6 +449,32 @@ __global__ void __launch_bounds__(DEC_THREADS) q4_xchg_merge_k(const Q4XchgDev *
     xchg_wait_merge<HD, HEADS>(xd, unit, __ldcg(&xd->win[xd->rank]->epoch[unit]), mo, err);
 }
 
+#ifdef Q4_DEC_TIMING
+/* experiment builds only: per-block time stamps {globaltimer at start, then SM cycles since start at
+ * first data, end of the position loop, block record merged, exit} */
+__device__ unsigned long long q4_dbg_stamps[8192 * 16];
+#define Q4_STAMP(i)                                                                                   \
+    do {                                                                                              \
+        if (threadIdx.x == 0) {                                                                       \
+            const uint32_t bid_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);     \
+            if (bid_ < 8192) q4_dbg_stamps[bid_ * 16 + (i)] = (i) == 0 ? global_ns() : (unsigned long long)(clock64() - dbg_c0_); \
+        }                                                                                             \
+    } while (0)
+/* same, but not before the value `dep` is in a register */
+#define Q4_STAMP_DEP(i, dep)                                                                          \
+    do {                                                                                              \
+        long long c_;                                                                                 \
+        asm volatile("mov.u64 %0, %%clock64;" : "=l"(c_) : "r"((uint32_t)(dep)) : "memory");          \
+        if (threadIdx.x == 0) {                                                                       \
+            const uint32_t bid_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);     \
+            if (bid_ < 8192) q4_dbg_stamps[bid_ * 16 + (i)] = (unsigned long long)(c_ - dbg_c0_);     \
+        }                                                                                             \
+    } while (0)
+#else
+#define Q4_STAMP(i) do { } while (0)
+#define Q4_STAMP_DEP(i, dep) do { } while (0)
+#endif
+
 /* ---- the kernel ---------------------------------------------------------------------------- */
 constexpr int RING_STAGES = 4;
 constexpr int RING_STAGE_BYTES = 2048 + 2048 + 256 + 64;   /* K rows, V rows, scale rows, positions */
@@ -478,6 +504,16 @@ q4_decode_k(const DecParams P) {
     constexpr int NBQ = Q8 ? NB : 1;
 
     extern __shared__ __align__(16) uint8_t smem_raw[];
+#ifdef Q4_DEC_TIMING
+    const long long dbg_c0_ = clock64();
+    if (threadIdx.x == 0) {
+        const uint32_t bid_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+        uint32_t smid_;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid_));
+        if (bid_ < 8192) q4_dbg_stamps[bid_ * 16 + 7] = smid_;
+    }
+#endif
+    Q4_STAMP(0);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const uint32_t split = blockIdx.x, kh = blockIdx.y, u = blockIdx.z;
     const uint32_t S = P.S;
@@ -751,8 +787,11 @@ q4_decode_k(const DecParams P) {
             cp_async_commit();   /* one group per stage, empty or not, keeps the wait count uniform */
         };
         int32_t pa = my_pos(0), pb = my_pos(1), pc = my_pos(2), pd = my_pos(3), pe = my_pos(4), pf = my_pos(5);
+        Q4_STAMP_DEP(8, max_kv);
+        Q4_STAMP_DEP(9, pa | pb);
         issue(0, pa);
         issue(1, pb);
+        Q4_STAMP(10);
         pa = pc; pb = pd;      /* next iteration's stages */
         pc = pe; pd = pf;      /* the ones after: list entries are fetched two iterations ahead */
 
@@ -802,6 +841,7 @@ q4_decode_k(const DecParams P) {
             }
         }
 
+        Q4_STAMP_DEP(11, qs[0][0][0]);
         for (uint32_t it = 0; it < n_even; it += 2) {
             issue(it + 2, pa);
             issue(it + 3, pb);
@@ -810,6 +850,9 @@ q4_decode_k(const DecParams P) {
             pd = my_pos(it + 7);
             cp_async_wait<2>();                  /* all but the two newest stages have landed */
             __syncwarp();
+#ifdef Q4_DEC_TIMING
+            if (it == 0) Q4_STAMP(1);
+#endif
             uint32_t st[2];
             st[0] = ring + (it % RING_STAGES) * RING_STAGE_BYTES;
             st[1] = ring + ((it + 1) % RING_STAGES) * RING_STAGE_BYTES;
@@ -941,6 +984,7 @@ q4_decode_k(const DecParams P) {
             }
             __syncwarp();   /* every lane is done with both stages before a later issue overwrites them */
         }
+        Q4_STAMP(2);
         cp_async_wait<0>();
         __syncthreads();    /* the epilogue below reuses the ring memory of all warps */
     } else {
@@ -1074,9 +1118,13 @@ q4_decode_k(const DecParams P) {
     if (P.cluster) {
         float *own = reinterpret_cast<float *>(smem_raw + Cfg::EPI_BYTES);
         merge_records<HD, HEADS>(sm, DEC_WARPS, false, own, mo);
+        Q4_STAMP(3);
         cluster_sync_all();
+        Q4_STAMP(4);
         cluster_merge<HD, HEADS>((uint32_t)__cvta_generic_to_shared(own), S, cluster_ctarank(), mo);
+        Q4_STAMP(5);
         cluster_sync_all();
+        Q4_STAMP(6);
         return;
     }
     /* level 1: record per block; groups of DEC_GROUP blocks are merged by their last arrival,
@@ -1322,6 +1370,12 @@ bool q4i_xchg_merge(const q4_gpu_xchg *x, const float *gate, float *out) {
     }
     return q4i_fail(Q4E_ARG, "exchange merge: hd must be 32, 64, 128 or 256");
 }
+
+#ifdef Q4_DEC_TIMING
+extern "C" bool q4_dbg_fetch_stamps(unsigned long long *host, size_t n) {
+    return cudaMemcpyFromSymbol(host, q4_dbg_stamps, n * sizeof(unsigned long long)) == cudaSuccess;
+}
+#endif
 
 extern "C" bool q4_gpu_lse_merge(const float *parts, uint32_t n_parts, uint32_t n_head, uint32_t hd,
                                  const float *gate, float *out) {

@@ -43,7 +43,7 @@ struct q4_gpu_kv {
 struct Q4State {
     bool ok;
     int device, sm_count;
-    cudaStream_t own_stream, stream, copy_stream;
+    cudaStream_t own_stream, stream, copy_stream, down_stream;   /* compute, uploads, downloads */
     int capturing;
     int32_t *pos_d, *pos_h;
     uint32_t *err_d;             /* device-side sticky error bits */

@@ -76,6 +76,8 @@ extern "C" bool q4_hip_init(void) {
     g_q4.stream = g_q4.own_stream;
     if (cudaStreamCreateWithFlags(&g_q4.copy_stream, cudaStreamNonBlocking) != cudaSuccess)
         g_q4.copy_stream = nullptr;
+    if (cudaStreamCreateWithFlags(&g_q4.down_stream, cudaStreamNonBlocking) != cudaSuccess)
+        g_q4.down_stream = nullptr;
     if (cudaMalloc(&g_q4.pos_d, sizeof(int32_t)) != cudaSuccess) return false;
     if (cudaMemset(g_q4.pos_d, 0, sizeof(int32_t)) != cudaSuccess) return false;
     if (cudaMallocHost(&g_q4.pos_h, sizeof(int32_t) * 64) != cudaSuccess) return false;
@@ -95,6 +97,7 @@ extern "C" void q4_hip_shutdown(void) {
     if (g_q4.err_d) cudaFree(g_q4.err_d);
     if (g_q4.own_stream) cudaStreamDestroy(g_q4.own_stream);
     if (g_q4.copy_stream) cudaStreamDestroy(g_q4.copy_stream);
+    if (g_q4.down_stream) cudaStreamDestroy(g_q4.down_stream);
     memset(&g_q4, 0, sizeof(g_q4));
 }
 
@@ -176,6 +179,15 @@ extern "C" void q4_hip_copy_wait(void) {
     else (void)cudaDeviceSynchronize();
 }
 extern "C" void *q4_gpu_copy_stream(void) { return g_q4.ok ? (void *)g_q4.copy_stream : nullptr; }
+/* Results back to the host on a third stream, so that a download uses the device-to-host copy engine
+ * while the next step computes and the step after uploads.  Ordered by the caller with events on
+ * q4_gpu_download_stream(). */
+extern "C" bool q4_gpu_copy_d2h(void *dst, const void *src, size_t n) {
+    if (!g_q4.ok || !dst || !src || !n) return false;
+    cudaStream_t st = g_q4.down_stream ? g_q4.down_stream : g_q4.stream;
+    return q4i_check(cudaMemcpyAsync(dst, src, n, cudaMemcpyDeviceToHost, st), "copy_d2h");
+}
+extern "C" void *q4_gpu_download_stream(void) { return g_q4.ok ? (void *)g_q4.down_stream : nullptr; }
 extern "C" bool q4_hip_stream_sync(void) {
     if (!g_q4.ok) return false;
     return q4i_check(cudaStreamSynchronize(g_q4.stream), "stream_sync");
