@@ -290,6 +290,16 @@ bool q4_gpu_batch_decode(q4_gpu_batch *b, uint32_t layer, const void *q, int q_b
                          const float *gate, float *out, const int32_t *idx, uint32_t width,
                          uint32_t idx_kvh_stride, uint32_t idx_sess_stride, uint32_t n_head,
                          float scale);
+/* q4_gpu_batch_append then q4_gpu_batch_decode as one call; on a q8_0 store at hd 128 it is one launch per layer
+ * (the attention kernel quantises and stores each session's newest K/V row itself, same bytes as the
+ * append).  k, v: [n_sessions][n_kvh*hd] fp32.  Replaces the pair src/q4_fwd.c:891 + :922. */
+bool q4_gpu_batch_append_decode(q4_gpu_batch *b, uint32_t layer, const float *k, const float *v, const void *q,
+                                int q_bf16, const float *gate, float *out, const int32_t *idx, uint32_t width,
+                                uint32_t idx_kvh_stride, uint32_t idx_sess_stride, uint32_t n_head, float scale);
+/* Same for one session at the device position word (q4_gpu_kv_append_d + q4_gpu_kv_decode with n_kv = 0). */
+bool q4_gpu_kv_append_decode_d(q4_gpu_kv *kv, uint32_t layer, const float *k, const float *v, const void *q,
+                               int q_bf16, const float *gate, float *out, uint32_t n_head, const int32_t *idx,
+                               uint32_t width, uint32_t idx_kvh_stride, float scale);
 
 /* ---- dense causal prefill attention on the tensor cores (tcgen05 / TMEM): query t of the chunk
  * attends rows [0, kv_base + t + 1) of the store.  q, out: [n_tok][n_head][hd] bf16; gate: fp32 or

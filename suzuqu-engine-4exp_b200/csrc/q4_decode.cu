@@ -70,6 +70,7 @@ struct DecParams {
     uint32_t *err;
     const Q4XchgDev *xchg;   /* sequence-sharded decode: exchange window (null otherwise) */
     uint32_t xchg_phase;
+    const float *new_k, *new_v;   /* fused append of the newest row (native q8_0 store), or null */
 };
 
 /* ---- small device helpers ---------------------------------------------------------------- */
@@ -519,7 +520,8 @@ q4_decode_k(const DecParams P) {
     const uint32_t S = P.S;
 
     const Q4Cache C = P.many ? *P.many[u] : P.one;
-    uint32_t n_kv = (P.pos ? (uint32_t)P.pos[P.many ? u : 0] : P.kv_base + u) + 1u;
+    const uint32_t newest = P.pos ? (uint32_t)P.pos[P.many ? u : 0] : P.kv_base + u;
+    uint32_t n_kv = newest + 1u;
     if (n_kv > C.max_kv) n_kv = C.max_kv;
     const int32_t *list = P.idx ? P.idx + (size_t)u * P.idx_unit_stride + (size_t)kh * P.idx_kvh_stride
                                 : nullptr;
@@ -536,6 +538,34 @@ q4_decode_k(const DecParams P) {
         sbase = C.s + (uint64_t)P.layer * C.s_layer_stride + (uint64_t)kh * C.s_kvh_stride;
     const uint32_t tok_stride = C.tok_stride, s_tok_stride = C.s_tok_stride;
     const uint32_t max_kv = C.max_kv;
+
+    /* ---- fused append: the newest row of this (session, kv head) is quantised and stored here, by
+     * every split of the unit (identical bytes), before any row is read: a block's own stores are ordered
+     * before its later reads by the barrier, so no split depends on another block having written.  8
+     * lanes per 32-value block, the first hd/4 threads take the K row and the next hd/4 the V row. */
+    if constexpr (Cfg::STAGED) {   /* rows are read with cp.async (coherent at L2), never through the read-only path */
+        if (P.new_k) {
+            constexpr uint32_t QL = HD / 4;
+            const uint32_t tid = threadIdx.x;
+            const bool which = tid >= QL, live = tid < 2 * QL && newest < max_kv;
+            const uint32_t w = which ? tid - QL : tid, b = w >> 3, sub = w & 7u;
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (live)
+                x = *reinterpret_cast<const float4 *>((which ? P.new_v : P.new_k) +
+                                                      ((size_t)u * P.n_kvh + kh) * HD + b * 32 + sub * 4);
+            float d, id;
+            q4d_block_scale(x, d, id);
+            if (live) {
+                uint8_t *row = const_cast<uint8_t *>(which ? vbase : kbase) + (uint64_t)newest * tok_stride;
+                *reinterpret_cast<uint32_t *>(row + b * 32 + sub * 4) = q4d_quant4(x, id);
+                if (sub == 0)
+                    reinterpret_cast<__half *>(const_cast<uint8_t *>(sbase) + (uint64_t)newest * s_tok_stride)[(which ? NB : 0) + b] =
+                        __float2half_rn(d);
+            }
+            if (newest >= max_kv && tid == 0) atomicOr(P.err, (uint32_t)Q4E_RANGE);
+            __syncthreads();
+        }
+    }
 
     /* position j of the list / range, or -1 (padding, out of range) */
     auto position = [&](uint32_t j) -> int32_t {
@@ -1342,6 +1372,11 @@ bool q4i_decode(const Q4DecodeArgs &a) {
     p.err = g_q4.err_d;
     p.xchg = a.xchg;
     p.xchg_phase = (uint32_t)a.xchg_phase;
+    p.new_k = a.new_k;
+    p.new_v = a.new_v;
+    if (a.new_k || a.new_v)
+        Q4_REQUIRE(a.new_k && a.new_v && a.layout == LAY_Q8P && a.hd == 128,
+                   "decode: fused append needs both rows and the native q8_0 store at hd 128");
     dim3 grid(S, a.n_kvh, a.n_units);
     switch (a.layout) {
     case LAY_F32: return launch_hd<LAY_F32>(p, grid, a.hd);

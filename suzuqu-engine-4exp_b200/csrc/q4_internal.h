@@ -66,6 +66,30 @@ bool q4i_scratch(size_t part_floats, size_t n_counters); /* grows outside captur
         if (!(cond)) return q4i_fail(Q4E_ARG, what); \
     } while (0)
 
+#ifdef __CUDACC__
+/* ---- the q8_0 quantiser, one copy for every kernel that writes a cache row.  8 lanes share a block
+ * of 32 values (4 each): d = amax / 127 and id = 1 / d as IEEE fp32 divisions, codes =
+ * clamp(rint(x * id), +-127), stored scale = fp16(d) (quantize_row_q8_0's arithmetic,
+ * src/q4_quant.c / src/q4_rocm.cu f32_to_q8 kernels). */
+__device__ __forceinline__ uint32_t q4d_quant4(const float4 x, float id) {
+    int q0 = __float2int_rn(__fmul_rn(x.x, id)), q1 = __float2int_rn(__fmul_rn(x.y, id));
+    int q2 = __float2int_rn(__fmul_rn(x.z, id)), q3 = __float2int_rn(__fmul_rn(x.w, id));
+    q0 = max(-127, min(127, q0)); q1 = max(-127, min(127, q1));
+    q2 = max(-127, min(127, q2)); q3 = max(-127, min(127, q3));
+    return (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
+           ((uint32_t)(q3 & 0xff) << 24);
+}
+/* amax over the 8 lanes that share a block (all 32 lanes of the warp must call), then d and 1/d */
+__device__ __forceinline__ void q4d_block_scale(const float4 x, float &d, float &id) {
+    float a = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
+    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
+    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
+    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 4));
+    d = __fdiv_rn(a, 127.f);
+    id = d > 0.f ? __fdiv_rn(1.f, d) : 0.f;
+}
+#endif
+
 /* ---- record exchange between the ranks of a sequence-sharded decode -----------------------------
  * Every rank owns one window in its own memory that all peers can write.  It starts with this header;
  * the records follow at XCHG_REC_OFFSET: float rec[2][units][world][slot_floats], one slot per
@@ -120,6 +144,9 @@ struct Q4DecodeArgs {
      * (XCHG_FUSED) wait for theirs and write the merged output; null = single-rank decode */
     const Q4XchgDev *xchg;
     int xchg_phase;
+    /* fused append (native q8_0 store only): the new K and V rows [unit][n_kvh*hd] (fp32) are quantised
+     * and stored at each unit's position by the attention kernel itself before it reads the cache */
+    const float *new_k, *new_v;
 };
 bool q4i_decode(const Q4DecodeArgs &a);
 

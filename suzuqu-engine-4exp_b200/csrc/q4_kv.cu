@@ -29,23 +29,6 @@ struct AppendParams {
     uint32_t *err;
 };
 
-__device__ __forceinline__ uint32_t quant4(const float4 x, float id) {
-    int q0 = __float2int_rn(__fmul_rn(x.x, id)), q1 = __float2int_rn(__fmul_rn(x.y, id));
-    int q2 = __float2int_rn(__fmul_rn(x.z, id)), q3 = __float2int_rn(__fmul_rn(x.w, id));
-    q0 = max(-127, min(127, q0)); q1 = max(-127, min(127, q1));
-    q2 = max(-127, min(127, q2)); q3 = max(-127, min(127, q3));
-    return (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
-           ((uint32_t)(q3 & 0xff) << 24);
-}
-/* amax over the 8 lanes that share a block, then d and 1/d exactly as the reference writes them */
-__device__ __forceinline__ void block_scale(const float4 x, float &d, float &id) {
-    float a = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
-    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
-    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
-    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 4));
-    d = __fdiv_rn(a, 127.f);
-    id = d > 0.f ? __fdiv_rn(1.f, d) : 0.f;
-}
 __device__ __forceinline__ float4 load4(const float *p, bool aligned) {
     if (aligned) return *reinterpret_cast<const float4 *>(p);
     return make_float4(p[0], p[1], p[2], p[3]);
@@ -59,9 +42,9 @@ __global__ void q4_f32_to_q8_k(const float *src, uint8_t *dst, uint64_t nblocks,
     const bool live = b < nblocks;
     const float4 x = live ? load4(src + b * 32 + sub * 4, aligned) : make_float4(0.f, 0.f, 0.f, 0.f);
     float d, id;
-    block_scale(x, d, id);
+    q4d_block_scale(x, d, id);
     if (!live) return;
-    const uint32_t c = quant4(x, id);
+    const uint32_t c = q4d_quant4(x, id);
     uint8_t *o = dst + b * 34;
     if (sub == 0) *reinterpret_cast<__half *>(o) = __float2half_rn(d);
     uint16_t *cp = reinterpret_cast<uint16_t *>(o + 2 + sub * 4);
@@ -91,7 +74,7 @@ __global__ void q4_append_k(const AppendParams P) {
     if (live) x = *reinterpret_cast<const float4 *>((which ? P.v : P.k) + (size_t)r * P.n_kvh * P.hd +
                                                      (size_t)blk * 32 + sub * 4);
     float d = 0.f, id = 0.f;
-    if (LAY == LAY_Q8P || LAY == LAY_Q8R) block_scale(x, d, id);
+    if (LAY == LAY_Q8P || LAY == LAY_Q8R) q4d_block_scale(x, d, id);
     if (!live) return;
     const Q4Cache C = P.many ? *P.many[r] : P.one;
     const uint32_t p = P.pos ? (uint32_t)P.pos[P.many ? r : 0] + (P.many ? 0u : r) : P.pos0 + r;
@@ -102,14 +85,14 @@ __global__ void q4_append_k(const AppendParams P) {
     uint8_t *row = const_cast<uint8_t *>(which ? C.v : C.k) + (uint64_t)P.layer * C.layer_stride +
                    (uint64_t)kh * C.kvh_stride + (uint64_t)p * C.tok_stride;
     if (LAY == LAY_Q8P) {
-        *reinterpret_cast<uint32_t *>(row + b * 32 + sub * 4) = quant4(x, id);
+        *reinterpret_cast<uint32_t *>(row + b * 32 + sub * 4) = q4d_quant4(x, id);
         if (sub == 0) {
             uint8_t *srow = const_cast<uint8_t *>(C.s) + (uint64_t)P.layer * C.s_layer_stride +
                             (uint64_t)kh * C.s_kvh_stride + (uint64_t)p * C.s_tok_stride;
             reinterpret_cast<__half *>(srow)[(which ? nb : 0u) + b] = __float2half_rn(d);
         }
     } else if (LAY == LAY_Q8R) {
-        const uint32_t c = quant4(x, id);
+        const uint32_t c = q4d_quant4(x, id);
         uint8_t *o = row + b * 34;
         if (sub == 0) *reinterpret_cast<__half *>(o) = __float2half_rn(d);
         uint16_t *cp = reinterpret_cast<uint16_t *>(o + 2 + sub * 4);
@@ -588,6 +571,59 @@ extern "C" bool q4_gpu_batch_decode(q4_gpu_batch *b, uint32_t layer, const void 
     a.pos = b->pos_d;
     a.hint_rows = b->max_pos + 1;
     a.scale = scale;
+    return q4i_decode(a);
+}
+
+/* Append + attend in one call.  On the native q8_0 store this is ONE launch per layer: the attention
+ * kernel quantises and stores the newest rows itself; other kinds run the append kernel first. */
+extern "C" bool q4_gpu_batch_append_decode(q4_gpu_batch *b, uint32_t layer, const float *k, const float *v, const void *q,
+                                           int q_bf16, const float *gate, float *out, const int32_t *idx, uint32_t width,
+                                           uint32_t idx_kvh_stride, uint32_t idx_sess_stride, uint32_t n_head, float scale) {
+    if (!g_q4.ok) return q4i_fail(Q4E_INIT, "batch_append_decode: library not initialised");
+    Q4_REQUIRE(b && b->n && k && v && q && out && b->kv[0] && layer < b->kv[0]->n_layers && n_head,
+               "batch_append_decode: bad argument");
+    const bool fused = b->kv[0]->kind == Q4K_Q8 && b->kv[0]->hd == 128;
+    if (!fused && !q4_gpu_batch_append(b, layer, k, v)) return false;
+    Q4DecodeArgs a;
+    memset(&a, 0, sizeof(a));
+    a.many = b->d_views;
+    a.layout = store_layout(b->kv[0]->kind);
+    a.layer = layer;
+    a.n_units = b->n;
+    a.n_head = n_head;
+    a.n_kvh = b->kv[0]->n_kvh;
+    a.hd = b->kv[0]->hd;
+    a.q = q; a.q_bf16 = q_bf16; a.gate = gate; a.out = out;
+    a.idx = idx; a.width = width; a.idx_kvh_stride = idx_kvh_stride; a.idx_unit_stride = idx_sess_stride;
+    a.pos = b->pos_d;
+    a.hint_rows = b->max_pos + 1;
+    a.scale = scale;
+    if (fused) { a.new_k = k; a.new_v = v; }
+    return q4i_decode(a);
+}
+/* Single session, position from the device position word (graph-captured decode). */
+extern "C" bool q4_gpu_kv_append_decode_d(q4_gpu_kv *kv, uint32_t layer, const float *k, const float *v, const void *q,
+                                          int q_bf16, const float *gate, float *out, uint32_t n_head, const int32_t *idx,
+                                          uint32_t width, uint32_t idx_kvh_stride, float scale) {
+    if (!g_q4.ok) return q4i_fail(Q4E_INIT, "kv_append_decode_d: library not initialised");
+    Q4_REQUIRE(kv && k && v && q && out && layer < kv->n_layers && n_head, "kv_append_decode_d: bad argument");
+    const bool fused = kv->kind == Q4K_Q8 && kv->hd == 128;
+    if (!fused && !q4_gpu_kv_append_d(kv, layer, k, v)) return false;
+    Q4DecodeArgs a;
+    memset(&a, 0, sizeof(a));
+    a.one = kv->view;
+    a.layout = store_layout(kv->kind);
+    a.layer = layer;
+    a.n_units = 1;
+    a.n_head = n_head;
+    a.n_kvh = kv->n_kvh;
+    a.hd = kv->hd;
+    a.q = q; a.q_bf16 = q_bf16; a.gate = gate; a.out = out;
+    a.idx = idx; a.width = width; a.idx_kvh_stride = idx_kvh_stride;
+    a.pos = g_q4.pos_d;
+    a.hint_rows = kv->max_kv;
+    a.scale = scale;
+    if (fused) { a.new_k = k; a.new_v = v; }
     return q4i_decode(a);
 }
 

@@ -136,22 +136,13 @@ __global__ void q4_prep_append_k(const PrepAppendParams P) {
     const uint32_t nb = P.hd / 32u, sub = threadIdx.x & 7u, b = threadIdx.x >> 3;
     const bool live = b < nb;
     const float4 x = live ? *reinterpret_cast<const float4 *>(row_s + b * 32 + sub * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-    float a = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
-    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
-    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
-    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 4));
+    float d, id;
+    q4d_block_scale(x, d, id);
     if (!live) return;
     uint8_t *row = const_cast<uint8_t *>(which ? P.C.v : P.C.k) + (uint64_t)P.layer * P.C.layer_stride +
                    (uint64_t)kh * P.C.kvh_stride + (uint64_t)pos * P.C.tok_stride;
     if (P.layout == LAY_Q8P) {
-        const float d = __fdiv_rn(a, 127.f);
-        const float id = d > 0.f ? __fdiv_rn(1.f, d) : 0.f;
-        int q0 = __float2int_rn(__fmul_rn(x.x, id)), q1 = __float2int_rn(__fmul_rn(x.y, id));
-        int q2 = __float2int_rn(__fmul_rn(x.z, id)), q3 = __float2int_rn(__fmul_rn(x.w, id));
-        q0 = max(-127, min(127, q0)); q1 = max(-127, min(127, q1));
-        q2 = max(-127, min(127, q2)); q3 = max(-127, min(127, q3));
-        *reinterpret_cast<uint32_t *>(row + b * 32 + sub * 4) =
-            (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
+        *reinterpret_cast<uint32_t *>(row + b * 32 + sub * 4) = q4d_quant4(x, id);
         if (sub == 0) {
             uint8_t *srow = const_cast<uint8_t *>(P.C.s) + (uint64_t)P.layer * P.C.s_layer_stride +
                             (uint64_t)kh * P.C.s_kvh_stride + (uint64_t)pos * P.C.s_tok_stride;

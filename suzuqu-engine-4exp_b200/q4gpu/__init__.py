@@ -72,6 +72,8 @@ SIGNATURES = {
     "q4_gpu_batch_bind": (_b, [_v, _u32, _v]), "q4_gpu_batch_set_pos": (_b, [_v, _v, _u32]),
     "q4_gpu_batch_append": (_b, [_v, _u32, _v, _v]),
     "q4_gpu_batch_decode": (_b, [_v, _u32, _v, _i, _v, _v, _v, _u32, _u32, _u32, _u32, _f]),
+    "q4_gpu_batch_append_decode": (_b, [_v, _u32, _v, _v, _v, _i, _v, _v, _v, _u32, _u32, _u32, _u32, _f]),
+    "q4_gpu_kv_append_decode_d": (_b, [_v, _u32, _v, _v, _v, _i, _v, _v, _u32, _v, _u32, _u32, _f]),
 }
 
 _lib = None
@@ -193,6 +195,13 @@ class KVStore:
         check(self.L.q4_gpu_kv_prefill(self.h, layer, _ptr(q_bf16), _ptr(gate), _ptr(out_bf16), n_head, n_tok,
                                        kv_base, scale), "q4_gpu_kv_prefill")
 
+    def append_decode_d(self, layer, k, v, q, out, n_head, scale, gate=None, idx=None, width=0, idx_kvh_stride=0,
+                        q_bf16=False):
+        """append at the device position word + decode over rows [0, position] in one call"""
+        check(self.L.q4_gpu_kv_append_decode_d(self.h, layer, _ptr(k), _ptr(v), _ptr(q), int(q_bf16), _ptr(gate),
+                                               _ptr(out), n_head, _ptr(idx), width, idx_kvh_stride, scale),
+              "q4_gpu_kv_append_decode_d")
+
     def decode_partial(self, layer, q, part, n_head, scale, idx=None, width=0, idx_kvh_stride=0, n_kv=0,
                        q_bf16=False):
         check(self.L.q4_gpu_kv_decode_partial(self.h, layer, _ptr(q), int(q_bf16), _ptr(part), n_head,
@@ -286,3 +295,10 @@ class Batch:
         check(self.L.q4_gpu_batch_decode(self.h, layer, _ptr(q), int(q_bf16), _ptr(gate), _ptr(out), _ptr(idx),
                                          width, idx_kvh_stride, idx_sess_stride, n_head, scale),
               "q4_gpu_batch_decode")
+
+    def append_decode(self, layer, k, v, q, out, n_head, scale, gate=None, idx=None, width=0, idx_kvh_stride=0,
+                      idx_sess_stride=0, q_bf16=False):
+        """append + decode in one call (one launch per layer on a q8_0 store at hd 128)"""
+        check(self.L.q4_gpu_batch_append_decode(self.h, layer, _ptr(k), _ptr(v), _ptr(q), int(q_bf16), _ptr(gate),
+                                                _ptr(out), _ptr(idx), width, idx_kvh_stride, idx_sess_stride,
+                                                n_head, scale), "q4_gpu_batch_append_decode")
