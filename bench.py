@@ -581,9 +581,9 @@ def run_seqshard(args, torch, q4gpu, L, dist, rank, world, peak_gbs):
     if rank == 0:
         print(json.dumps({"metric": "dense_decode_us_per_layer_ctx262144", "mode": "seqshard", "n_gpus": world,
                           "steps": args.steps,
-                          "exchange": "in-kernel: peer stores of %d B per peer per layer + epoch flags over NVLink; "
-                                      "us_per_layer_nccl_allgather is the same step with an NCCL all-gather + merge kernel"
-                                      % (N_HEAD * (HD + 4) * 4),
+                          "exchange": "in-kernel: %d B of {value, epoch} packets stored per peer per layer over NVLink, "
+                                      "polled and merged by the same launch; us_per_layer_nccl_allgather is the same step "
+                                      "with an NCCL all-gather + merge kernel" % (N_HEAD * (HD + 4) * 8),
                           "result": res}), flush=True)
 
 

@@ -250,7 +250,8 @@ bool q4_gpu_lse_merge(const float *parts, uint32_t n_parts, uint32_t n_head, uin
  * (it runs one GPU); the merge is gqa_dec_comb_k's (src/q4_rocm.cu:6968-7012), taken across GPUs.
  * Every rank of a node owns the rows [b, e) of one context in a store of its own and an exchange
  * window; q4_gpu_kv_decode_xchg attends the local rows, stores the rank's (acc, m, l) record into
- * every peer's window over NVLink, waits (bounded) for the peers' records and writes the merged,
+ * every peer's window over NVLink (8-byte packets that carry the call's epoch, so no fence or flag
+ * follows them), polls (bounded) for the peers' records in its own window and writes the merged,
  * gated output on every rank: one launch per layer, no host round trip, no collective library.
  *   create   : rank/world <= 16, n_kvh <= 16; allocates the window (cudaMalloc) and clears it.
  *   handle   : the 64-byte CUDA IPC handle of the local window, to be sent to every peer once.

@@ -63,7 +63,7 @@ struct DecParams {
     uint32_t kv_base;
     float scale_log2e;
     uint32_t S;
-    uint32_t cluster; /* 1: the splits of a unit form one thread-block cluster and merge through DSMEM */
+    uint32_t cluster; /* blocks per cluster (0 = none): the S splits of a unit form one cluster and merge through DSMEM */
     uint32_t debug;   /* measurement aid: 1 = copy the tiles but skip the arithmetic */
     float *scratch;
     uint32_t *counters;
@@ -71,6 +71,7 @@ struct DecParams {
     const Q4XchgDev *xchg;   /* sequence-sharded decode: exchange window (null otherwise) */
     uint32_t xchg_phase;
     const float *new_k, *new_v;   /* fused append of the newest row (native q8_0 store), or null */
+    uint32_t pdl;                 /* launched with programmatic stream serialization */
 };
 
 /* ---- small device helpers ---------------------------------------------------------------- */
@@ -306,7 +307,9 @@ __device__ __forceinline__ float ld_cluster(uint32_t a) {
 /* When the splits of a unit are the blocks of one cluster (at most 8), every block leaves its record
  * in its own shared memory and block r merges heads r, r+S, .. by reading all S records through
  * distributed shared memory: no scratch, no atomics, no global round trips.  Called between two
- * cluster barriers (records complete before, nobody exits while peers still read after). */
+ * cluster barriers (records complete before, nobody exits while peers still read after).  (Clusters of 8
+ * as a first level under a merge in global memory were measured for units with hundreds of splits:
+ * slower than two levels in global memory, 53.8 vs 51.5 us at 262144 rows.) */
 template <int HD, int HEADS>
 __device__ __noinline__ void cluster_merge(uint32_t rec_saddr, uint32_t S, uint32_t rank, const MergeOut mo) {
     constexpr int REC = HD + 4;
@@ -357,83 +360,129 @@ __device__ __noinline__ void cluster_merge(uint32_t rec_saddr, uint32_t S, uint3
 }
 
 /* ---- exchange of the units' records between ranks (sequence-sharded decode) --------------------
- * The block that finishes a unit's last merge leaves the record in its own window, stores it into the
- * same slot of every peer's window (plain peer stores over NVLink), publishes it with one release
- * store of the call's epoch per peer, waits for the peers' epochs in its own window and merges the
- * `world` records into the output.  Slots and flags are double-buffered by the parity of the epoch:
- * a rank can be at most one call ahead of a peer, because it cannot finish call e+1 before the peer
- * has published e+1, which the peer does only after it finished reading call e.  Every wait is
- * bounded; when it runs out the status bit Q4E_PEER is set and the output is the rank's own part. */
+ * The block that finishes a unit's last merge holds the rank's record in shared memory.  It stores
+ * the record into slot (parity, unit, rank) of every rank's window, its own included, as 8-byte
+ * packets {fp32 value, epoch}: peer stores over NVLink, no fence and no separate flag, because a
+ * packet is written atomically and carries its own validity (the call's epoch).  It then reads all
+ * `world` records from its own window, polling each packet until the epoch matches, and merges
+ * them into the output.  Slots are double-buffered by the parity of the epoch: a rank can be at most
+ * one call ahead of a peer, because it cannot finish call e+1 before the peer has published e+1,
+ * which the peer does only after it has finished reading call e.  Every wait is bounded; when one
+ * runs out, status bit Q4E_PEER is set and the output is the rank's own part. */
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void *p) {
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_sys_v4(void *p, uint4 v) {
+    asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
-__device__ __forceinline__ float *xchg_slot(const Q4XchgDev *xd, Q4XchgWin *w, uint32_t par, uint32_t unit,
+/* packets of slot (parity, unit, writer) in window w */
+__device__ __forceinline__ uint2 *xchg_slot(const Q4XchgDev *xd, Q4XchgWin *w, uint32_t par, uint32_t unit,
                                             uint32_t writer) {
-    float *base = reinterpret_cast<float *>(reinterpret_cast<char *>(w) + XCHG_REC_OFFSET);
+    uint2 *base = reinterpret_cast<uint2 *>(reinterpret_cast<char *>(w) + XCHG_REC_OFFSET);
     return base + ((size_t)(par * xd->units + unit) * xd->world + writer) * xd->slot_floats;
-}
-/* where the unit's last merge leaves this rank's record for the call that is running */
-__device__ __noinline__ float *xchg_own_slot(const Q4XchgDev *xd, uint32_t unit) {
-    Q4XchgWin *w = xd->win[xd->rank];
-    const uint32_t epoch = __ldcg(&w->epoch[unit]) + 1u;
-    return xchg_slot(xd, w, epoch & 1u, unit, xd->rank);
 }
 template <int HD, int HEADS>
 __device__ __noinline__ void xchg_wait_merge(const Q4XchgDev *xd, uint32_t unit, uint32_t epoch, const MergeOut mo,
                                              uint32_t *err) {
+    constexpr int REC = HD + 4;
     __shared__ uint32_t s_missing;
     const uint32_t rank = xd->rank, world = xd->world, par = epoch & 1u;
     Q4XchgWin *w = xd->win[rank];
     if (threadIdx.x == 0) s_missing = 0u;
     __syncthreads();
-    if (threadIdx.x < world && threadIdx.x != rank) {
-        const uint32_t *f = &w->flags[par][unit][threadIdx.x];
-        const unsigned long long t0 = global_ns(), limit = xd->timeout_ns;
-        uint32_t polls = 0;
-        while ((int32_t)(ld_acquire_sys(f) - epoch) < 0) {
-            if (++polls < 64u) continue;
-            __nanosleep(100);
-            /* time limit, plus a poll limit in case the timer does not advance */
-            if ((polls & 255u) == 0u && (global_ns() - t0 > limit || polls > (1u << 26))) {
-                atomicOr(&s_missing, 1u << threadIdx.x);
-                break;
+    const unsigned long long t0 = global_ns(), limit = xd->timeout_ns;
+    /* pass 0 merges all ranks' records; pass 1 runs only after a wait ran out and merges this rank's alone */
+    for (int pass = 0; pass < 2; pass++) {
+        const bool alone = pass == 1;
+        const uint32_t n_src = alone ? 1u : world;
+        for (uint32_t i = threadIdx.x; i < mo.gqa * (HD / 4); i += DEC_THREADS) {
+            const uint32_t h = i / (HD / 4), d = (i % (HD / 4)) * 4;
+            float M = -CUDART_INF_F, L = 0.f;
+            float4 A = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (uint32_t s0 = 0; s0 < n_src; s0 += 4) {
+                uint4 pm[4], pa[4], pb[4];   /* {m, e, l, e}, {x0, e, x1, e}, {x2, e, x3, e} */
+                uint32_t polls = 0;
+                for (;;) {
+                    bool ok = true;
+#pragma unroll
+                    for (uint32_t k = 0; k < 4; k++) {
+                        const uint32_t src = alone ? rank : min(s0 + k, world - 1u);
+                        const uint2 *pk = xchg_slot(xd, w, par, unit, src) + (size_t)h * REC;
+                        pm[k] = ld_relaxed_sys_v4(pk + HD);
+                        pa[k] = ld_relaxed_sys_v4(pk + d);
+                        pb[k] = ld_relaxed_sys_v4(pk + d + 2);
+                    }
+#pragma unroll
+                    for (uint32_t k = 0; k < 4; k++)
+                        ok = ok && pm[k].y == epoch && pm[k].w == epoch && pa[k].y == epoch && pa[k].w == epoch &&
+                             pb[k].y == epoch && pb[k].w == epoch;
+                    if (ok) break;
+                    if (++polls > 32u) __nanosleep(100);
+                    /* time limit, plus a poll limit in case the timer does not advance */
+                    if ((polls & 63u) == 0u && (global_ns() - t0 > limit || polls > (1u << 24))) {
+                        atomicOr(&s_missing, 1u);
+                        break;
+                    }
+                }
+                if (!alone && s_missing) break;   /* this or another thread gave up: pass 1 redoes the item */
+                float Mn = M;
+#pragma unroll
+                for (uint32_t k = 0; k < 4; k++)
+                    if (s0 + k < n_src) Mn = fmaxf(Mn, __uint_as_float(pm[k].x));
+                const float Mu = Mn == -CUDART_INF_F ? 0.f : Mn;
+                const float c = ex2(M - Mu);   /* 0 for the first chunk (M = -inf) */
+                L *= c; A.x *= c; A.y *= c; A.z *= c; A.w *= c;
+#pragma unroll
+                for (uint32_t k = 0; k < 4; k++) {
+                    const float wgt = s0 + k < n_src ? ex2(__uint_as_float(pm[k].x) - Mu) : 0.f;
+                    L = fmaf(wgt, __uint_as_float(pm[k].z), L);
+                    A.x = fmaf(wgt, __uint_as_float(pa[k].x), A.x); A.y = fmaf(wgt, __uint_as_float(pa[k].z), A.y);
+                    A.z = fmaf(wgt, __uint_as_float(pb[k].x), A.z); A.w = fmaf(wgt, __uint_as_float(pb[k].z), A.w);
+                }
+                M = Mn;
             }
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            float4 o = make_float4(A.x * inv, A.y * inv, A.z * inv, A.w * inv);
+            const size_t off = (mo.row0 + h) * HD + d;
+            if (mo.gate) {
+                const float4 gt = *reinterpret_cast<const float4 *>(mo.gate + off);
+                o.x *= 1.f / (1.f + __expf(-gt.x)); o.y *= 1.f / (1.f + __expf(-gt.y));
+                o.z *= 1.f / (1.f + __expf(-gt.z)); o.w *= 1.f / (1.f + __expf(-gt.w));
+            }
+            *reinterpret_cast<float4 *>(mo.out + off) = o;
         }
+        __syncthreads();
+        if (!s_missing || alone) break;
+        if (threadIdx.x == 0) atomicOr(err, (uint32_t)Q4E_PEER);
     }
-    __syncthreads();
-    const bool alone = s_missing != 0u;
-    if (alone && threadIdx.x == 0) atomicOr(err, (uint32_t)Q4E_PEER);
-    merge_records<HD, HEADS>(xchg_slot(xd, w, par, unit, alone ? rank : 0u), alone ? 1u : world, true, nullptr, mo);
 }
+/* rec: the rank's merged record for the unit, [gqa][REC] floats in shared memory, complete (the merge
+ * that wrote it ends with a block barrier) */
 template <int HD, int HEADS>
-__device__ __noinline__ void xchg_finish(const Q4XchgDev *xd, uint32_t phase, uint32_t unit, const MergeOut mo,
-                                         uint32_t *err) {
+__device__ __noinline__ void xchg_finish(const Q4XchgDev *xd, uint32_t phase, uint32_t unit, const float *rec,
+                                         const MergeOut mo, uint32_t *err) {
     constexpr int REC = HD + 4;
     const uint32_t rank = xd->rank, world = xd->world;
     Q4XchgWin *w = xd->win[rank];
     const uint32_t epoch = __ldcg(&w->epoch[unit]) + 1u, par = epoch & 1u;
-    /* the merge that wrote the record ended with a block barrier: all of it is visible here */
-    const float4 *own = reinterpret_cast<const float4 *>(xchg_slot(xd, w, par, unit, rank));
-    const uint32_t n4 = mo.gqa * REC / 4;
-    for (uint32_t p = 0; p < world; p++) {
-        if (p == rank) continue;
-        float4 *dst = reinterpret_cast<float4 *>(xchg_slot(xd, xd->win[p], par, unit, rank));
-        for (uint32_t i = threadIdx.x; i < n4; i += DEC_THREADS) dst[i] = own[i];
+    const uint32_t n2 = mo.gqa * REC / 2;
+    for (uint32_t q = 0; q < world; q++) {
+        const uint32_t p = (rank + 1u + q) % world;   /* peers first, own window last */
+        uint4 *dst = reinterpret_cast<uint4 *>(xchg_slot(xd, xd->win[p], par, unit, rank));
+        for (uint32_t i = threadIdx.x; i < n2; i += DEC_THREADS) {
+            const float2 v = *reinterpret_cast<const float2 *>(rec + 2 * i);
+            st_relaxed_sys_v4(dst + i, make_uint4(__float_as_uint(v.x), epoch, __float_as_uint(v.y), epoch));
+        }
     }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x < world && threadIdx.x != rank)
-        st_release_sys(&xd->win[threadIdx.x]->flags[par][unit][rank], epoch);
+    __syncthreads();   /* every thread has read the old epoch before it changes */
     if (threadIdx.x == 0) w->epoch[unit] = epoch;
     if (phase == XCHG_PUSH) return;
     xchg_wait_merge<HD, HEADS>(xd, unit, epoch, mo, err);
@@ -520,6 +569,15 @@ q4_decode_k(const DecParams P) {
     const uint32_t S = P.S;
 
     const Q4Cache C = P.many ? *P.many[u] : P.one;
+    /* Programmatic dependent launch: the blocks of this launch may already be resident while the previous
+     * kernel of the stream drains.  Only the cache view above (written when the store was created or bound)
+     * is read before this point; positions, lists, queries and rows are read after it. */
+    if (P.pdl) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        /* the next launch of the stream may bring its blocks in as slots free up (it still waits, at its
+         * own griddepcontrol.wait, for this grid to finish before it reads anything this grid writes) */
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
     const uint32_t newest = P.pos ? (uint32_t)P.pos[P.many ? u : 0] : P.kv_base + u;
     uint32_t n_kv = newest + 1u;
     if (n_kv > C.max_kv) n_kv = C.max_kv;
@@ -1139,10 +1197,11 @@ q4_decode_k(const DecParams P) {
     mo.out = P.out; mo.part_out = P.part_out; mo.gate = P.gate;
     mo.row0 = (size_t)u * P.n_head + (size_t)kh * P.gqa;
     mo.gqa = P.gqa;
+    /* exchange mode: the unit's last merge leaves this rank's record here instead of finalising */
+    float *fin = P.xchg ? reinterpret_cast<float *>(smem_raw + Cfg::EPI_BYTES) : nullptr;
     if (S == 1) {
-        float *fin = P.xchg ? xchg_own_slot(P.xchg, (uint32_t)unit) : nullptr;
         merge_records<HD, HEADS>(sm, DEC_WARPS, false, fin, mo);
-        if (fin) xchg_finish<HD, HEADS>(P.xchg, P.xchg_phase, (uint32_t)unit, mo, P.err);
+        if (fin) xchg_finish<HD, HEADS>(P.xchg, P.xchg_phase, (uint32_t)unit, fin, mo, P.err);
         return;
     }
     if (P.cluster) {
@@ -1175,8 +1234,9 @@ q4_decode_k(const DecParams P) {
     bool last = false;
     for (int level = 0;; level++) {
         merge_records<HD, HEADS>(src, count, global, dst, mo);
+        Q4_STAMP(3 + level);
         if (last) {                                        /* finalised, or this rank's record is complete */
-            if (P.xchg) xchg_finish<HD, HEADS>(P.xchg, P.xchg_phase, (uint32_t)unit, mo, P.err);
+            if (fin) xchg_finish<HD, HEADS>(P.xchg, P.xchg_phase, (uint32_t)unit, fin, mo, P.err);
             return;
         }
         if (!arrive_last(arrive, expected)) return;        /* someone else carries on */
@@ -1194,7 +1254,7 @@ q4_decode_k(const DecParams P) {
             last = true;
             dst = nullptr;
         }
-        if (last && P.xchg) dst = xchg_own_slot(P.xchg, (uint32_t)unit);
+        if (last) dst = fin;
     }
 }
 
@@ -1236,24 +1296,29 @@ bool launch(const DecParams &p, dim3 grid) {
             return false;
     }
     attr_done = true;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(DEC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = g_q4.stream;
+    cudaLaunchAttribute at[2];
+    unsigned n_at = 0;
     if (p.cluster) {
-        cudaLaunchConfig_t cfg;
-        memset(&cfg, 0, sizeof(cfg));
-        cfg.gridDim = grid;
-        cfg.blockDim = dim3(DEC_THREADS);
-        cfg.dynamicSmemBytes = smem;
-        cfg.stream = g_q4.stream;
-        cudaLaunchAttribute at[1];
-        at[0].id = cudaLaunchAttributeClusterDimension;
-        at[0].val.clusterDim.x = grid.x;
-        at[0].val.clusterDim.y = 1;
-        at[0].val.clusterDim.z = 1;
-        cfg.attrs = at;
-        cfg.numAttrs = 1;
-        return q4i_check(cudaLaunchKernelEx(&cfg, q4_decode_k<LAY, HD, NHT>, p), "decode cluster launch");
+        at[n_at].id = cudaLaunchAttributeClusterDimension;
+        at[n_at].val.clusterDim.x = p.cluster;
+        at[n_at].val.clusterDim.y = 1;
+        at[n_at].val.clusterDim.z = 1;
+        n_at++;
     }
-    q4_decode_k<LAY, HD, NHT><<<grid, DEC_THREADS, smem, g_q4.stream>>>(p);
-    return q4i_check(cudaGetLastError(), "decode launch");
+    if (p.pdl) {
+        at[n_at].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[n_at].val.programmaticStreamSerializationAllowed = 1;
+        n_at++;
+    }
+    cfg.attrs = at;
+    cfg.numAttrs = n_at;
+    return q4i_check(cudaLaunchKernelEx(&cfg, q4_decode_k<LAY, HD, NHT>, p), "decode launch");
 }
 template <int LAY, int HD>
 bool launch_nht(const DecParams &p, dim3 grid) {
@@ -1315,11 +1380,11 @@ bool q4i_decode(const Q4DecodeArgs &a) {
         const char *e = getenv("Q4_DEC_CLUSTER");
         use_cluster = e ? atoi(e) : 1;
     }
-    bool cluster = false;
+    uint32_t cluster = 0;   /* blocks per cluster; 0 = plain launch with the merge in global memory */
     if (a.xchg) Q4_REQUIRE(a.n_units == 1 && a.out && !a.part_out && !a.many, "decode: exchange mode is for one token of one session");
     if (use_cluster && !a.scratch_part && !a.xchg && (S <= 8 || steps <= 512)) {
         if (S > 8) S = 8;
-        cluster = S > 1;
+        cluster = S > 1 ? S : 0u;
     }
 
     if (a.scratch_part && a.scratch_clamp) {
@@ -1336,7 +1401,7 @@ bool q4i_decode(const Q4DecodeArgs &a) {
         if ((S > 1 && a.scratch_part_floats < need_part) || a.scratch_n_counters < need_ctr)
             return q4i_fail(Q4E_SCRATCH, "decode: caller scratch too small");
     } else {
-        if (!q4i_scratch(S > 1 && !cluster ? need_part : 0, need_ctr)) return false;
+        if (!q4i_scratch(S > 1 && cluster != S ? need_part : 0, need_ctr)) return false;
         scratch = g_q4.part;
         counters = g_q4.counters;
     }
@@ -1361,7 +1426,7 @@ bool q4i_decode(const Q4DecodeArgs &a) {
     p.kv_base = a.kv_base;
     p.scale_log2e = a.scale * 1.4426950408889634f;
     p.S = S;
-    p.cluster = cluster ? 1u : 0u;
+    p.cluster = cluster;
     {
         static int dbg = -1;
         if (dbg < 0) { const char *e = getenv("Q4_DEC_DEBUG"); dbg = e ? atoi(e) : 0; }
@@ -1374,6 +1439,12 @@ bool q4i_decode(const Q4DecodeArgs &a) {
     p.xchg_phase = (uint32_t)a.xchg_phase;
     p.new_k = a.new_k;
     p.new_v = a.new_v;
+    {
+        /* Q4_DEC_PDL=0 switches programmatic dependent launch off */
+        static int pdl = -1;
+        if (pdl < 0) { const char *e = getenv("Q4_DEC_PDL"); pdl = e ? atoi(e) : 1; }
+        p.pdl = pdl ? 1u : 0u;
+    }
     if (a.new_k || a.new_v)
         Q4_REQUIRE(a.new_k && a.new_v && a.layout == LAY_Q8P && a.hd == 128,
                    "decode: fused append needs both rows and the native q8_0 store at hd 128");
@@ -1407,6 +1478,10 @@ bool q4i_xchg_merge(const q4_gpu_xchg *x, const float *gate, float *out) {
 }
 
 #ifdef Q4_DEC_TIMING
+extern "C" bool q4_dbg_clear_stamps(void) {
+    void *p = nullptr;
+    return cudaGetSymbolAddress(&p, q4_dbg_stamps) == cudaSuccess && cudaMemset(p, 0, sizeof(q4_dbg_stamps)) == cudaSuccess;
+}
 extern "C" bool q4_dbg_fetch_stamps(unsigned long long *host, size_t n) {
     return cudaMemcpyFromSymbol(host, q4_dbg_stamps, n * sizeof(unsigned long long)) == cudaSuccess;
 }

@@ -92,14 +92,14 @@ __device__ __forceinline__ void q4d_block_scale(const float4 x, float &d, float 
 
 /* ---- record exchange between the ranks of a sequence-sharded decode -----------------------------
  * Every rank owns one window in its own memory that all peers can write.  It starts with this header;
- * the records follow at XCHG_REC_OFFSET: float rec[2][units][world][slot_floats], one slot per
- * (parity of the call count, unit = kv head, writing rank), each slot the kernel's internal record
- * layout for the unit's heads: {acc[hd], m (log2 units, scale folded in), l, 2 pad} per head. */
+ * the records follow at XCHG_REC_OFFSET: packet rec[2][units][world][slot_floats], one slot per
+ * (parity of the call count, unit = kv head, writing rank).  A slot is the kernel's internal record
+ * for the unit's heads, {acc[hd], m (log2 units, scale folded in), l, 2 pad} per head, each fp32
+ * value stored as an 8-byte packet {value, epoch of the call that wrote it}. */
 constexpr uint32_t XCHG_MAX_WORLD = 16, XCHG_MAX_UNITS = 16;
 constexpr size_t XCHG_REC_OFFSET = 4096;
 struct Q4XchgWin {
     uint32_t epoch[XCHG_MAX_UNITS];                       /* calls completed by the owner, per unit */
-    uint32_t flags[2][XCHG_MAX_UNITS][XCHG_MAX_WORLD];    /* [parity][unit][writer] = epoch of the record in the slot */
 };
 /* who and where, in the owner's device memory (never written by peers) */
 struct Q4XchgDev {

@@ -38,7 +38,7 @@ extern "C" q4_gpu_xchg *q4_gpu_xchg_create(uint32_t rank, uint32_t world, uint32
     x->host.rank = rank; x->host.world = world; x->host.units = n_kvh;
     x->host.slot_floats = heads * (hd + 4);
     x->host.timeout_ns = 2000ull * 1000ull * 1000ull;
-    x->win_bytes = XCHG_REC_OFFSET + (size_t)2 * n_kvh * world * x->host.slot_floats * sizeof(float);
+    x->win_bytes = XCHG_REC_OFFSET + (size_t)2 * n_kvh * world * x->host.slot_floats * 8u;   /* 8-byte packets */
     bool ok = cudaMalloc(&x->win, x->win_bytes) == cudaSuccess && cudaMalloc(&x->dev, sizeof(Q4XchgDev)) == cudaSuccess &&
               cudaMemset(x->win, 0, x->win_bytes) == cudaSuccess;
     if (ok) {
