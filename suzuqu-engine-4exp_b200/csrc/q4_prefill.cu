@@ -1,28 +1,37 @@
 /*
  * Dense causal prefill attention over the native q8_0 store on the 5th-generation tensor cores
- * (tcgen05.mma, accumulators in tensor memory).  Query t of the chunk attends rows
- * [0, min(kv_base + t + 1, max_kv)) -- the semantics of gqa_prefill_k (src/q4_rocm.cu:7019-7206) as
- * launched by q4_hip_qsa_decode_n with n_tok > 1 (:7263,7286-7298); the reference computes it with
- * scalar FMAs on an fp16 tile and re-dequantises every K/V tile for every query token.
+ * (tcgen05.mma, accumulators in tensor memory, operands brought in by TMA).  Query t of the chunk
+ * attends rows [0, min(kv_base + t + 1, max_kv)) -- the semantics of gqa_prefill_k
+ * (src/q4_rocm.cu:7019-7206) as launched by q4_hip_qsa_decode_n with n_tok > 1 (:7263,7286-7298);
+ * the reference computes it with scalar FMAs on an fp16 tile and re-dequantises every K/V tile for
+ * every query token.
  *
- * One block = one kv head x a group of query tokens whose (token, head) pairs fill the 128 rows
- * of the MMA (16 tokens x 8 heads at the benchmark shape), so every dequantised K/V tile is shared
- * by the whole GQA group and by 16 tokens.  Per 64-position tile:
+ * Two launches per call:
  *
- *   all 4 warps : int8 codes + fp16 block scales (prefetched into registers one tile ahead)
- *                 -> fp16 (exact integer via the magic-number trick, times the scale, as the reference's
- *                 fp16 tile) -> shared memory in the K-major 128-byte-swizzled operand layout; V is
- *                 transposed on the way so that both products read K-major operands
- *   one thread  : S[128 x 64]  = Q . K^T      8 x tcgen05.mma (k = 16), fp32 in tensor memory
- *   all 4 warps : thread r owns row r: tcgen05.ld its 64 scores, causal mask, running max with lazy
- *                 rescale (the stored max only moves when it would grow by more than 2^8, so the
- *                 O accumulator in tensor memory is rarely touched), P = exp2(..) as fp16 -> shared
- *   one thread  : O[128 x 128] += P . V        4 x tcgen05.mma
+ *  1. q4_pf_stage_k dequantises the rows the chunk can see, once, into two fp16 staging tensors in
+ *     device memory: K as [kv head][row][128] and V transposed as [kv head][dim][row] (value =
+ *     fp16(code * scale), the reference's fp16 tile).  25 MB at the benchmark shape, against
+ *     1.4 TFLOP of attention that reads each of its tiles 512 times.
+ *  2. q4_prefill_k: one block = one kv head x a group of query tokens whose (token, head) pairs
+ *     fill the 128 rows of the MMA (16 tokens x 8 heads at the benchmark shape).  Per 64-position
+ *     tile, K and V^T arrive by TMA (128-byte swizzle, two stages each) straight into the K-major
+ *     operand layout, so no thread touches them:
  *
- * Two blocks fit on an SM (82 KB of shared memory, 256 of the 512 tensor-memory columns each), so
- * one block's softmax overlaps the other's MMAs.  Every mbarrier wait is bounded: on expiry the
- * block records Q4E_CUDA in the status word, stops waiting and still frees its tensor memory.
+ *       one thread  : S[j+1] = Q . K[j+1]^T   8 x tcgen05.mma (k = 16) into the other of two score
+ *                     buffers in tensor memory, issued before the softmax of tile j starts
+ *       all 4 warps : thread r owns row r: tcgen05.ld its 64 scores of tile j, causal mask, running
+ *                     max with lazy rescale (the stored max only moves when it would grow by more
+ *                     than 2^8, so the O accumulator in tensor memory is rarely touched),
+ *                     P = exp2(..) as fp16 -> shared memory
+ *       one thread  : O[128 x 128] += P . V[j]   4 x tcgen05.mma
+ *
+ *     Two blocks fit on an SM (113 KB of shared memory, 256 of the 512 tensor-memory columns each), so
+ *     one block's softmax also overlaps the other's MMAs.
+ *
+ * Every mbarrier wait is bounded: on expiry the block records Q4E_CUDA in the status word, stops
+ * waiting and still frees its tensor memory.
  */
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <math_constants.h>
 #include <string.h>
@@ -34,18 +43,20 @@ namespace {
 constexpr int PF_ROWS = 128, PF_BN = 64, PF_HD = 128;
 constexpr uint32_t PF_Q_BYTES = 2 * PF_ROWS * 128, PF_K_BYTES = 2 * PF_BN * 128, PF_V_BYTES = PF_HD * 128,
                    PF_P_BYTES = PF_ROWS * 128;
-constexpr uint32_t PF_SMEM = PF_Q_BYTES + PF_K_BYTES + PF_V_BYTES + PF_P_BYTES + 1024 /* alignment */ + 64;
-constexpr uint32_t PF_TMEM_COLS = 256, PF_S_COL = 0, PF_O_COL = 64;
+constexpr uint32_t PF_STAGES = 2;
+/* Q | P | K stages | V stages | barriers in the alignment slack */
+constexpr uint32_t PF_TILE_BYTES = PF_Q_BYTES + PF_P_BYTES + PF_STAGES * (PF_K_BYTES + PF_V_BYTES);
+constexpr uint32_t PF_SMEM = PF_TILE_BYTES + 1024;
+constexpr uint32_t PF_TMEM_COLS = 256, PF_S_COL = 0, PF_O_COL = 128;   /* S0 at 0, S1 at 64, O at 128 */
 constexpr uint32_t PF_SPIN_LIMIT = 1u << 24;
 constexpr float PF_RESCALE_TAU = 8.f;
 
 struct PrefillParams {
-    Q4Cache C;
-    uint32_t layer, n_head, n_kvh, gqa, tpc /* tokens per block */;
+    uint32_t n_head, n_kvh, gqa, tpc /* tokens per block */;
     const __nv_bfloat16 *q;
     const float *gate;
     __nv_bfloat16 *out;
-    uint32_t n_tok, kv_base;
+    uint32_t n_tok, kv_base, max_kv;
     float scale_log2e;
     uint32_t *err;
 };
@@ -121,29 +132,102 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-__global__ void __launch_bounds__(128, 2) q4_prefill_k(const PrefillParams P) {
+/* ---- TMA: 3-D tiled loads that complete on an mbarrier */
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int32_t x, int32_t y,
+                                            int32_t z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+
+/* ---- staging: rows [0, n) of (layer, kv head) -> fp16 K [kh][row][128] and V^T [kh][dim][n_pad].
+ * Block = 64 positions of one kv head, 256 threads: thread t takes the 32-value block t & 3 of row
+ * t >> 2, for K and for V; V goes through shared memory to come out position-contiguous. */
+constexpr int PF_VT_PITCH = PF_BN + 2;   /* halves per dim row of the transposition tile (odd word count) */
+__device__ __forceinline__ void dequant32(const uint8_t *codes, __half scale, uint32_t (&o)[16]) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4 *>(codes)), b = __ldg(reinterpret_cast<const uint4 *>(codes) + 1);
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    const __half2 s2 = __half2half2(scale);
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        /* int8 -> the fp16 numbers 1152 + code by a byte permute, minus 1152 (exact), times the scale */
+        const uint32_t x = w[i] ^ 0x80808080u;
+        o[2 * i] = h2u(__hmul2(u2h(magic_sub(__byte_perm(x, 0x64646464u, 0x4140))), s2));
+        o[2 * i + 1] = h2u(__hmul2(u2h(magic_sub(__byte_perm(x, 0x64646464u, 0x4342))), s2));
+    }
+}
+__global__ void __launch_bounds__(256) q4_pf_stage_k(const Q4Cache C, uint32_t layer, uint32_t n, uint32_t n_pad,
+                                                     __half *kf, __half *vt) {
+    __shared__ __half tile[PF_HD * PF_VT_PITCH];
+    const uint32_t kh = blockIdx.y, p0 = blockIdx.x * PF_BN, tid = threadIdx.x;
+    const uint32_t r = tid >> 2, qb = tid & 3u, p = p0 + r;
+    const uint8_t *kq = C.k + (uint64_t)layer * C.layer_stride + (uint64_t)kh * C.kvh_stride;
+    const uint8_t *vq = C.v + (uint64_t)layer * C.layer_stride + (uint64_t)kh * C.kvh_stride;
+    const uint8_t *sc = C.s + (uint64_t)layer * C.s_layer_stride + (uint64_t)kh * C.s_kvh_stride;
+    uint32_t o[16];
+    if (p < n) {
+        const __half *srow = reinterpret_cast<const __half *>(sc + (uint64_t)p * C.s_tok_stride);
+        dequant32(kq + (uint64_t)p * C.tok_stride + qb * 32u, __ldg(srow + qb), o);
+        uint4 *dst = reinterpret_cast<uint4 *>(kf + ((size_t)kh * n + p) * PF_HD + qb * 32u);
+#pragma unroll
+        for (int i = 0; i < 4; i++) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+        dequant32(vq + (uint64_t)p * C.tok_stride + qb * 32u, __ldg(srow + 4 + qb), o);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; i++) o[i] = 0u;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        const __half2 h = u2h(o[i]);
+        tile[(qb * 32u + 2 * i) * PF_VT_PITCH + r] = __low2half(h);
+        tile[(qb * 32u + 2 * i + 1) * PF_VT_PITCH + r] = __high2half(h);
+    }
+    __syncthreads();
+    /* dim d = tid >> 1, positions 32 * (tid & 1) .. + 31: 64 contiguous bytes of V^T */
+    const uint32_t d = tid >> 1, h0 = (tid & 1u) * 32u;
+    uint32_t w[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++)
+        w[i] = *reinterpret_cast<const uint32_t *>(&tile[d * PF_VT_PITCH + h0 + 2 * i]);
+    uint4 *dst = reinterpret_cast<uint4 *>(vt + ((size_t)kh * PF_HD + d) * n_pad + p0 + h0);
+#pragma unroll
+    for (int i = 0; i < 4; i++) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+}
+
+__global__ void __launch_bounds__(128, 2) q4_prefill_k(const PrefillParams P, const __grid_constant__ CUtensorMap map_k,
+                                                       const __grid_constant__ CUtensorMap map_v) {
     extern __shared__ uint8_t smem_dyn[];
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t kh = blockIdx.y, t0 = blockIdx.x * P.tpc;
-    const Q4Cache &C = P.C;
+    /* later token groups see more rows: launch them first so the tail of the grid is made of short blocks */
+    const uint32_t kh = blockIdx.y, t0 = (gridDim.x - 1u - blockIdx.x) * P.tpc;
 
     /* 1024-byte aligned operand tiles (the swizzle pattern is anchored to the address) */
     const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
-    const uint32_t sQ = base, sK = sQ + PF_Q_BYTES, sV = sK + PF_K_BYTES, sP = sV + PF_V_BYTES;
-    const uint32_t bar_s = sP + PF_P_BYTES, bar_o = bar_s + 8, s_tmem = bar_o + 8;
+    const uint32_t sQ = base, sP = sQ + PF_Q_BYTES, sK = sP + PF_P_BYTES, sV = sK + PF_STAGES * PF_K_BYTES;
+    /* barriers in the alignment slack in front of the tiles when there is room, else behind them */
+    const uint32_t bars = (base - smem_u32(smem_dyn) >= 64u) ? smem_u32(smem_dyn) : base + PF_TILE_BYTES;
+    const uint32_t full_k = bars, full_v = bars + 16, bar_s = bars + 32, bar_o = bars + 48, s_tmem = bars + 56;
 
     /* row r = (token t0 + r / gqa, head kh*gqa + r % gqa); rows past tpc*gqa or past n_tok are padding */
     const uint32_t tl = tid / P.gqa, hh = tid % P.gqa, tok = t0 + tl;
     const bool row_live = tl < P.tpc && tok < P.n_tok;
     uint32_t row_nkv = 0;                      /* this row attends positions [0, row_nkv) */
-    if (row_live) row_nkv = min(P.kv_base + tok + 1u, C.max_kv);
+    if (row_live) row_nkv = min(P.kv_base + tok + 1u, P.max_kv);
     const uint32_t t_last = min(t0 + P.tpc, P.n_tok) - 1u;
-    const uint32_t cta_nkv = min(P.kv_base + t_last + 1u, C.max_kv);
-    const uint32_t cta_min_nkv = min(P.kv_base + t0 + 1u, C.max_kv);
+    const uint32_t cta_nkv = min(P.kv_base + t_last + 1u, P.max_kv);
+    const uint32_t cta_min_nkv = min(P.kv_base + t0 + 1u, P.max_kv);
     const uint32_t n_tiles = (cta_nkv + PF_BN - 1u) / PF_BN;
 
     if (tid == 0) {
-        mbar_init(bar_s, 1);
+#pragma unroll
+        for (uint32_t s = 0; s < PF_STAGES; s++) {
+            mbar_init(full_k + 8 * s, 1);
+            mbar_init(full_v + 8 * s, 1);
+            mbar_init(bar_s + 8 * s, 1);
+        }
         mbar_init(bar_o, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -169,83 +253,9 @@ __global__ void __launch_bounds__(128, 2) q4_prefill_k(const PrefillParams P) {
             asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
         }
     }
-
-    const uint8_t *kq = C.k + (uint64_t)P.layer * C.layer_stride + (uint64_t)kh * C.kvh_stride;
-    const uint8_t *vq = C.v + (uint64_t)P.layer * C.layer_stride + (uint64_t)kh * C.kvh_stride;
-    const uint8_t *sc = C.s + (uint64_t)P.layer * C.s_layer_stride + (uint64_t)kh * C.s_kvh_stride;
-
-    /* K units: (row lane + 32u, block warp), u = 0,1.  V unit: (position pair 2*lane, block warp). */
-    uint4 kraw[2][2], vraw[2][2];
-    __half kscale[2], vscale[2];
-    auto prefetch = [&](uint32_t tile) {
-        const uint32_t p0 = tile * PF_BN;
-#pragma unroll
-        for (int u = 0; u < 2; u++) {
-            const uint32_t p = p0 + lane + 32u * u;
-            const uint32_t pc = min(p, cta_nkv - 1u);
-            const uint4 *src = reinterpret_cast<const uint4 *>(kq + (uint64_t)pc * C.tok_stride + warp * 32u);
-            kraw[u][0] = __ldg(src);
-            kraw[u][1] = __ldg(src + 1);
-            kscale[u] = p < cta_nkv ? __ldg(reinterpret_cast<const __half *>(sc + (uint64_t)pc * C.s_tok_stride) + warp)
-                                    : __ushort_as_half(0);
-        }
-#pragma unroll
-        for (int u = 0; u < 2; u++) {
-            const uint32_t p = p0 + 2u * lane + u;
-            const uint32_t pc = min(p, cta_nkv - 1u);
-            const uint4 *src = reinterpret_cast<const uint4 *>(vq + (uint64_t)pc * C.tok_stride + warp * 32u);
-            vraw[u][0] = __ldg(src);
-            vraw[u][1] = __ldg(src + 1);
-            /* a scale of 0 for rows past the end keeps stale bytes from ever reaching the MMA as NaN */
-            vscale[u] = p < cta_nkv ? __ldg(reinterpret_cast<const __half *>(sc + (uint64_t)pc * C.s_tok_stride) + 4 + warp)
-                                    : __ushort_as_half(0);
-        }
-    };
-    auto dequant_to_smem = [&]() {
-        /* K: 32 dims of two rows -> 4 chunks each in k-block warp/2 */
-#pragma unroll
-        for (int u = 0; u < 2; u++) {
-            const uint32_t row = lane + 32u * u;
-            const __half2 s2 = __half2half2(kscale[u]);
-            const uint32_t w[8] = {kraw[u][0].x, kraw[u][0].y, kraw[u][0].z, kraw[u][0].w,
-                                   kraw[u][1].x, kraw[u][1].y, kraw[u][1].z, kraw[u][1].w};
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                uint32_t o[4];
-#pragma unroll
-                for (int i = 0; i < 2; i++) {
-                    const uint32_t x = w[2 * c + i] ^ 0x80808080u;
-                    o[2 * i] = h2u(__hmul2(u2h(magic_sub(__byte_perm(x, 0x64646464u, 0x4140))), s2));
-                    o[2 * i + 1] = h2u(__hmul2(u2h(magic_sub(__byte_perm(x, 0x64646464u, 0x4342))), s2));
-                }
-                const uint32_t a = sK + (warp >> 1) * (PF_BN * 128) + sw128(row, (warp & 1) * 4 + c);
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
-            }
-        }
-        /* V^T: dims 32*warp + j as rows, positions (2*lane, 2*lane+1) as one 4-byte element pair */
-        {
-            const __half2 s2 = __halves2half2(vscale[0], vscale[1]);
-            const uint32_t a0[8] = {vraw[0][0].x, vraw[0][0].y, vraw[0][0].z, vraw[0][0].w,
-                                    vraw[0][1].x, vraw[0][1].y, vraw[0][1].z, vraw[0][1].w};
-            const uint32_t a1[8] = {vraw[1][0].x, vraw[1][0].y, vraw[1][0].z, vraw[1][0].w,
-                                    vraw[1][1].x, vraw[1][1].y, vraw[1][1].z, vraw[1][1].w};
-#pragma unroll
-            for (int wd = 0; wd < 8; wd++) {
-#pragma unroll
-                for (int bi = 0; bi < 4; bi++) {
-                    const uint32_t u = __byte_perm(a0[wd], a1[wd], ((4 + bi) << 8) | bi);
-                    const uint32_t v = h2u(__hmul2(u2h(magic_sub((u & 0x00FF00FFu) ^ 0x64806480u)), s2));
-                    const uint32_t d = warp * 32u + wd * 4 + bi;
-                    const uint32_t a = sV + d * 128u + (((lane >> 2) ^ (d & 7u)) << 4) + (lane & 3u) * 4u;
-                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
-                }
-            }
-        }
-    };
-
-    prefetch(0);
+    fence_async_smem();
     tc_fence_before();
-    __syncthreads();
+    __syncthreads();          /* barriers initialised, Q in place, tensor memory allocated */
     tc_fence_after();
     uint32_t tmem;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem) : "r"(s_tmem));
@@ -254,41 +264,67 @@ __global__ void __launch_bounds__(128, 2) q4_prefill_k(const PrefillParams P) {
     constexpr uint32_t IDESC_QK = (1u << 4) | ((uint32_t)(PF_BN >> 3) << 17) | ((uint32_t)(PF_ROWS >> 4) << 24);
     constexpr uint32_t IDESC_PV = (1u << 4) | ((uint32_t)(PF_HD >> 3) << 17) | ((uint32_t)(PF_ROWS >> 4) << 24);
 
-    float m_ref = -CUDART_INF_F, l_run = 0.f;
-    bool ok = true;
-    for (uint32_t tile = 0; tile < n_tiles && ok; tile++) {
-        const uint32_t par = tile & 1u;
-        /* the previous P.V must have drained before V^T and P are overwritten */
-        if (tile > 0) ok = mbar_wait(bar_o, par ^ 1u);
-        tc_fence_after();
-        dequant_to_smem();
-        if (tile + 1 < n_tiles) prefetch(tile + 1);
-        fence_async_smem();
-        tc_fence_before();
-        __syncthreads();
-        if (tid == 0) {
-            tc_fence_after();
+    /* thread 0 is the producer and the MMA issuer */
+    auto load_k = [&](uint32_t tile) {     /* two 64-dim boxes of 64 rows */
+        const uint32_t st = tile % PF_STAGES, bar = full_k + 8 * st, dst = sK + st * PF_K_BYTES;
+        mbar_expect_tx(bar, PF_K_BYTES);
+        tma_load_3d(dst, &map_k, bar, 0, (int32_t)(tile * PF_BN), (int32_t)kh);
+        tma_load_3d(dst + PF_BN * 128, &map_k, bar, 64, (int32_t)(tile * PF_BN), (int32_t)kh);
+    };
+    auto load_v = [&](uint32_t tile) {     /* one box: 64 positions x 128 dims of V^T */
+        const uint32_t st = tile % PF_STAGES, bar = full_v + 8 * st;
+        mbar_expect_tx(bar, PF_V_BYTES);
+        tma_load_3d(sV + st * PF_V_BYTES, &map_v, bar, (int32_t)(tile * PF_BN), 0, (int32_t)kh);
+    };
+    auto issue_qk = [&](uint32_t tile) {
+        const uint32_t st = tile % PF_STAGES;
 #pragma unroll
-            for (uint32_t kk = 0; kk < 8; kk++) {
-                const uint64_t ad = umma_desc(sQ + (kk >> 2) * (PF_ROWS * 128) + (kk & 3) * 32);
-                const uint64_t bd = umma_desc(sK + (kk >> 2) * (PF_BN * 128) + (kk & 3) * 32);
-                umma_f16(tmem + PF_S_COL, ad, bd, IDESC_QK, kk > 0);
-            }
-            umma_commit(bar_s);
+        for (uint32_t kk = 0; kk < 8; kk++) {
+            const uint64_t ad = umma_desc(sQ + (kk >> 2) * (PF_ROWS * 128) + (kk & 3) * 32);
+            const uint64_t bd = umma_desc(sK + st * PF_K_BYTES + (kk >> 2) * (PF_BN * 128) + (kk & 3) * 32);
+            umma_f16(tmem + PF_S_COL + st * PF_BN, ad, bd, IDESC_QK, kk > 0);
         }
-        ok = ok && mbar_wait(bar_s, par);
+        umma_commit(bar_s + 8 * st);
+    };
+
+    bool ok = true;
+    if (tid == 0 && n_tiles > 0) {
+        load_k(0);
+        load_v(0);
+        if (n_tiles > 1) {
+            load_k(1);
+            load_v(1);
+        }
+        ok = mbar_wait(full_k, 0);
         tc_fence_after();
+        if (ok) issue_qk(0);
+    }
+
+    float m_ref = -CUDART_INF_F, l_run = 0.f;
+    for (uint32_t tile = 0; tile < n_tiles && ok; tile++) {
+        const uint32_t st = tile % PF_STAGES, use = (tile / PF_STAGES) & 1u;
+        /* scores of the next tile into the other buffer while this tile's softmax runs (its last reader,
+         * the softmax of tile - 1, finished before the block barrier at the end of the previous pass) */
+        if (tid == 0 && tile + 1 < n_tiles) {
+            ok = mbar_wait(full_k + 8 * ((tile + 1) % PF_STAGES), ((tile + 1) / PF_STAGES) & 1u);
+            tc_fence_after();
+            if (ok) issue_qk(tile + 1);
+        }
+        ok = ok && mbar_wait(bar_s + 8 * st, use);
+        tc_fence_after();
+        /* Q.K of this tile is complete: its K stage is free for the tile two ahead */
+        if (tid == 0 && tile + 2 < n_tiles) load_k(tile + 2);
 
         /* ---- softmax of this thread's row */
         float s[64];
-        tmem_ld32(t_lane + PF_S_COL, *reinterpret_cast<float(*)[32]>(&s[0]));
-        tmem_ld32(t_lane + PF_S_COL + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+        tmem_ld32(t_lane + PF_S_COL + st * PF_BN, *reinterpret_cast<float(*)[32]>(&s[0]));
+        tmem_ld32(t_lane + PF_S_COL + st * PF_BN + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
         tmem_wait_ld();
         const uint32_t p0 = tile * PF_BN;
         float mx = -CUDART_INF_F;
         if (p0 + PF_BN <= cta_min_nkv && row_live) {
 #pragma unroll
-            for (int i = 0; i < 64; i++) mx = fmaxf(mx, s[i]);
+            for (int i = 0; i < 64; i += 2) mx = fmaxf(mx, fmaxf(s[i], s[i + 1]));
         } else {
 #pragma unroll
             for (int i = 0; i < 64; i++) {
@@ -304,49 +340,61 @@ __global__ void __launch_bounds__(128, 2) q4_prefill_k(const PrefillParams P) {
             m_ref = mx;
             l_run *= alpha;
         }
-        if (tile > 0 && __any_sync(0xffffffffu, grow)) {
-            /* O row *= alpha.  The previous P.V has completed (waited for above). */
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                float o[32];
-                tmem_ld32(t_lane + PF_O_COL + 32 * c, o);
-                tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; i++) o[i] *= alpha;
-                tmem_st32(t_lane + PF_O_COL + 32 * c, o);
-            }
-            tmem_wait_st();
-        }
         const float mneg = m_ref == -CUDART_INF_F ? 0.f : -m_ref;
         float lsum = 0.f;
+        uint32_t pk[32];
 #pragma unroll
-        for (int c = 0; c < 8; c++) {
-            uint32_t o[4];
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const float e0 = ex2f(fmaf(s[8 * c + 2 * i], P.scale_log2e, mneg));
-                const float e1 = ex2f(fmaf(s[8 * c + 2 * i + 1], P.scale_log2e, mneg));
-                const __half2 h = __floats2half2_rn(e0, e1);
-                lsum += __low2float(h) + __high2float(h);   /* the denominator sums what the MMA sees */
-                o[i] = h2u(h);
-            }
-            const uint32_t a = sP + sw128(tid, c);
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+        for (int i = 0; i < 32; i++) {
+            const float e0 = ex2f(fmaf(s[2 * i], P.scale_log2e, mneg));
+            const float e1 = ex2f(fmaf(s[2 * i + 1], P.scale_log2e, mneg));
+            lsum += e0 + e1;
+            pk[i] = h2u(__floats2half2_rn(e0, e1));
         }
         l_run += lsum;
+
+        /* the previous P.V must have drained before P is overwritten and O is rescaled; its V stage is
+         * then free for the tile after this one */
+        if (tile > 0) {
+            ok = ok && mbar_wait(bar_o, (tile - 1u) & 1u);
+            tc_fence_after();
+            if (tid == 0 && tile + 1 < n_tiles && tile + 1 >= PF_STAGES) load_v(tile + 1);
+            if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    float o[32];
+                    tmem_ld32(t_lane + PF_O_COL + 32 * c, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) o[i] *= alpha;
+                    tmem_st32(t_lane + PF_O_COL + 32 * c, o);
+                }
+                tmem_wait_st();
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < 8; c++) {
+            const uint32_t a = sP + sw128(tid, c);
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(pk[4 * c]), "r"(pk[4 * c + 1]),
+                         "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3]) : "memory");
+        }
         fence_async_smem();
         tc_fence_before();
         __syncthreads();
         if (tid == 0) {
             tc_fence_after();
+            ok = ok && mbar_wait(full_v + 8 * st, use);
+            tc_fence_after();
+            if (ok) {
 #pragma unroll
-            for (uint32_t kk = 0; kk < 4; kk++) {
-                const uint64_t ad = umma_desc(sP + kk * 32);
-                const uint64_t bd = umma_desc(sV + kk * 32);
-                umma_f16(tmem + PF_O_COL, ad, bd, IDESC_PV, (tile > 0 || kk > 0) ? 1u : 0u);
+                for (uint32_t kk = 0; kk < 4; kk++) {
+                    const uint64_t ad = umma_desc(sP + kk * 32);
+                    const uint64_t bd = umma_desc(sV + st * PF_V_BYTES + kk * 32);
+                    umma_f16(tmem + PF_O_COL, ad, bd, IDESC_PV, (tile > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(bar_o);
             }
-            umma_commit(bar_o);
         }
+        ok = __syncthreads_and(ok);   /* a wait that ran out anywhere ends the loop everywhere */
     }
     if (ok && n_tiles > 0) ok = mbar_wait(bar_o, (n_tiles - 1u) & 1u);
     tc_fence_after();
@@ -387,7 +435,47 @@ __global__ void __launch_bounds__(128, 2) q4_prefill_k(const PrefillParams P) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(PF_TMEM_COLS) : "memory");
 }
 
+/* ---- host side: staging tensors, tensor maps, launches */
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult st;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &st) == cudaSuccess &&
+            st == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+        else
+            (void)cudaGetLastError();
+    }
+    return fn;
+}
+
+/* fp16 staging of the rows a chunk can see; grows on demand, never inside a graph capture */
+__half *g_stage = nullptr;
+size_t g_stage_halves = 0;
+bool stage_reserve(size_t halves) {
+    if (halves <= g_stage_halves) return true;
+    if (g_q4.capturing) return q4i_fail(Q4E_SCRATCH, "kv_prefill: staging buffer too small inside a capture");
+    if (!q4i_check(cudaStreamSynchronize(g_q4.stream), "prefill staging sync")) return false;
+    if (g_stage) cudaFree(g_stage);
+    g_stage = nullptr;
+    g_stage_halves = 0;
+    const size_t want = halves + halves / 4;
+    if (!q4i_check(cudaMalloc(&g_stage, want * sizeof(__half)), "prefill staging alloc")) return false;
+    g_stage_halves = want;
+    return true;
+}
+
 }  // namespace
+
+void q4i_prefill_release() {
+    if (g_stage) cudaFree(g_stage);
+    g_stage = nullptr;
+    g_stage_halves = 0;
+}
 
 extern "C" bool q4_gpu_kv_prefill(const q4_gpu_kv *kv, uint32_t layer, const void *q_bf16, const float *gate,
                                   void *out_bf16, uint32_t n_head, uint32_t n_tok, uint32_t kv_base, float scale) {
@@ -404,10 +492,40 @@ extern "C" bool q4_gpu_kv_prefill(const q4_gpu_kv *kv, uint32_t layer, const voi
             return false;
         attr = true;
     }
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return q4i_fail(Q4E_CUDA, "kv_prefill: cuTensorMapEncodeTiled is not available from this driver");
+
+    /* rows the chunk can see, staged as fp16: K [kvh][n][128], V^T [kvh][128][n_pad] */
+    const uint64_t n64 = (uint64_t)kv_base + n_tok;
+    const uint32_t n = (uint32_t)(n64 < kv->max_kv ? n64 : kv->max_kv);
+    const uint32_t n_pad = (n + PF_BN - 1u) / PF_BN * PF_BN;
+    const size_t k_halves = (size_t)kv->n_kvh * n * PF_HD, v_halves = (size_t)kv->n_kvh * PF_HD * n_pad;
+    const size_t k_room = (k_halves + 63) & ~(size_t)63;    /* keeps V^T 128-byte aligned */
+    if (!stage_reserve(k_room + v_halves)) return false;
+    __half *kf = g_stage, *vt = g_stage + k_room;
+    q4_pf_stage_k<<<dim3(n_pad / PF_BN, kv->n_kvh), 256, 0, g_q4.stream>>>(kv->view, layer, n, n_pad, kf, vt);
+    if (!q4i_check(cudaGetLastError(), "prefill staging launch")) return false;
+
+    CUtensorMap map_k, map_v;
+    {
+        const cuuint64_t dims[3] = {PF_HD, n, kv->n_kvh};
+        const cuuint64_t strides[2] = {PF_HD * sizeof(__half), (cuuint64_t)n * PF_HD * sizeof(__half)};
+        const cuuint32_t box[3] = {64, PF_BN, 1}, estr[3] = {1, 1, 1};
+        if (enc(&map_k, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, kf, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return q4i_fail(Q4E_CUDA, "kv_prefill: tensor map (K) rejected");
+    }
+    {
+        const cuuint64_t dims[3] = {n, PF_HD, kv->n_kvh};
+        const cuuint64_t strides[2] = {(cuuint64_t)n_pad * sizeof(__half), (cuuint64_t)PF_HD * n_pad * sizeof(__half)};
+        const cuuint32_t box[3] = {PF_BN, PF_HD, 1}, estr[3] = {1, 1, 1};
+        if (enc(&map_v, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, vt, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return q4i_fail(Q4E_CUDA, "kv_prefill: tensor map (V) rejected");
+    }
+
     PrefillParams p;
     memset(&p, 0, sizeof(p));
-    p.C = kv->view;
-    p.layer = layer;
     p.n_head = n_head;
     p.n_kvh = kv->n_kvh;
     p.gqa = n_head / kv->n_kvh;
@@ -417,9 +535,10 @@ extern "C" bool q4_gpu_kv_prefill(const q4_gpu_kv *kv, uint32_t layer, const voi
     p.out = (__nv_bfloat16 *)out_bf16;
     p.n_tok = n_tok;
     p.kv_base = kv_base;
+    p.max_kv = kv->max_kv;
     p.scale_log2e = scale * 1.4426950408889634f;
     p.err = g_q4.err_d;
     dim3 grid((n_tok + p.tpc - 1) / p.tpc, kv->n_kvh);
-    q4_prefill_k<<<grid, 128, PF_SMEM, g_q4.stream>>>(p);
+    q4_prefill_k<<<grid, 128, PF_SMEM, g_q4.stream>>>(p, map_k, map_v);
     return q4i_check(cudaGetLastError(), "prefill launch");
 }
