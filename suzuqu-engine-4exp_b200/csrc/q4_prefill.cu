@@ -17,19 +17,22 @@
  *     tile, K and V^T arrive by TMA (128-byte swizzle, two stages each) straight into the K-major
  *     operand layout, so no thread touches them:
  *
- *       one thread  : S[j+1] = Q . K[j+1]^T   8 x tcgen05.mma (k = 16) into the other of two score
- *                     buffers in tensor memory, issued before the softmax of tile j starts
- *       all 4 warps : thread r owns row r: tcgen05.ld its 64 scores of tile j, causal mask, running
- *                     max with lazy rescale (the stored max only moves when it would grow by more
- *                     than 2^8, so the O accumulator in tensor memory is rarely touched),
- *                     P = exp2(..) as fp16 -> shared memory
- *       one thread  : O[128 x 128] += P . V[j]   4 x tcgen05.mma
+ *       control warp (one thread): TMA loads two tiles ahead; S[j+2] = Q . K[j+2]^T, 8 x tcgen05.mma
+ *                     (k = 16) into the score buffer that the softmax of tile j has just released
+ *                     (two score buffers in tensor memory, so the tensor core always has the next
+ *                     tile's scores ready); O[128 x 128] += P . V[j], 4 x tcgen05.mma, as soon as
+ *                     the softmax warps have published P
+ *       4 softmax warps: thread r owns row r: tcgen05.ld its 64 scores of tile j, causal mask,
+ *                     running max with lazy rescale (the stored max only moves when it would grow
+ *                     by more than 2^8, so the O accumulator in tensor memory is rarely touched),
+ *                     P = exp2(..) as fp16 -> shared memory, mbarrier arrive
  *
- *     Two blocks fit on an SM (113 KB of shared memory, 256 of the 512 tensor-memory columns each), so
- *     one block's softmax also overlaps the other's MMAs.
+ *     The two roles meet only at mbarriers (scores ready, P ready, P.V drained, tiles landed): there
+ *     is no block-wide barrier inside the tile loop.  Two blocks fit on an SM (113 KB of shared
+ *     memory, 256 of the 512 tensor-memory columns each).
  *
- * Every mbarrier wait is bounded: on expiry the block records Q4E_CUDA in the status word, stops
- * waiting and still frees its tensor memory.
+ * Every mbarrier wait is bounded: on expiry the thread raises a block-wide abort flag that every
+ * other wait polls, the block records Q4E_CUDA in the status word, and still frees its tensor memory.
  */
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -44,6 +47,7 @@ constexpr int PF_ROWS = 128, PF_BN = 64, PF_HD = 128;
 constexpr uint32_t PF_Q_BYTES = 2 * PF_ROWS * 128, PF_K_BYTES = 2 * PF_BN * 128, PF_V_BYTES = PF_HD * 128,
                    PF_P_BYTES = PF_ROWS * 128;
 constexpr uint32_t PF_STAGES = 2;
+constexpr uint32_t PF_THREADS = PF_ROWS + 32;   /* 4 softmax warps + the control warp */
 /* Q | P | K stages | V stages | barriers in the alignment slack */
 constexpr uint32_t PF_TILE_BYTES = PF_Q_BYTES + PF_P_BYTES + PF_STAGES * (PF_K_BYTES + PF_V_BYTES);
 constexpr uint32_t PF_SMEM = PF_TILE_BYTES + 1024;
@@ -92,17 +96,17 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
-/* bounded wait: false when the phase did not complete within the spin limit */
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < PF_SPIN_LIMIT; i++) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
+/* one probe of a phase; the callers bound the number of probes */
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0u;
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
     uint32_t *r = reinterpret_cast<uint32_t *>(v);
@@ -197,8 +201,8 @@ __global__ void __launch_bounds__(256) q4_pf_stage_k(const Q4Cache C, uint32_t l
     for (int i = 0; i < 4; i++) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
 }
 
-__global__ void __launch_bounds__(128, 2) q4_prefill_k(const PrefillParams P, const __grid_constant__ CUtensorMap map_k,
-                                                       const __grid_constant__ CUtensorMap map_v) {
+__global__ void __launch_bounds__(PF_THREADS, 2) q4_prefill_k(const PrefillParams P, const __grid_constant__ CUtensorMap map_k,
+                                                              const __grid_constant__ CUtensorMap map_v) {
     extern __shared__ uint8_t smem_dyn[];
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     /* later token groups see more rows: launch them first so the tail of the grid is made of short blocks */
@@ -208,12 +212,15 @@ __global__ void __launch_bounds__(128, 2) q4_prefill_k(const PrefillParams P, co
     const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
     const uint32_t sQ = base, sP = sQ + PF_Q_BYTES, sK = sP + PF_P_BYTES, sV = sK + PF_STAGES * PF_K_BYTES;
     /* barriers in the alignment slack in front of the tiles when there is room, else behind them */
-    const uint32_t bars = (base - smem_u32(smem_dyn) >= 64u) ? smem_u32(smem_dyn) : base + PF_TILE_BYTES;
-    const uint32_t full_k = bars, full_v = bars + 16, bar_s = bars + 32, bar_o = bars + 48, s_tmem = bars + 56;
+    const uint32_t bars = (base - smem_u32(smem_dyn) >= 96u) ? smem_u32(smem_dyn) : base + PF_TILE_BYTES;
+    const uint32_t full_k = bars, full_v = bars + 16, bar_s = bars + 32, bar_o = bars + 48, bar_p = bars + 56,
+                   s_tmem = bars + 64, s_abort = bars + 68;
 
-    /* row r = (token t0 + r / gqa, head kh*gqa + r % gqa); rows past tpc*gqa or past n_tok are padding */
+    /* softmax thread r < 128 owns row r = (token t0 + r / gqa, head kh*gqa + r % gqa); rows past tpc*gqa or
+     * past n_tok are padding.  Warp 4 is the control warp: TMA producer and MMA issuer. */
+    const bool softmax_thread = tid < PF_ROWS;
     const uint32_t tl = tid / P.gqa, hh = tid % P.gqa, tok = t0 + tl;
-    const bool row_live = tl < P.tpc && tok < P.n_tok;
+    const bool row_live = softmax_thread && tl < P.tpc && tok < P.n_tok;
     uint32_t row_nkv = 0;                      /* this row attends positions [0, row_nkv) */
     if (row_live) row_nkv = min(P.kv_base + tok + 1u, P.max_kv);
     const uint32_t t_last = min(t0 + P.tpc, P.n_tok) - 1u;
@@ -221,24 +228,25 @@ __global__ void __launch_bounds__(128, 2) q4_prefill_k(const PrefillParams P, co
     const uint32_t cta_min_nkv = min(P.kv_base + t0 + 1u, P.max_kv);
     const uint32_t n_tiles = (cta_nkv + PF_BN - 1u) / PF_BN;
 
-    if (tid == 0) {
+    if (warp == 4) {
+        if (lane == 0) {
 #pragma unroll
-        for (uint32_t s = 0; s < PF_STAGES; s++) {
-            mbar_init(full_k + 8 * s, 1);
-            mbar_init(full_v + 8 * s, 1);
-            mbar_init(bar_s + 8 * s, 1);
+            for (uint32_t s = 0; s < PF_STAGES; s++) {
+                mbar_init(full_k + 8 * s, 1);
+                mbar_init(full_v + 8 * s, 1);
+                mbar_init(bar_s + 8 * s, 1);
+            }
+            mbar_init(bar_o, 1);
+            mbar_init(bar_p, PF_ROWS);
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(s_abort), "r"(0u) : "memory");
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         }
-        mbar_init(bar_o, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 0) {
+        __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_tmem),
                      "r"(PF_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-
-    /* ---- Q rows: bf16 -> fp16 (exact for normal values), K-major swizzled, 2 k-blocks of 64 dims */
-    {
+    } else {
+        /* ---- Q rows: bf16 -> fp16 (exact for normal values), K-major swizzled, 2 k-blocks of 64 dims */
         const __nv_bfloat16 *qrow = P.q + ((size_t)tok * P.n_head + (size_t)kh * P.gqa + hh) * PF_HD;
 #pragma unroll
         for (uint32_t c = 0; c < 16; c++) {
@@ -252,186 +260,219 @@ __global__ void __launch_bounds__(128, 2) q4_prefill_k(const PrefillParams P, co
             const uint32_t a = sQ + (c >> 3) * (PF_ROWS * 128) + sw128(tid, c & 7);
             asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
         }
+        fence_async_smem();
     }
-    fence_async_smem();
     tc_fence_before();
     __syncthreads();          /* barriers initialised, Q in place, tensor memory allocated */
     tc_fence_after();
     uint32_t tmem;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem) : "r"(s_tmem));
-    const uint32_t t_lane = tmem + ((warp * 32u) << 16);   /* this warp's 32 lanes of tensor memory */
 
     constexpr uint32_t IDESC_QK = (1u << 4) | ((uint32_t)(PF_BN >> 3) << 17) | ((uint32_t)(PF_ROWS >> 4) << 24);
     constexpr uint32_t IDESC_PV = (1u << 4) | ((uint32_t)(PF_HD >> 3) << 17) | ((uint32_t)(PF_ROWS >> 4) << 24);
-
-    /* thread 0 is the producer and the MMA issuer */
-    auto load_k = [&](uint32_t tile) {     /* two 64-dim boxes of 64 rows */
-        const uint32_t st = tile % PF_STAGES, bar = full_k + 8 * st, dst = sK + st * PF_K_BYTES;
-        mbar_expect_tx(bar, PF_K_BYTES);
-        tma_load_3d(dst, &map_k, bar, 0, (int32_t)(tile * PF_BN), (int32_t)kh);
-        tma_load_3d(dst + PF_BN * 128, &map_k, bar, 64, (int32_t)(tile * PF_BN), (int32_t)kh);
-    };
-    auto load_v = [&](uint32_t tile) {     /* one box: 64 positions x 128 dims of V^T */
-        const uint32_t st = tile % PF_STAGES, bar = full_v + 8 * st;
-        mbar_expect_tx(bar, PF_V_BYTES);
-        tma_load_3d(sV + st * PF_V_BYTES, &map_v, bar, (int32_t)(tile * PF_BN), 0, (int32_t)kh);
-    };
-    auto issue_qk = [&](uint32_t tile) {
-        const uint32_t st = tile % PF_STAGES;
-#pragma unroll
-        for (uint32_t kk = 0; kk < 8; kk++) {
-            const uint64_t ad = umma_desc(sQ + (kk >> 2) * (PF_ROWS * 128) + (kk & 3) * 32);
-            const uint64_t bd = umma_desc(sK + st * PF_K_BYTES + (kk >> 2) * (PF_BN * 128) + (kk & 3) * 32);
-            umma_f16(tmem + PF_S_COL + st * PF_BN, ad, bd, IDESC_QK, kk > 0);
+    /* bounded wait that also gives up when any thread of the block has given up */
+    auto wait = [&](uint32_t bar, uint32_t parity) -> bool {
+        for (uint32_t i = 0; i < PF_SPIN_LIMIT; i++) {
+            if (mbar_test(bar, parity)) return true;
+            if ((i & 1023u) == 1023u) {
+                uint32_t a;
+                asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(a) : "r"(s_abort) : "memory");
+                if (a) return false;
+            }
         }
-        umma_commit(bar_s + 8 * st);
+        asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(s_abort), "r"(1u) : "memory");
+        return false;
     };
-
     bool ok = true;
-    if (tid == 0 && n_tiles > 0) {
-        load_k(0);
-        load_v(0);
-        if (n_tiles > 1) {
-            load_k(1);
-            load_v(1);
-        }
-        ok = mbar_wait(full_k, 0);
-        tc_fence_after();
-        if (ok) issue_qk(0);
-    }
 
-    float m_ref = -CUDART_INF_F, l_run = 0.f;
-    for (uint32_t tile = 0; tile < n_tiles && ok; tile++) {
-        const uint32_t st = tile % PF_STAGES, use = (tile / PF_STAGES) & 1u;
-        /* scores of the next tile into the other buffer while this tile's softmax runs (its last reader,
-         * the softmax of tile - 1, finished before the block barrier at the end of the previous pass) */
-        if (tid == 0 && tile + 1 < n_tiles) {
-            ok = mbar_wait(full_k + 8 * ((tile + 1) % PF_STAGES), ((tile + 1) / PF_STAGES) & 1u);
-            tc_fence_after();
-            if (ok) issue_qk(tile + 1);
-        }
-        ok = ok && mbar_wait(bar_s + 8 * st, use);
-        tc_fence_after();
-        /* Q.K of this tile is complete: its K stage is free for the tile two ahead */
-        if (tid == 0 && tile + 2 < n_tiles) load_k(tile + 2);
-
-        /* ---- softmax of this thread's row */
-        float s[64];
-        tmem_ld32(t_lane + PF_S_COL + st * PF_BN, *reinterpret_cast<float(*)[32]>(&s[0]));
-        tmem_ld32(t_lane + PF_S_COL + st * PF_BN + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
-        tmem_wait_ld();
-        const uint32_t p0 = tile * PF_BN;
-        float mx = -CUDART_INF_F;
-        if (p0 + PF_BN <= cta_min_nkv && row_live) {
+    if (warp == 4) {
+        /* ================= control: one thread feeds the TMA and the tensor core ================= */
+        if (lane == 0 && n_tiles > 0) {
+            auto load_k = [&](uint32_t tile) {     /* two 64-dim boxes of 64 rows */
+                const uint32_t st = tile % PF_STAGES, bar = full_k + 8 * st, dst = sK + st * PF_K_BYTES;
+                mbar_expect_tx(bar, PF_K_BYTES);
+                tma_load_3d(dst, &map_k, bar, 0, (int32_t)(tile * PF_BN), (int32_t)kh);
+                tma_load_3d(dst + PF_BN * 128, &map_k, bar, 64, (int32_t)(tile * PF_BN), (int32_t)kh);
+            };
+            auto load_v = [&](uint32_t tile) {     /* one box: 64 positions x 128 dims of V^T */
+                const uint32_t st = tile % PF_STAGES, bar = full_v + 8 * st;
+                mbar_expect_tx(bar, PF_V_BYTES);
+                tma_load_3d(sV + st * PF_V_BYTES, &map_v, bar, (int32_t)(tile * PF_BN), 0, (int32_t)kh);
+            };
+            auto issue_qk = [&](uint32_t tile) {
+                const uint32_t st = tile % PF_STAGES;
 #pragma unroll
-            for (int i = 0; i < 64; i += 2) mx = fmaxf(mx, fmaxf(s[i], s[i + 1]));
-        } else {
-#pragma unroll
-            for (int i = 0; i < 64; i++) {
-                if (p0 + i >= row_nkv) s[i] = -CUDART_INF_F;
-                mx = fmaxf(mx, s[i]);
-            }
-        }
-        mx *= P.scale_log2e;                      /* scale > 0: max commutes with the scaling */
-        float alpha = 1.f;
-        const bool grow = mx > m_ref + PF_RESCALE_TAU;   /* also true on the first live tile (m_ref = -inf) */
-        if (grow) {
-            alpha = ex2f(m_ref - mx);             /* 0 on the first tile */
-            m_ref = mx;
-            l_run *= alpha;
-        }
-        const float mneg = m_ref == -CUDART_INF_F ? 0.f : -m_ref;
-        float lsum = 0.f;
-        uint32_t pk[32];
-#pragma unroll
-        for (int i = 0; i < 32; i++) {
-            const float e0 = ex2f(fmaf(s[2 * i], P.scale_log2e, mneg));
-            const float e1 = ex2f(fmaf(s[2 * i + 1], P.scale_log2e, mneg));
-            lsum += e0 + e1;
-            pk[i] = h2u(__floats2half2_rn(e0, e1));
-        }
-        l_run += lsum;
-
-        /* the previous P.V must have drained before P is overwritten and O is rescaled; its V stage is
-         * then free for the tile after this one */
-        if (tile > 0) {
-            ok = ok && mbar_wait(bar_o, (tile - 1u) & 1u);
-            tc_fence_after();
-            if (tid == 0 && tile + 1 < n_tiles && tile + 1 >= PF_STAGES) load_v(tile + 1);
-            if (__any_sync(0xffffffffu, grow)) {
-#pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    float o[32];
-                    tmem_ld32(t_lane + PF_O_COL + 32 * c, o);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; i++) o[i] *= alpha;
-                    tmem_st32(t_lane + PF_O_COL + 32 * c, o);
+                for (uint32_t kk = 0; kk < 8; kk++) {
+                    const uint64_t ad = umma_desc(sQ + (kk >> 2) * (PF_ROWS * 128) + (kk & 3) * 32);
+                    const uint64_t bd = umma_desc(sK + st * PF_K_BYTES + (kk >> 2) * (PF_BN * 128) + (kk & 3) * 32);
+                    umma_f16(tmem + PF_S_COL + st * PF_BN, ad, bd, IDESC_QK, kk > 0);
                 }
-                tmem_wait_st();
+                umma_commit(bar_s + 8 * st);
+            };
+            /* tiles whose loads have been issued / whose arrival has been seen, for the drain below */
+            uint32_t k_issued = 0, k_seen = 0, v_issued = 0, v_seen = 0;
+            load_k(0);
+            load_v(0);
+            k_issued = v_issued = 1;
+            if (n_tiles > 1) {
+                load_k(1);
+                load_v(1);
+                k_issued = v_issued = 2;
             }
-        }
-#pragma unroll
-        for (int c = 0; c < 8; c++) {
-            const uint32_t a = sP + sw128(tid, c);
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(pk[4 * c]), "r"(pk[4 * c + 1]),
-                         "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3]) : "memory");
-        }
-        fence_async_smem();
-        tc_fence_before();
-        __syncthreads();
-        if (tid == 0) {
+            /* both score buffers are filled ahead of the softmax */
+            ok = wait(full_k, 0);
             tc_fence_after();
-            ok = ok && mbar_wait(full_v + 8 * st, use);
-            tc_fence_after();
-            if (ok) {
-#pragma unroll
-                for (uint32_t kk = 0; kk < 4; kk++) {
-                    const uint64_t ad = umma_desc(sP + kk * 32);
-                    const uint64_t bd = umma_desc(sV + st * PF_V_BYTES + kk * 32);
-                    umma_f16(tmem + PF_O_COL, ad, bd, IDESC_PV, (tile > 0 || kk > 0) ? 1u : 0u);
+            if (ok) { k_seen = 1; issue_qk(0); }
+            if (ok && n_tiles > 1) {
+                ok = wait(full_k + 8, 0);
+                tc_fence_after();
+                if (ok) { k_seen = 2; issue_qk(1); }
+            }
+            for (uint32_t tile = 0; tile < n_tiles && ok; tile++) {
+                const uint32_t st = tile % PF_STAGES, use = (tile / PF_STAGES) & 1u;
+                /* Q.K of this tile complete: its K stage takes the tile two ahead */
+                ok = wait(bar_s + 8 * st, use);
+                if (ok && tile + 2 < n_tiles) { load_k(tile + 2); k_issued = tile + 3; }
+                /* P.V of the previous tile complete: its V stage takes the tile after this one */
+                if (ok && tile > 0) {
+                    ok = wait(bar_o, (tile - 1u) & 1u);
+                    if (ok && tile + 1 < n_tiles && tile + 1 >= PF_STAGES) { load_v(tile + 1); v_issued = tile + 2; }
                 }
-                umma_commit(bar_o);
-            }
-        }
-        ok = __syncthreads_and(ok);   /* a wait that ran out anywhere ends the loop everywhere */
-    }
-    if (ok && n_tiles > 0) ok = mbar_wait(bar_o, (n_tiles - 1u) & 1u);
-    tc_fence_after();
-    if (!ok && lane == 0) atomicOr(P.err, (uint32_t)Q4E_CUDA);
-
-    /* ---- epilogue: O / l * sigmoid(gate) -> bf16 */
-    if (ok) {
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        const size_t off = ((size_t)tok * P.n_head + (size_t)kh * P.gqa + hh) * PF_HD;
+                /* softmax of this tile done: P is in shared memory, O is rescaled, S[st] has been read */
+                ok = ok && wait(bar_p, tile & 1u);
+                ok = ok && wait(full_v + 8 * st, use);
+                tc_fence_after();
+                if (ok) {
+                    v_seen = tile + 1;
 #pragma unroll
-        for (int c = 0; c < 4; c++) {
-            float o[32];
-            tmem_ld32(t_lane + PF_O_COL + 32 * c, o);
-            tmem_wait_ld();
-            if (row_live) {
-#pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        float x0 = o[i + 2 * j] * inv, x1 = o[i + 2 * j + 1] * inv;
-                        if (P.gate) {
-                            const float2 gt = *reinterpret_cast<const float2 *>(P.gate + off + 32 * c + i + 2 * j);
-                            x0 *= 1.f / (1.f + __expf(-gt.x));
-                            x1 *= 1.f / (1.f + __expf(-gt.y));
-                        }
-                        __nv_bfloat162 b = __floats2bfloat162_rn(x0, x1);
-                        w[j] = *reinterpret_cast<uint32_t *>(&b);
+                    for (uint32_t kk = 0; kk < 4; kk++) {
+                        const uint64_t ad = umma_desc(sP + kk * 32);
+                        const uint64_t bd = umma_desc(sV + st * PF_V_BYTES + kk * 32);
+                        umma_f16(tmem + PF_O_COL, ad, bd, IDESC_PV, (tile > 0 || kk > 0) ? 1u : 0u);
                     }
-                    *reinterpret_cast<uint4 *>(P.out + off + 32 * c + i) = make_uint4(w[0], w[1], w[2], w[3]);
+                    umma_commit(bar_o);
+                    if (tile + 2 < n_tiles) {
+                        ok = wait(full_k + 8 * st, ((tile + 2) / PF_STAGES) & 1u);
+                        tc_fence_after();
+                        if (ok) { k_seen = tile + 3; issue_qk(tile + 2); }
+                    }
+                }
+            }
+            /* gave up somewhere: copies still in flight must land before the block's shared memory is
+             * released (bounded again; these probes ignore the abort flag) */
+            for (uint32_t t = k_seen; t < k_issued; t++)
+                for (uint32_t i = 0; i < PF_SPIN_LIMIT && !mbar_test(full_k + 8 * (t % PF_STAGES), (t / PF_STAGES) & 1u); i++) {}
+            for (uint32_t t = v_seen; t < v_issued; t++)
+                for (uint32_t i = 0; i < PF_SPIN_LIMIT && !mbar_test(full_v + 8 * (t % PF_STAGES), (t / PF_STAGES) & 1u); i++) {}
+        }
+    } else {
+        /* ================= softmax: thread r owns row r ================= */
+        const uint32_t t_lane = tmem + ((warp * 32u) << 16);   /* this warp's 32 lanes of tensor memory */
+        float m_ref = -CUDART_INF_F, l_run = 0.f;
+        for (uint32_t tile = 0; tile < n_tiles && ok; tile++) {
+            const uint32_t st = tile % PF_STAGES, use = (tile / PF_STAGES) & 1u;
+            ok = __all_sync(0xffffffffu, wait(bar_s + 8 * st, use));   /* a warp leaves the loop as one */
+            tc_fence_after();
+            float s[64];
+            tmem_ld32(t_lane + PF_S_COL + st * PF_BN, *reinterpret_cast<float(*)[32]>(&s[0]));
+            tmem_ld32(t_lane + PF_S_COL + st * PF_BN + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+            tmem_wait_ld();
+            const uint32_t p0 = tile * PF_BN;
+            float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;
+            if (!(p0 + PF_BN <= cta_min_nkv && row_live)) {
+#pragma unroll
+                for (int i = 0; i < 64; i++)
+                    if (p0 + i >= row_nkv) s[i] = -CUDART_INF_F;
+            }
+#pragma unroll
+            for (int i = 0; i < 64; i += 4) {
+                mx0 = fmaxf(mx0, s[i]); mx1 = fmaxf(mx1, s[i + 1]);
+                mx2 = fmaxf(mx2, s[i + 2]); mx3 = fmaxf(mx3, s[i + 3]);
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * P.scale_log2e;   /* scale > 0 */
+            float alpha = 1.f;
+            const bool grow = mx > m_ref + PF_RESCALE_TAU;   /* also true on the first live tile (m_ref = -inf) */
+            if (grow) {
+                alpha = ex2f(m_ref - mx);             /* 0 on the first tile */
+                m_ref = mx;
+                l_run *= alpha;
+            }
+            const float mneg = m_ref == -CUDART_INF_F ? 0.f : -m_ref;
+            float ls0 = 0.f, ls1 = 0.f;
+            uint32_t pk[32];
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+                const float e0 = ex2f(fmaf(s[2 * i], P.scale_log2e, mneg));
+                const float e1 = ex2f(fmaf(s[2 * i + 1], P.scale_log2e, mneg));
+                ls0 += e0;
+                ls1 += e1;
+                pk[i] = h2u(__floats2half2_rn(e0, e1));
+            }
+            l_run += ls0 + ls1;
+            /* the previous P.V must have drained before P is overwritten and O is rescaled */
+            if (tile > 0) {
+                ok = __all_sync(0xffffffffu, ok && wait(bar_o, (tile - 1u) & 1u));
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        float o[32];
+                        tmem_ld32(t_lane + PF_O_COL + 32 * c, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; i++) o[i] *= alpha;
+                        tmem_st32(t_lane + PF_O_COL + 32 * c, o);
+                    }
+                    tmem_wait_st();
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                const uint32_t a = sP + sw128(tid, c);
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(pk[4 * c]), "r"(pk[4 * c + 1]),
+                             "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3]) : "memory");
+            }
+            fence_async_smem();
+            tc_fence_before();
+            mbar_arrive(bar_p);
+        }
+        if (ok && n_tiles > 0) ok = wait(bar_o, (n_tiles - 1u) & 1u);
+        tc_fence_after();
+
+        /* ---- epilogue: O / l * sigmoid(gate) -> bf16 */
+        if (ok) {
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            const size_t off = ((size_t)tok * P.n_head + (size_t)kh * P.gqa + hh) * PF_HD;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                float o[32];
+                tmem_ld32(t_lane + PF_O_COL + 32 * c, o);
+                tmem_wait_ld();
+                if (row_live) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            float x0 = o[i + 2 * j] * inv, x1 = o[i + 2 * j + 1] * inv;
+                            if (P.gate) {
+                                const float2 gt = *reinterpret_cast<const float2 *>(P.gate + off + 32 * c + i + 2 * j);
+                                x0 *= 1.f / (1.f + __expf(-gt.x));
+                                x1 *= 1.f / (1.f + __expf(-gt.y));
+                            }
+                            __nv_bfloat162 b = __floats2bfloat162_rn(x0, x1);
+                            w[j] = *reinterpret_cast<uint32_t *>(&b);
+                        }
+                        *reinterpret_cast<uint4 *>(P.out + off + 32 * c + i) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
                 }
             }
         }
     }
+    if (!ok && lane == 0) atomicOr(P.err, (uint32_t)Q4E_CUDA);
     tc_fence_before();
     __syncthreads();
-    if (warp == 0)
+    if (warp == 4)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(PF_TMEM_COLS) : "memory");
 }
 
@@ -539,6 +580,6 @@ extern "C" bool q4_gpu_kv_prefill(const q4_gpu_kv *kv, uint32_t layer, const voi
     p.scale_log2e = scale * 1.4426950408889634f;
     p.err = g_q4.err_d;
     dim3 grid((n_tok + p.tpc - 1) / p.tpc, kv->n_kvh);
-    q4_prefill_k<<<grid, 128, PF_SMEM, g_q4.stream>>>(p, map_k, map_v);
+    q4_prefill_k<<<grid, PF_THREADS, PF_SMEM, g_q4.stream>>>(p, map_k, map_v);
     return q4i_check(cudaGetLastError(), "prefill launch");
 }
