@@ -17,17 +17,17 @@
  *     tile, K and V^T arrive by TMA (128-byte swizzle, two stages each) straight into the K-major
  *     operand layout, so no thread touches them:
  *
- *       control warp (one thread): TMA loads two tiles ahead; S[j+2] = Q . K[j+2]^T, 8 x tcgen05.mma
- *                     (k = 16) into the score buffer that the softmax of tile j has just released
- *                     (two score buffers in tensor memory, so the tensor core always has the next
- *                     tile's scores ready); O[128 x 128] += P . V[j], 4 x tcgen05.mma, as soon as
- *                     the softmax warps have published P
+ *       producer warp (one thread): TMA loads, two tiles of K and of V^T in flight
+ *       issuer warp (one thread): O[128 x 128] += P . V[j], 4 x tcgen05.mma (k = 16), as soon as the
+ *                     softmax warps have published P, then S[j+2] = Q . K[j+2]^T, 8 x tcgen05.mma,
+ *                     into the score buffer that the softmax of tile j has just released (two score
+ *                     buffers in tensor memory, so the next tile's scores are always ready)
  *       4 softmax warps: thread r owns row r: tcgen05.ld its 64 scores of tile j, causal mask,
  *                     running max with lazy rescale (the stored max only moves when it would grow
  *                     by more than 2^8, so the O accumulator in tensor memory is rarely touched),
  *                     P = exp2(..) as fp16 -> shared memory, mbarrier arrive
  *
- *     The two roles meet only at mbarriers (scores ready, P ready, P.V drained, tiles landed): there
+ *     The roles meet only at mbarriers (scores ready, P ready, P.V drained, tiles landed): there
  *     is no block-wide barrier inside the tile loop.  Two blocks fit on an SM (113 KB of shared
  *     memory, 256 of the 512 tensor-memory columns each).
  *
@@ -47,7 +47,7 @@ constexpr int PF_ROWS = 128, PF_BN = 64, PF_HD = 128;
 constexpr uint32_t PF_Q_BYTES = 2 * PF_ROWS * 128, PF_K_BYTES = 2 * PF_BN * 128, PF_V_BYTES = PF_HD * 128,
                    PF_P_BYTES = PF_ROWS * 128;
 constexpr uint32_t PF_STAGES = 2;
-constexpr uint32_t PF_THREADS = PF_ROWS + 32;   /* 4 softmax warps + the control warp */
+constexpr uint32_t PF_THREADS = PF_ROWS + 64;   /* 4 softmax warps, the tensor-core issuer, the TMA producer */
 /* Q | P | K stages | V stages | barriers in the alignment slack */
 constexpr uint32_t PF_TILE_BYTES = PF_Q_BYTES + PF_P_BYTES + PF_STAGES * (PF_K_BYTES + PF_V_BYTES);
 constexpr uint32_t PF_SMEM = PF_TILE_BYTES + 1024;
@@ -201,6 +201,17 @@ __global__ void __launch_bounds__(256) q4_pf_stage_k(const Q4Cache C, uint32_t l
     for (int i = 0; i < 4; i++) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
 }
 
+#ifdef Q4_PF_TIMING
+/* experiment builds only: cycles spent per wait kind, per block: [0..4] control (bar_s, bar_o, bar_p, full_v,
+ * full_k), [5..8] softmax warp 0 lane 0 (bar_s, tcgen05.ld, bar_o, total), [9] tiles */
+__device__ unsigned long long q4_pf_dbg[4096 * 16];
+#define PF_T0() const long long t_ = clock64()
+#define PF_ACC(i) acc_[i] += clock64() - t_
+#else
+#define PF_T0() do { } while (0)
+#define PF_ACC(i) do { } while (0)
+#endif
+
 __global__ void __launch_bounds__(PF_THREADS, 2) q4_prefill_k(const PrefillParams P, const __grid_constant__ CUtensorMap map_k,
                                                               const __grid_constant__ CUtensorMap map_v) {
     extern __shared__ uint8_t smem_dyn[];
@@ -217,7 +228,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) q4_prefill_k(const PrefillParam
                    s_tmem = bars + 64, s_abort = bars + 68;
 
     /* softmax thread r < 128 owns row r = (token t0 + r / gqa, head kh*gqa + r % gqa); rows past tpc*gqa or
-     * past n_tok are padding.  Warp 4 is the control warp: TMA producer and MMA issuer. */
+     * past n_tok are padding.  Warp 4 issues the MMAs, warp 5 the TMA loads (one thread each). */
     const bool softmax_thread = tid < PF_ROWS;
     const uint32_t tl = tid / P.gqa, hh = tid % P.gqa, tok = t0 + tl;
     const bool row_live = softmax_thread && tl < P.tpc && tok < P.n_tok;
@@ -245,7 +256,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) q4_prefill_k(const PrefillParam
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_tmem),
                      "r"(PF_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    } else {
+    } else if (warp < 4) {
         /* ---- Q rows: bf16 -> fp16 (exact for normal values), K-major swizzled, 2 k-blocks of 64 dims */
         const __nv_bfloat16 *qrow = P.q + ((size_t)tok * P.n_head + (size_t)kh * P.gqa + hh) * PF_HD;
 #pragma unroll
@@ -284,9 +295,13 @@ __global__ void __launch_bounds__(PF_THREADS, 2) q4_prefill_k(const PrefillParam
         return false;
     };
     bool ok = true;
+#ifdef Q4_PF_TIMING
+    long long acc_[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+    const long long t_begin_ = clock64();
+#endif
 
-    if (warp == 4) {
-        /* ================= control: one thread feeds the TMA and the tensor core ================= */
+    if (warp == 5) {
+        /* ================= producer: one thread keeps two tiles of K and of V^T in flight ================= */
         if (lane == 0 && n_tiles > 0) {
             auto load_k = [&](uint32_t tile) {     /* two 64-dim boxes of 64 rows */
                 const uint32_t st = tile % PF_STAGES, bar = full_k + 8 * st, dst = sK + st * PF_K_BYTES;
@@ -299,6 +314,40 @@ __global__ void __launch_bounds__(PF_THREADS, 2) q4_prefill_k(const PrefillParam
                 mbar_expect_tx(bar, PF_V_BYTES);
                 tma_load_3d(sV + st * PF_V_BYTES, &map_v, bar, (int32_t)(tile * PF_BN), 0, (int32_t)kh);
             };
+            uint32_t k_issued = 1, v_issued = 1;
+            load_k(0);
+            load_v(0);
+            if (n_tiles > 1) {
+                load_k(1);
+                load_v(1);
+                k_issued = v_issued = 2;
+            }
+            for (uint32_t tile = 0; tile < n_tiles && ok; tile++) {
+                const uint32_t st = tile % PF_STAGES, use = (tile / PF_STAGES) & 1u;
+                /* Q.K of this tile complete: its K stage takes the tile two ahead */
+                if (tile + 2 < n_tiles) {
+                    { PF_T0(); ok = wait(bar_s + 8 * st, use); PF_ACC(0); }
+                    if (ok) { load_k(tile + 2); k_issued = tile + 3; }
+                }
+                /* P.V of the previous tile complete: its V stage takes the tile after this one */
+                if (ok && tile > 0 && tile + 1 < n_tiles) {
+                    { PF_T0(); ok = wait(bar_o, (tile - 1u) & 1u); PF_ACC(1); }
+                    if (ok) { load_v(tile + 1); v_issued = tile + 2; }
+                }
+            }
+            /* Gave up somewhere: copies still in flight must land before the block's shared memory is
+             * released (bounded again; these probes ignore the abort flag; phases that completed long ago
+             * answer at once). */
+            if (!ok) {
+                for (uint32_t t = k_issued > 2 ? k_issued - 2 : 0; t < k_issued; t++)
+                    for (uint32_t i = 0; i < PF_SPIN_LIMIT && !mbar_test(full_k + 8 * (t % PF_STAGES), (t / PF_STAGES) & 1u); i++) {}
+                for (uint32_t t = v_issued > 2 ? v_issued - 2 : 0; t < v_issued; t++)
+                    for (uint32_t i = 0; i < PF_SPIN_LIMIT && !mbar_test(full_v + 8 * (t % PF_STAGES), (t / PF_STAGES) & 1u); i++) {}
+            }
+        }
+    } else if (warp == 4) {
+        /* ================= tensor-core issuer: one thread ================= */
+        if (lane == 0 && n_tiles > 0) {
             auto issue_qk = [&](uint32_t tile) {
                 const uint32_t st = tile % PF_STAGES;
 #pragma unroll
@@ -309,41 +358,25 @@ __global__ void __launch_bounds__(PF_THREADS, 2) q4_prefill_k(const PrefillParam
                 }
                 umma_commit(bar_s + 8 * st);
             };
-            /* tiles whose loads have been issued / whose arrival has been seen, for the drain below */
-            uint32_t k_issued = 0, k_seen = 0, v_issued = 0, v_seen = 0;
-            load_k(0);
-            load_v(0);
-            k_issued = v_issued = 1;
-            if (n_tiles > 1) {
-                load_k(1);
-                load_v(1);
-                k_issued = v_issued = 2;
-            }
             /* both score buffers are filled ahead of the softmax */
             ok = wait(full_k, 0);
             tc_fence_after();
-            if (ok) { k_seen = 1; issue_qk(0); }
+            if (ok) issue_qk(0);
             if (ok && n_tiles > 1) {
                 ok = wait(full_k + 8, 0);
                 tc_fence_after();
-                if (ok) { k_seen = 2; issue_qk(1); }
+                if (ok) issue_qk(1);
             }
             for (uint32_t tile = 0; tile < n_tiles && ok; tile++) {
                 const uint32_t st = tile % PF_STAGES, use = (tile / PF_STAGES) & 1u;
-                /* Q.K of this tile complete: its K stage takes the tile two ahead */
-                ok = wait(bar_s + 8 * st, use);
-                if (ok && tile + 2 < n_tiles) { load_k(tile + 2); k_issued = tile + 3; }
-                /* P.V of the previous tile complete: its V stage takes the tile after this one */
-                if (ok && tile > 0) {
-                    ok = wait(bar_o, (tile - 1u) & 1u);
-                    if (ok && tile + 1 < n_tiles && tile + 1 >= PF_STAGES) { load_v(tile + 1); v_issued = tile + 2; }
-                }
+                /* operands first (they land while the softmax runs), then the softmax's hand-over, so that
+                 * nothing but the issue itself stands between "P is ready" and the two products */
+                { PF_T0(); ok = wait(full_v + 8 * st, use); PF_ACC(3); }
+                if (ok && tile + 2 < n_tiles) { PF_T0(); ok = wait(full_k + 8 * st, ((tile + 2) / PF_STAGES) & 1u); PF_ACC(4); }
                 /* softmax of this tile done: P is in shared memory, O is rescaled, S[st] has been read */
-                ok = ok && wait(bar_p, tile & 1u);
-                ok = ok && wait(full_v + 8 * st, use);
+                { PF_T0(); ok = ok && wait(bar_p, tile & 1u); PF_ACC(2); }
                 tc_fence_after();
                 if (ok) {
-                    v_seen = tile + 1;
 #pragma unroll
                     for (uint32_t kk = 0; kk < 4; kk++) {
                         const uint64_t ad = umma_desc(sP + kk * 32);
@@ -351,32 +384,32 @@ __global__ void __launch_bounds__(PF_THREADS, 2) q4_prefill_k(const PrefillParam
                         umma_f16(tmem + PF_O_COL, ad, bd, IDESC_PV, (tile > 0 || kk > 0) ? 1u : 0u);
                     }
                     umma_commit(bar_o);
-                    if (tile + 2 < n_tiles) {
-                        ok = wait(full_k + 8 * st, ((tile + 2) / PF_STAGES) & 1u);
-                        tc_fence_after();
-                        if (ok) { k_seen = tile + 3; issue_qk(tile + 2); }
-                    }
+                    if (tile + 2 < n_tiles) issue_qk(tile + 2);
                 }
             }
-            /* gave up somewhere: copies still in flight must land before the block's shared memory is
-             * released (bounded again; these probes ignore the abort flag) */
-            for (uint32_t t = k_seen; t < k_issued; t++)
-                for (uint32_t i = 0; i < PF_SPIN_LIMIT && !mbar_test(full_k + 8 * (t % PF_STAGES), (t / PF_STAGES) & 1u); i++) {}
-            for (uint32_t t = v_seen; t < v_issued; t++)
-                for (uint32_t i = 0; i < PF_SPIN_LIMIT && !mbar_test(full_v + 8 * (t % PF_STAGES), (t / PF_STAGES) & 1u); i++) {}
+#ifdef Q4_PF_TIMING
+            {
+                const uint32_t b_ = blockIdx.x + gridDim.x * blockIdx.y;
+                if (b_ < 4096) for (int i = 2; i < 5; i++) q4_pf_dbg[b_ * 16 + i] = (unsigned long long)acc_[i];
+            }
+#endif
         }
     } else {
-        /* ================= softmax: thread r owns row r ================= */
+        /* ================= softmax (warps 0-3): thread r owns row r ================= */
         const uint32_t t_lane = tmem + ((warp * 32u) << 16);   /* this warp's 32 lanes of tensor memory */
         float m_ref = -CUDART_INF_F, l_run = 0.f;
         for (uint32_t tile = 0; tile < n_tiles && ok; tile++) {
             const uint32_t st = tile % PF_STAGES, use = (tile / PF_STAGES) & 1u;
-            ok = __all_sync(0xffffffffu, wait(bar_s + 8 * st, use));   /* a warp leaves the loop as one */
+            { PF_T0(); ok = __all_sync(0xffffffffu, wait(bar_s + 8 * st, use)); PF_ACC(5); }   /* a warp leaves the loop as one */
             tc_fence_after();
             float s[64];
-            tmem_ld32(t_lane + PF_S_COL + st * PF_BN, *reinterpret_cast<float(*)[32]>(&s[0]));
-            tmem_ld32(t_lane + PF_S_COL + st * PF_BN + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
-            tmem_wait_ld();
+            {
+                PF_T0();
+                tmem_ld32(t_lane + PF_S_COL + st * PF_BN, *reinterpret_cast<float(*)[32]>(&s[0]));
+                tmem_ld32(t_lane + PF_S_COL + st * PF_BN + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+                tmem_wait_ld();
+                PF_ACC(6);
+            }
             const uint32_t p0 = tile * PF_BN;
             float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;
             if (!(p0 + PF_BN <= cta_min_nkv && row_live)) {
@@ -411,7 +444,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) q4_prefill_k(const PrefillParam
             l_run += ls0 + ls1;
             /* the previous P.V must have drained before P is overwritten and O is rescaled */
             if (tile > 0) {
-                ok = __all_sync(0xffffffffu, ok && wait(bar_o, (tile - 1u) & 1u));
+                { PF_T0(); ok = __all_sync(0xffffffffu, ok && wait(bar_o, (tile - 1u) & 1u)); PF_ACC(7); }
                 tc_fence_after();
                 if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll
@@ -438,6 +471,16 @@ __global__ void __launch_bounds__(PF_THREADS, 2) q4_prefill_k(const PrefillParam
         }
         if (ok && n_tiles > 0) ok = wait(bar_o, (n_tiles - 1u) & 1u);
         tc_fence_after();
+#ifdef Q4_PF_TIMING
+        if (tid == 0) {
+            const uint32_t b_ = blockIdx.x + gridDim.x * blockIdx.y;
+            if (b_ < 4096) {
+                for (int i = 5; i < 8; i++) q4_pf_dbg[b_ * 16 + i] = (unsigned long long)acc_[i];
+                q4_pf_dbg[b_ * 16 + 8] = (unsigned long long)(clock64() - t_begin_);
+                q4_pf_dbg[b_ * 16 + 9] = n_tiles;
+            }
+        }
+#endif
 
         /* ---- epilogue: O / l * sigmoid(gate) -> bf16 */
         if (ok) {
@@ -511,6 +554,12 @@ bool stage_reserve(size_t halves) {
 }
 
 }  // namespace
+
+#ifdef Q4_PF_TIMING
+extern "C" bool q4_pf_dbg_fetch(unsigned long long *host, size_t n) {
+    return cudaMemcpyFromSymbol(host, q4_pf_dbg, n * sizeof(unsigned long long)) == cudaSuccess;
+}
+#endif
 
 void q4i_prefill_release() {
     if (g_stage) cudaFree(g_stage);
