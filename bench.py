@@ -457,6 +457,44 @@ def extras_prefill(torch, q4gpu, L, ext, peaks):
             "queries_per_s": n_tok / (t_app + t_att)}
 
 
+def extras_indexer(torch, q4gpu, L, ext, peak_gbs):
+    """QSA indexer at ctx 262144 (the step that produces the lists): per layer, score 65536 pooled blocks
+    (4 indexer heads, fp32 pool = 33.5 MB) and select the top 512 + tail into a 2051-wide list, at the device
+    position word; 12 layers x (score + select) captured in one graph, pools of the 12 layers 402 MB >> L2"""
+    pos, ratio, n_head, k_blk = 262143, 4, 4, 512
+    nb = (pos + 1) // ratio
+    pool = torch.randn(N_LAYERS, nb, HD, device="cuda")
+    q = torch.randn(N_LAYERS, n_head, HD, device="cuda")
+    score = torch.empty(N_LAYERS, nb, device="cuda")
+    sel = torch.empty(N_LAYERS, WIDTH, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    L.q4_hip_pos_push(pos)
+
+    def enqueue(with_select):
+        for l in range(N_LAYERS):
+            assert L.q4_hip_qsa_score_d(q[l].data_ptr(), pool[l].data_ptr(), score[l].data_ptr(), nb, n_head, HD, ratio)
+            if with_select:
+                assert L.q4_hip_qsa_topk_d(score[l].data_ptr(), sel[l].data_ptr(), nb, k_blk, ratio, WIDTH)
+    res = {}
+    for name, with_select in (("score_plus_select_us_per_layer", True), ("score_us_per_layer", False)):
+        enqueue(with_select)
+        assert L.q4_hip_graph_begin() == 1
+        enqueue(with_select)
+        gr = L.q4_hip_graph_end()
+        assert gr
+
+        def one(i, gr=gr):
+            assert L.q4_hip_graph_launch(gr)
+        timed(torch, ext, one, 3)
+        res[name] = 1e6 * timed(torch, ext, one, 10) / (10 * N_LAYERS)
+        L.q4_hip_graph_free(gr)
+    by = nb * HD * 4
+    res.update({"workload": "QSA indexer, ctx 262144: 65536 pooled blocks x 4 heads scored, exact top-512 + tail -> 2051 positions",
+                "pool_bytes_per_layer": by, "score_gbs": by / res["score_us_per_layer"] / 1e3,
+                "score_frac_of_measured_hbm": by / res["score_us_per_layer"] / 1e3 / peak_gbs})
+    return res
+
+
 def extras_dense(torch, q4gpu, L, ext, peak_gbs, kinds=("q8_0", "f16", "f32")):
     """configs[4] on one GPU: full attention over 262144 rows, q8_0 / f16 / f32 KV, 12 layers"""
     ctx = 262144
@@ -598,7 +636,7 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--groups", type=int, default=0, help="replicas of the session group (0 = enough to defeat L2)")
     ap.add_argument("--ctx-max", type=int, default=131072, help="upper end of the context-length draw (profiling: small)")
-    ap.add_argument("--only", default="", choices=["", "single", "dense", "prefill"],
+    ap.add_argument("--only", default="", choices=["", "single", "dense", "prefill", "indexer"],
                     help="run just one of the ctx-262144 extras (for profiler captures)")
     ap.add_argument("--dense-kinds", default="q8_0,f16,f32")
     ap.add_argument("--mode", default="sessions", choices=["sessions", "seqshard"],
@@ -647,6 +685,8 @@ def main():
             res = extras_single_session(torch, q4gpu, L, ext, peak_gbs)
         elif args.only == "prefill":
             res = extras_prefill(torch, q4gpu, L, ext, peaks)
+        elif args.only == "indexer":
+            res = extras_indexer(torch, q4gpu, L, ext, peak_gbs)
         else:
             res = extras_dense(torch, q4gpu, L, ext, peak_gbs, args.dense_kinds.split(","))
         print(json.dumps({"only": args.only, "result": res}), flush=True)
@@ -766,6 +806,7 @@ def main():
         line["single_session_ctx262144"] = extras_single_session(torch, q4gpu, L, ext, peak_gbs)
         line["dense_ctx262144"] = extras_dense(torch, q4gpu, L, ext, peak_gbs)
         line["prefill_8192_over_16384"] = extras_prefill(torch, q4gpu, L, ext, peaks)
+        line["indexer_ctx262144"] = extras_indexer(torch, q4gpu, L, ext, peak_gbs)
         line["cpu_baseline"] = cpu_baseline(ctxs, args.cpu_seconds)
     print(json.dumps(line), flush=True)
     if dist is not None:

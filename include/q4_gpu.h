@@ -132,6 +132,27 @@ bool q4_hip_qsa_decode_idx(const float *d_q, const void *d_kcache, const void *d
  * src/q4.h:704, src/q4_rocm.cu:7698-7707 */
 bool q4_hip_qsa_topk_alloc(void);
 
+/* ---- QSA indexer (src/q4.h:698-706, 916-927; src/q4_rocm.cu:7366-7940): the producer of the `sel`
+ * lists.  raw_f16: the indexer's fp16 key store [token][128]; pool: fp32 [block][128], block b =
+ * mean of `ratio` keys, RMSNorm (wn, eps), RoPE at position b*ratio; score[t][b] = sum over the
+ * n_head <= 4 indexer heads of relu(q[t][h] . pool[b]) for b < (pos0 + t + 1) / ratio, else -1e30;
+ * topk: the min(n_vis, k_blk <= 512) best blocks by (score descending, index ascending) as positions
+ * (blocks above the threshold in index order, then ties in index order), then the newest partial
+ * block up to the token's position, then -1, `width` entries per token.  The _d forms take the
+ * position from the device position word (graph-captured decode).  hd must be 128. */
+bool q4_hip_qsa_pool(const void *raw_f16, float *pool, const float *wn, uint32_t hd, uint32_t ratio,
+                     uint32_t b0, uint32_t b1, uint32_t n_rot, float rope_base, float eps);
+bool q4_hip_qsa_pool_d(const void *raw, float *pool, const float *wn, uint32_t hd, uint32_t ratio,
+                       uint32_t n_rot, float rope_base, float eps);
+bool q4_hip_qsa_score(const float *q, const float *pool, float *score, uint32_t n_tok, uint32_t n_blocks,
+                      uint32_t stride, uint32_t n_head, uint32_t hd, uint32_t pos0, uint32_t ratio);
+bool q4_hip_qsa_score_d(const float *q, const float *pool, float *score, uint32_t stride, uint32_t n_head,
+                        uint32_t hd, uint32_t ratio);
+bool q4_hip_qsa_topk(const float *score, int32_t *sel, uint32_t n_tok, uint32_t n_blocks, uint32_t stride,
+                     uint32_t k_blk, uint32_t ratio, uint32_t pos0, uint32_t width);
+bool q4_hip_qsa_topk_d(const float *score, int32_t *sel, uint32_t stride, uint32_t k_blk, uint32_t ratio,
+                       uint32_t width);
+
 /* ======================================================================================= */
 /* 2. B200-native additions                                                                 */
 /* ======================================================================================= */

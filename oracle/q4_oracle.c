@@ -506,6 +506,109 @@ Q4O_API int q4o_attn_items(const q4o_item *items, uint32_t n_items, uint32_t n_h
     return 0;
 }
 
+/* ------------------------------------------------------------------ QSA indexer -------- */
+/* qsa_pool_k (src/q4_rocm.cu:7366-7402): block b = mean of `ratio` raw fp16 keys (summed in token
+ * order, divided once), RMSNorm whose sum of squares is the kernel's shared-memory tree
+ * (red[d] += red[d + st], st = 64, 32, .. 1), weight, RoPE at the block's first position. */
+Q4O_API void q4o_ix_pool(const uint16_t *raw, float *pool, const float *wn, uint32_t hd, uint32_t ratio,
+                         uint32_t b0, uint32_t b1, uint32_t n_rot, float base, float eps) {
+    if (hd != 128) return;
+    for (uint32_t b = b0; b < b1; b++) {
+        float v[128], red[128];
+        const uint16_t *src = raw + (size_t)b * ratio * hd;
+        for (uint32_t d = 0; d < hd; d++) {
+            float s = 0.f;
+            for (uint32_t j = 0; j < ratio; j++) s += q4o_f16_to_f32(src[(size_t)j * hd + d]);
+            v[d] = s / (float)ratio;
+            red[d] = v[d] * v[d];
+        }
+        for (uint32_t st = 64; st > 0; st >>= 1)
+            for (uint32_t d = 0; d < st; d++) red[d] += red[d + st];
+        float inv = 1.f / sqrtf(red[0] / (float)hd + eps);
+        for (uint32_t d = 0; d < hd; d++) v[d] = v[d] * inv * (wn ? wn[d] : 1.f);
+        for (uint32_t d = 0; d + 1 < hd && d < n_rot; d += 2) {
+            uint32_t p = d >> 1;
+            float freq = powf(base, -(float)p / (float)(n_rot / 2u));
+            float ang = (float)(b * ratio) * freq;
+            float c = cosf(ang), si = sinf(ang);
+            float x0 = v[d], x1 = v[d + 1];
+            v[d] = x0 * c - x1 * si;
+            v[d + 1] = x0 * si + x1 * c;
+        }
+        memcpy(pool + (size_t)b * hd, v, sizeof(float) * hd);
+    }
+}
+
+/* qsa_score_k (src/q4_rocm.cu:7405-7436): score[t][b] = sum_h relu(q[t][h] . pool[b]) for the blocks
+ * token t can see (b < (pos + 1) / ratio), else -1e30.  `dot += q[i] * k[i]` in dim order is one
+ * fused multiply-add per term on the GPU (hipcc contracts a * b + c by default), restated as fmaf. */
+Q4O_API void q4o_ix_score(const float *q, const float *pool, float *score, uint32_t n_tok, uint32_t n_blocks,
+                          uint32_t stride, uint32_t n_head, uint32_t hd, uint32_t pos0, uint32_t ratio) {
+    for (uint32_t t = 0; t < n_tok; t++) {
+        uint32_t pos = pos0 + t, n_vis = ratio ? (pos + 1) / ratio : 0;
+        for (uint32_t b = 0; b < n_blocks; b++) {
+            float s = -1.0e30f;
+            if (b < n_vis) {
+                s = 0.f;
+                const float *kb = pool + (size_t)b * hd;
+                for (uint32_t h = 0; h < n_head; h++) {
+                    const float *qq = q + ((size_t)t * n_head + h) * hd;
+                    float dot = 0.f;
+                    for (uint32_t i = 0; i < hd; i++) dot = fmaf(qq[i], kb[i], dot);
+                    s += fmaxf(dot, 0.f);
+                }
+            }
+            score[(size_t)t * stride + b] = s;
+        }
+    }
+}
+
+static uint32_t ix_key(float f) {   /* qsa_tk_xkey (:7464-7467): order-preserving uint of a float */
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+static int ix_cmp_desc(const void *a, const void *b) {
+    uint32_t x = *(const uint32_t *)a, y = *(const uint32_t *)b;
+    return x < y ? 1 : x > y ? -1 : 0;
+}
+/* qsa_topk_k + qsa_write_sel (src/q4_rocm.cu:7722-7846): the need = min(n_vis, k_blk) best blocks by
+ * (score descending, index ascending), emitted as: every block above the threshold key in ascending
+ * index order, then threshold ties in ascending index order; each expands to its `ratio` positions;
+ * then the positions of the newest partial block up to pos; then -1.  All blocks fit (need == n_vis):
+ * the dense prefix 0..pos, -1 beyond. */
+Q4O_API void q4o_ix_topk(const float *score, int32_t *sel, uint32_t n_tok, uint32_t stride, uint32_t k_blk,
+                         uint32_t ratio, uint32_t pos0, uint32_t width) {
+    for (uint32_t t = 0; t < n_tok; t++) {
+        uint32_t pos = pos0 + t, n_vis = ratio ? (pos + 1) / ratio : 0;
+        uint32_t need = n_vis < k_blk ? n_vis : k_blk;
+        const float *row = score + (size_t)t * stride;
+        int32_t *out = sel + (size_t)t * width;
+        if (need == n_vis) {
+            for (uint32_t w = 0; w < width; w++) out[w] = w <= pos ? (int32_t)w : -1;
+            continue;
+        }
+        uint32_t *keys = (uint32_t *)malloc(sizeof(uint32_t) * n_vis);
+        for (uint32_t b = 0; b < n_vis; b++) keys[b] = ix_key(row[b]);
+        qsort(keys, n_vis, sizeof(uint32_t), ix_cmp_desc);
+        uint32_t thr = keys[need - 1];
+        free(keys);
+        int32_t *chosen = (int32_t *)malloc(sizeof(int32_t) * need);
+        uint32_t n = 0;
+        for (uint32_t b = 0; b < n_vis && n < need; b++)
+            if (ix_key(row[b]) > thr) chosen[n++] = (int32_t)b;
+        for (uint32_t b = 0; b < n_vis && n < need; b++)
+            if (ix_key(row[b]) == thr) chosen[n++] = (int32_t)b;
+        uint32_t w = 0;
+        for (uint32_t i = 0; i < n && w < width; i++)
+            for (uint32_t j = 0; j < ratio && w < width; j++) out[w++] = (int32_t)((uint32_t)chosen[i] * ratio + j);
+        uint32_t tail = n_vis * ratio;
+        while (tail <= pos && w < width) out[w++] = (int32_t)tail++;
+        while (w < width) out[w++] = -1;
+        free(chosen);
+    }
+}
+
 Q4O_API int q4o_max_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

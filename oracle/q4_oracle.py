@@ -69,6 +69,10 @@ def lib():
                                     C.c_void_p]
         L.q4o_max_threads.restype = C.c_int
         L.q4o_host_procs.restype = C.c_int
+        L.q4o_ix_pool.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
+                                  C.c_uint32, C.c_float, C.c_float]
+        L.q4o_ix_score.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_uint32] * 7
+        L.q4o_ix_topk.argtypes = [C.c_void_p, C.c_void_p] + [C.c_uint32] * 6
         L.q4o_attn_items.restype = C.c_int
         L.q4o_attn_items.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float,
                                      C.c_int, C.c_int]
@@ -237,6 +241,33 @@ def lse_merge(parts, n_head, hd, gate=None):
         gate = np.ascontiguousarray(gate, np.float32)
     lib().q4o_lse_merge(_p(parts), n_parts, n_head, hd, _p(gate), _p(out))
     return out
+
+
+def ix_pool(raw_f16, wn, ratio, b0, b1, n_rot, base, eps, pool=None, hd=128):
+    """qsa_pool_k: raw fp16 keys [n_tok][hd] (uint16) -> pooled blocks [b0, b1) of pool [n_blocks][hd]"""
+    raw_f16 = np.ascontiguousarray(raw_f16, np.uint16)
+    if pool is None:
+        pool = np.zeros((b1, hd), np.float32)
+    wn_c = None if wn is None else np.ascontiguousarray(wn, np.float32)
+    lib().q4o_ix_pool(_p(raw_f16), _p(pool), _p(wn_c), hd, ratio, b0, b1, n_rot, base, eps)
+    return pool
+
+
+def ix_score(q, pool, n_tok, n_blocks, stride, n_head, pos0, ratio, hd=128):
+    """qsa_score_k: q [n_tok][n_head][hd], pool [.][hd] -> score [n_tok][stride]"""
+    q = np.ascontiguousarray(q, np.float32)
+    pool = np.ascontiguousarray(pool, np.float32)
+    score = np.zeros((n_tok, stride), np.float32)
+    lib().q4o_ix_score(_p(q), _p(pool), _p(score), n_tok, n_blocks, stride, n_head, hd, pos0, ratio)
+    return score
+
+
+def ix_topk(score, n_tok, stride, k_blk, ratio, pos0, width):
+    """qsa_topk_k + qsa_write_sel: score [n_tok][stride] -> sel [n_tok][width]"""
+    score = np.ascontiguousarray(score, np.float32)
+    sel = np.zeros((n_tok, width), np.int32)
+    lib().q4o_ix_topk(_p(score), _p(sel), n_tok, stride, k_blk, ratio, pos0, width)
+    return sel
 
 
 def max_threads():

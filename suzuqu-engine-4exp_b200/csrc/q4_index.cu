@@ -1,0 +1,279 @@
+/*
+ * QSA indexer: the step that produces the 2051-wide selection lists the sparse decode consumes.
+ *
+ *   pool   qsa_pool_k / qsa_pool_dk (src/q4_rocm.cu:7366-7402, 7880-7933): block b of `ratio` tokens =
+ *          mean of their raw fp16 keys, RMSNorm, RoPE at the block's first position, fp32 [block][128]
+ *   score  qsa_score_k / qsa_score_dk (:7405-7436, 7469-7502): score[b] = sum_h relu(q_h . pool[b])
+ *          over the blocks the token can see -- at ctx 262 144 a 33.5 MB scan per layer, 30x the
+ *          bytes of the sparse attention it feeds, so this is the HBM-bound part
+ *   top-k  qsa_topk_k / the qsa_tk_* family (:7506-7666, 7722-7846): exact top-512 blocks by (score
+ *          descending, index ascending), expanded to positions plus the newest partial block
+ *
+ * Results are defined by the reference down to the order of the list, so the arithmetic keeps its
+ * association: the sum of squares is the same pairwise tree, a dot product is one fused multiply-add
+ * per dim in dim order (four heads = four independent chains per thread), and the selection is an
+ * exact radix select followed by an index-ordered compaction.  What changes is the mapping: a warp
+ * per pooled block with the tree in shuffles, a thread per pooled block for the scan with rows
+ * fetched as 16-byte loads that the L1 turns into whole lines, and one 1024-thread block per token
+ * for the whole selection (4 histogram passes with warp-aggregated shared-memory atomics, prefix
+ * scans for the ordered emit) instead of the reference's 12 launches per token.
+ */
+#include <math_constants.h>
+#include <string.h>
+
+#include "q4_internal.h"
+
+namespace {
+
+constexpr uint32_t IX_HD = 128;
+constexpr uint32_t IX_TK_THREADS = 1024, IX_MAX_KBLK = 512;
+
+/* ---- pool: one warp per block, lane l holds dims l, l+32, l+64, l+96 */
+__global__ void __launch_bounds__(128) q4_ix_pool_k(const __half *raw, float *pool, const float *wn, uint32_t ratio,
+                                                    uint32_t b0, uint32_t b1, uint32_t n_rot, float base, float eps,
+                                                    const int32_t *pp) {
+    const uint32_t lane = threadIdx.x & 31u, w = blockIdx.x * 4u + (threadIdx.x >> 5);
+    if (pp) {   /* device position: the block this token completes, if any */
+        const uint32_t pos = (uint32_t)*pp;
+        b0 = pos / ratio;
+        b1 = (pos + 1u) / ratio;
+    }
+    const uint32_t b = b0 + w;
+    if (b >= b1) return;
+    const __half *src = raw + (size_t)b * ratio * IX_HD;
+    float v[4], r[4];
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        float s = 0.f;
+        for (uint32_t j = 0; j < ratio; j++) s += __half2float(src[(size_t)j * IX_HD + lane + 32u * c]);
+        v[c] = __fdiv_rn(s, (float)ratio);
+        r[c] = __fmul_rn(v[c], v[c]);
+    }
+    /* red[d] += red[d + st] for st = 64, 32 is local to the lane; 16 .. 1 are shuffles */
+    float a = __fadd_rn(__fadd_rn(r[0], r[2]), __fadd_rn(r[1], r[3]));
+#pragma unroll
+    for (int st = 16; st > 0; st >>= 1) a = __fadd_rn(a, __shfl_down_sync(0xffffffffu, a, st));
+    const float tot = __shfl_sync(0xffffffffu, a, 0);
+    const float inv = rsqrtf(__fadd_rn(__fdiv_rn(tot, (float)IX_HD), eps));
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        const uint32_t d = lane + 32u * c;
+        v[c] = __fmul_rn(__fmul_rn(v[c], inv), wn ? wn[d] : 1.f);
+    }
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        const uint32_t d = lane + 32u * c;
+        const float other = __shfl_xor_sync(0xffffffffu, v[c], 1);
+        if ((d & ~1u) < n_rot) {
+            const uint32_t p = d >> 1;
+            const float freq = powf(base, -(float)p / (float)(n_rot / 2u));
+            const float ang = (float)(b * ratio) * freq;
+            const float cs = cosf(ang), sn = sinf(ang);
+            /* even dim: x0 * c - x1 * s; odd dim: x0 * s + x1 * c, with (x0, x1) the pair */
+            v[c] = (d & 1u) ? __fadd_rn(__fmul_rn(other, sn), __fmul_rn(v[c], cs))
+                            : __fsub_rn(__fmul_rn(v[c], cs), __fmul_rn(other, sn));
+        }
+        pool[(size_t)b * IX_HD + d] = v[c];
+    }
+}
+
+/* ---- score: one thread per pooled block, 4 heads = 4 fused-multiply-add chains in dim order */
+__global__ void __launch_bounds__(128) q4_ix_score_k(const float *q, const float *pool, float *score, uint32_t n_blocks,
+                                                     uint32_t stride, uint32_t n_head, uint32_t pos0, uint32_t ratio,
+                                                     const int32_t *pp) {
+    __shared__ float4 qs[IX_HD];   /* [dim] = the 4 heads' values (0 for heads that do not exist) */
+    const uint32_t t = blockIdx.y;
+    const uint32_t pos = (pp ? (uint32_t)*pp : pos0) + t;
+    const uint32_t n_vis = ratio ? (pos + 1u) / ratio : 0u;
+    if (pp) n_blocks = n_vis;      /* device position: the bound is derived here */
+    {
+        const uint32_t d = threadIdx.x;
+        float x[4] = {0.f, 0.f, 0.f, 0.f};
+        for (uint32_t h = 0; h < n_head; h++) x[h] = q[((size_t)t * n_head + h) * IX_HD + d];
+        qs[d] = make_float4(x[0], x[1], x[2], x[3]);
+    }
+    __syncthreads();
+    const uint32_t b = blockIdx.x * 128u + threadIdx.x;
+    if (b >= n_blocks) return;
+    float s = -1.0e30f;
+    if (b < n_vis) {
+        const float4 *row = reinterpret_cast<const float4 *>(pool + (size_t)b * IX_HD);
+        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll 8
+        for (uint32_t i = 0; i < IX_HD / 4; i++) {
+            const float4 k = __ldg(row + i);
+            const float4 q0 = qs[4 * i], q1 = qs[4 * i + 1], q2 = qs[4 * i + 2], q3 = qs[4 * i + 3];
+            d0 = __fmaf_rn(q0.x, k.x, d0); d1 = __fmaf_rn(q0.y, k.x, d1); d2 = __fmaf_rn(q0.z, k.x, d2); d3 = __fmaf_rn(q0.w, k.x, d3);
+            d0 = __fmaf_rn(q1.x, k.y, d0); d1 = __fmaf_rn(q1.y, k.y, d1); d2 = __fmaf_rn(q1.z, k.y, d2); d3 = __fmaf_rn(q1.w, k.y, d3);
+            d0 = __fmaf_rn(q2.x, k.z, d0); d1 = __fmaf_rn(q2.y, k.z, d1); d2 = __fmaf_rn(q2.z, k.z, d2); d3 = __fmaf_rn(q2.w, k.z, d3);
+            d0 = __fmaf_rn(q3.x, k.w, d0); d1 = __fmaf_rn(q3.y, k.w, d1); d2 = __fmaf_rn(q3.z, k.w, d2); d3 = __fmaf_rn(q3.w, k.w, d3);
+        }
+        const float dots[4] = {d0, d1, d2, d3};
+        s = 0.f;
+        for (uint32_t h = 0; h < n_head; h++) s = __fadd_rn(s, fmaxf(dots[h], 0.f));
+    }
+    score[(size_t)t * stride + b] = s;
+}
+
+/* ---- selection: one block per token */
+__device__ __forceinline__ uint32_t ix_key(float f) {   /* order-preserving uint of a float (:7464-7467) */
+    const uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+/* exclusive prefix sum of one value per thread over the block; returns the block total */
+__device__ uint32_t block_excl_scan(uint32_t v, uint32_t &excl, uint32_t *warp_tot /* [33] shared */) {
+    const uint32_t lane = threadIdx.x & 31u, w = threadIdx.x >> 5;
+    uint32_t x = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= (uint32_t)o) x += y;
+    }
+    __syncthreads();   /* warp_tot may still be read from the previous scan */
+    if (lane == 31) warp_tot[w] = x;
+    __syncthreads();
+    if (w == 0) {
+        uint32_t t = lane < IX_TK_THREADS / 32 ? warp_tot[lane] : 0u, s = t;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t y = __shfl_up_sync(0xffffffffu, s, o);
+            if (lane >= (uint32_t)o) s += y;
+        }
+        warp_tot[lane] = s - t;
+        if (lane == 31) warp_tot[32] = s;
+    }
+    __syncthreads();
+    excl = warp_tot[w] + x - v;
+    return warp_tot[32];
+}
+
+__global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topk_k(const float *score, int32_t *sel, uint32_t stride,
+                                                              uint32_t k_blk, uint32_t ratio, uint32_t pos0,
+                                                              uint32_t width, const int32_t *pp) {
+    __shared__ uint32_t hist[256], warp_tot[33], st_prefix, st_hi;
+    __shared__ int32_t chosen[IX_MAX_KBLK];
+    const uint32_t t = blockIdx.x, tx = threadIdx.x;
+    const uint32_t pos = (pp ? (uint32_t)*pp : pos0) + t;
+    const uint32_t n_vis = ratio ? (pos + 1u) / ratio : 0u;
+    const uint32_t need = n_vis < k_blk ? n_vis : k_blk;
+    const float *row = score + (size_t)t * stride;
+    int32_t *out = sel + (size_t)t * width;
+    if (need == n_vis) {   /* every complete block fits: the dense prefix */
+        for (uint32_t w = tx; w < width; w += IX_TK_THREADS) out[w] = w <= pos ? (int32_t)w : -1;
+        return;
+    }
+    /* exact need-th largest key: 4 passes over the 8-bit digits, most significant first */
+    if (tx == 0) { st_prefix = 0u; st_hi = 0u; }
+    for (int p = 0; p < 4; p++) {
+        if (tx < 256) hist[tx] = 0u;
+        __syncthreads();
+        const uint32_t sh = 24u - 8u * p, pre = st_prefix;
+        for (uint32_t b0 = 0; b0 < n_vis; b0 += IX_TK_THREADS) {
+            const uint32_t b = b0 + tx;
+            const bool live = b < n_vis;
+            const uint32_t u = live ? ix_key(__ldcg(row + b)) : 0u;
+            const bool in = live && (p == 0 || (u >> (sh + 8u)) == pre);
+            /* lanes that hit the same bin add once */
+            const uint32_t bin = in ? ((u >> sh) & 255u) : 256u + (tx & 31u);
+            const uint32_t peers = __match_any_sync(0xffffffffu, bin);
+            if (in && (uint32_t)(__ffs(peers) - 1) == (tx & 31u)) atomicAdd(&hist[bin], (uint32_t)__popc(peers));
+        }
+        __syncthreads();
+        if (tx == 0) {
+            const uint32_t target = need - st_hi;
+            uint32_t acc = 0, dg = 0;
+            for (int i = 255; i >= 0; i--) {
+                if (acc + hist[i] >= target) { dg = (uint32_t)i; break; }
+                acc += hist[i];
+            }
+            st_hi += acc;
+            st_prefix = (st_prefix << 8) | dg;
+        }
+        __syncthreads();
+    }
+    const uint32_t thr = st_prefix;
+    /* ordered compaction: blocks above the threshold in ascending index order, then threshold ties in
+     * ascending index order until `need` is full; each thread owns a contiguous slice of the row */
+    const uint32_t slice = (n_vis + IX_TK_THREADS - 1u) / IX_TK_THREADS;
+    const uint32_t c0 = min(tx * slice, n_vis), c1 = min(c0 + slice, n_vis);
+    uint32_t ng = 0, ne = 0;
+    for (uint32_t b = c0; b < c1; b++) {
+        const uint32_t u = ix_key(__ldcg(row + b));
+        ng += u > thr;
+        ne += u == thr;
+    }
+    uint32_t og, oe;
+    const uint32_t n_gt = block_excl_scan(ng, og, warp_tot);
+    (void)block_excl_scan(ne, oe, warp_tot);
+    for (uint32_t b = c0; b < c1; b++) {
+        const uint32_t u = ix_key(__ldcg(row + b));
+        if (u > thr) {
+            if (og < IX_MAX_KBLK) chosen[og] = (int32_t)b;
+            og++;
+        } else if (u == thr) {
+            if (n_gt + oe < need) chosen[n_gt + oe] = (int32_t)b;
+            oe++;
+        }
+    }
+    __syncthreads();
+    const uint32_t ncs = need * ratio;
+    for (uint32_t w = tx; w < width; w += IX_TK_THREADS) {
+        int32_t v;
+        if (w < ncs) {
+            const uint32_t i = w / ratio, j = w - i * ratio;
+            v = (int32_t)((uint32_t)chosen[i] * ratio + j);
+        } else {
+            const uint32_t tail = n_vis * ratio + (w - ncs);
+            v = tail <= pos ? (int32_t)tail : -1;
+        }
+        out[w] = v;
+    }
+}
+
+}  // namespace
+
+/* ======================================================================= reference ABI ===== */
+extern "C" bool q4_hip_qsa_pool(const void *raw_f16, float *pool, const float *wn, uint32_t hd, uint32_t ratio,
+                                uint32_t b0, uint32_t b1, uint32_t n_rot, float rope_base, float eps) {
+    if (!g_q4.ok || !raw_f16 || !pool || b1 <= b0 || hd != IX_HD || ratio == 0) return false;
+    q4_ix_pool_k<<<(b1 - b0 + 3u) / 4u, 128, 0, g_q4.stream>>>((const __half *)raw_f16, pool, wn, ratio, b0, b1, n_rot,
+                                                             rope_base, eps, nullptr);
+    return q4i_check(cudaGetLastError(), "qsa_pool launch");
+}
+extern "C" bool q4_hip_qsa_pool_d(const void *raw, float *pool, const float *wn, uint32_t hd, uint32_t ratio,
+                                  uint32_t n_rot, float rope_base, float eps) {
+    if (!g_q4.ok || !g_q4.pos_d || !raw || !pool || hd != IX_HD || ratio == 0) return false;
+    q4_ix_pool_k<<<1, 128, 0, g_q4.stream>>>((const __half *)raw, pool, wn, ratio, 0, 0, n_rot, rope_base, eps, g_q4.pos_d);
+    return q4i_check(cudaGetLastError(), "qsa_pool_d launch");
+}
+extern "C" bool q4_hip_qsa_score(const float *q, const float *pool, float *score, uint32_t n_tok, uint32_t n_blocks,
+                                 uint32_t stride, uint32_t n_head, uint32_t hd, uint32_t pos0, uint32_t ratio) {
+    if (!g_q4.ok || !q || !pool || !score || n_tok == 0 || hd != IX_HD || n_head == 0 || n_head > 4) return false;
+    if (n_blocks == 0) return true;
+    q4_ix_score_k<<<dim3((n_blocks + 127u) / 128u, n_tok), 128, 0, g_q4.stream>>>(q, pool, score, n_blocks, stride, n_head,
+                                                                                 pos0, ratio, nullptr);
+    return q4i_check(cudaGetLastError(), "qsa_score launch");
+}
+/* Device position (graph-captured decode): the grid covers `stride` blocks, the bound comes from the
+ * position word inside the kernel. */
+extern "C" bool q4_hip_qsa_score_d(const float *q, const float *pool, float *score, uint32_t stride, uint32_t n_head,
+                                   uint32_t hd, uint32_t ratio) {
+    if (!g_q4.ok || !g_q4.pos_d || !q || !pool || !score || hd != IX_HD || n_head == 0 || n_head > 4 || stride == 0)
+        return false;
+    q4_ix_score_k<<<dim3((stride + 127u) / 128u, 1), 128, 0, g_q4.stream>>>(q, pool, score, 0, stride, n_head, 0, ratio,
+                                                                           g_q4.pos_d);
+    return q4i_check(cudaGetLastError(), "qsa_score_d launch");
+}
+extern "C" bool q4_hip_qsa_topk(const float *score, int32_t *sel, uint32_t n_tok, uint32_t n_blocks, uint32_t stride,
+                                uint32_t k_blk, uint32_t ratio, uint32_t pos0, uint32_t width) {
+    (void)n_blocks;
+    if (!g_q4.ok || !score || !sel || n_tok == 0 || k_blk == 0 || k_blk > IX_MAX_KBLK || width == 0) return false;
+    q4_ix_topk_k<<<n_tok, IX_TK_THREADS, 0, g_q4.stream>>>(score, sel, stride, k_blk, ratio, pos0, width, nullptr);
+    return q4i_check(cudaGetLastError(), "qsa_topk launch");
+}
+extern "C" bool q4_hip_qsa_topk_d(const float *score, int32_t *sel, uint32_t stride, uint32_t k_blk, uint32_t ratio,
+                                  uint32_t width) {
+    if (!g_q4.ok || !g_q4.pos_d || !score || !sel || k_blk == 0 || k_blk > IX_MAX_KBLK || width == 0) return false;
+    q4_ix_topk_k<<<1, IX_TK_THREADS, 0, g_q4.stream>>>(score, sel, stride, k_blk, ratio, 0, width, g_q4.pos_d);
+    return q4i_check(cudaGetLastError(), "qsa_topk_d launch");
+}

@@ -62,6 +62,12 @@ SIGNATURES = {
     "q4_gpu_kv_decode_noalloc": (_b, [_v, _u32, _v, _i, _v, _v, _u32, _v, _u32, _u32, _u32, _f]),
     "q4_gpu_kv_decode_partial": (_b, [_v, _u32, _v, _i, _v, _u32, _v, _u32, _u32, _u32, _f]),
     "q4_gpu_lse_merge": (_b, [_v, _u32, _u32, _u32, _v, _v]),
+    "q4_hip_qsa_pool": (_b, [_v, _v, _v, _u32, _u32, _u32, _u32, _u32, _f, _f]),
+    "q4_hip_qsa_pool_d": (_b, [_v, _v, _v, _u32, _u32, _u32, _f, _f]),
+    "q4_hip_qsa_score": (_b, [_v, _v, _v, _u32, _u32, _u32, _u32, _u32, _u32, _u32]),
+    "q4_hip_qsa_score_d": (_b, [_v, _v, _v, _u32, _u32, _u32, _u32]),
+    "q4_hip_qsa_topk": (_b, [_v, _v, _u32, _u32, _u32, _u32, _u32, _u32, _u32]),
+    "q4_hip_qsa_topk_d": (_b, [_v, _v, _u32, _u32, _u32, _u32]),
     "q4_gpu_xchg_create": (_v, [_u32, _u32, _u32, _u32, _u32]), "q4_gpu_xchg_destroy": (None, [_v]),
     "q4_gpu_xchg_handle": (_b, [_v, _v]), "q4_gpu_xchg_window": (_v, [_v]),
     "q4_gpu_xchg_attach": (_b, [_v, _u32, _v]), "q4_gpu_xchg_attach_ptr": (_b, [_v, _u32, _v]),

@@ -201,3 +201,72 @@ def test_indexed_padding_and_all_masked(oracle):
     dead = np.full(40, -1, np.int32)
     z = oracle.attn(q, kc, vc, None, n_head, n_kvh, hd, 1, 0, n, 0.125, 2, idx=dead, width=40)[0]
     assert not z.any()
+
+
+# ------------------------------------------------------------------------------ QSA indexer
+def _ix_case(oracle, seed, n_tok, n_head=4, ratio=4):
+    raw = oracle.f32_to_f16(oracle.normal(seed, 0, n_tok * 128).reshape(n_tok, 128))
+    wn = 1.0 + 0.1 * oracle.normal(seed, 1, 128)
+    q = oracle.normal(seed, 2, n_head * 128).reshape(1, n_head, 128)
+    return raw, wn.astype(np.float32), q
+
+
+def test_indexer_pool_and_score_match_float64(oracle):
+    """qsa_pool_k / qsa_score_k restatements against a float64 evaluation of the same formulas"""
+    n_tok, ratio, n_rot, base, eps = 1027, 4, 64, 1e7, 1e-6
+    raw, wn, q = _ix_case(oracle, 41, n_tok)
+    nb = n_tok // ratio
+    pool = oracle.ix_pool(raw, wn, ratio, 0, nb, n_rot, base, eps)
+    x = raw[:nb * ratio].view(np.float16).reshape(nb, ratio, 128).astype(np.float64)
+    v = x.mean(axis=1)
+    v = v / np.sqrt((v * v).mean(axis=1, keepdims=True) + eps) * wn
+    ref = v.copy()
+    p = np.arange(n_rot // 2)
+    freq = base ** (-p / (n_rot // 2))
+    ang = (np.arange(nb) * ratio)[:, None].astype(np.float64) * freq[None, :]
+    ref[:, 0:n_rot:2] = v[:, 0:n_rot:2] * np.cos(ang) - v[:, 1:n_rot:2] * np.sin(ang)
+    ref[:, 1:n_rot:2] = v[:, 0:n_rot:2] * np.sin(ang) + v[:, 1:n_rot:2] * np.cos(ang)
+    assert np.abs(pool - ref).max() < 2e-3          # fp32 angles at positions ~1e3
+    assert np.abs(pool[:8] - ref[:8]).max() < 1e-5
+    pos = n_tok - 1
+    score = oracle.ix_score(q, pool, 1, nb + 3, nb + 8, 4, pos, ratio)
+    want = np.maximum(pool.astype(np.float64) @ q[0].astype(np.float64).T, 0).sum(axis=1)
+    n_vis = (pos + 1) // ratio
+    assert np.allclose(score[0, :n_vis], want[:n_vis], rtol=1e-5, atol=1e-4)
+    assert (score[0, n_vis:nb + 3] == np.float32(-1e30)).all()
+
+
+def _topk_reference(row, n_vis, need, ratio, pos, width):
+    """independent statement of the selection: sort by (score desc, index asc), keep `need`, emit above-threshold
+    blocks in index order, then threshold ties in index order"""
+    order = sorted(range(n_vis), key=lambda b: (-float(row[b]), b))[:need]
+    thr = row[order[-1]]
+    above = sorted(b for b in order if row[b] > thr)
+    ties = sorted(b for b in order if row[b] == thr)
+    sel = [b * ratio + j for b in above + ties for j in range(ratio)]
+    sel += list(range(n_vis * ratio, pos + 1))
+    sel = sel[:width] + [-1] * max(0, width - len(sel))
+    return np.array(sel, np.int32)
+
+
+@pytest.mark.parametrize("n_tok,k_blk,width", [(4099, 512, 2051), (1500, 512, 2051), (2051, 512, 2051), (2052, 512, 2051),
+                                                (300, 16, 67), (70, 16, 67)])
+def test_indexer_topk_order_and_ties(oracle, n_tok, k_blk, width):
+    """qsa_topk_k restatement: exact set, the reference's emit order, ties at the threshold broken by index
+    (relu makes exact zeros, and quantised scores make plenty of ties), dense prefix when every block fits"""
+    ratio, pos = 4, n_tok - 1
+    n_vis = (pos + 1) // ratio
+    rng = np.random.default_rng(n_tok)
+    for trial in range(3):
+        row = np.maximum(rng.standard_normal(n_vis + 5), 0).astype(np.float32)        # many exact zeros
+        if trial == 1:
+            row = np.round(row * 4) / 4                                                # heavy ties everywhere
+        if trial == 2:
+            row[:] = 1.0                                                               # all equal
+        sel = oracle.ix_topk(row[None, :], 1, n_vis + 5, k_blk, ratio, pos, width)[0]
+        need = min(n_vis, k_blk)
+        if need == n_vis:
+            want = np.array([w if w <= pos else -1 for w in range(width)], np.int32)
+        else:
+            want = _topk_reference(row, n_vis, need, ratio, pos, width)
+        assert np.array_equal(sel, want)
