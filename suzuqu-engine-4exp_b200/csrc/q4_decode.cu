@@ -64,7 +64,7 @@ struct DecParams {
     float scale_log2e;
     uint32_t S;
     uint32_t cluster; /* blocks per cluster (0 = none): the S splits of a unit form one cluster and merge through DSMEM */
-    uint32_t debug;   /* measurement aid: 1 = copy the tiles but skip the arithmetic */
+    uint32_t debug;   /* experiment builds (Q4_DEC_TIMING) only: 1 = copy the tiles but skip the arithmetic */
     float *scratch;
     uint32_t *counters;
     uint32_t *err;
@@ -944,11 +944,13 @@ q4_decode_k(const DecParams P) {
             uint32_t st[2];
             st[0] = ring + (it % RING_STAGES) * RING_STAGE_BYTES;
             st[1] = ring + ((it + 1) % RING_STAGES) * RING_STAGE_BYTES;
-            if (P.debug) {
+#ifdef Q4_DEC_TIMING
+            if (P.debug) {   /* experiment builds only: copy the tiles but skip the arithmetic */
                 acc[0][0][0] += __uint_as_float(lds32(st[0] + 4 * lane) ^ lds32(st[1] + 2048 + 4 * lane));
                 __syncwarp();
                 continue;
             }
+#endif
 
             /* ---- S^T = K . Q^T for both tiles */
             float sc[2][NHT][4];
@@ -1427,11 +1429,14 @@ bool q4i_decode(const Q4DecodeArgs &a) {
     p.scale_log2e = a.scale * 1.4426950408889634f;
     p.S = S;
     p.cluster = cluster;
+    p.debug = 0;
+#ifdef Q4_DEC_TIMING
     {
         static int dbg = -1;
         if (dbg < 0) { const char *e = getenv("Q4_DEC_DEBUG"); dbg = e ? atoi(e) : 0; }
         p.debug = (uint32_t)dbg;
     }
+#endif
     p.scratch = scratch;
     p.counters = counters;
     p.err = g_q4.err_d;

@@ -13,10 +13,11 @@
  * association: the sum of squares is the same pairwise tree, a dot product is one fused multiply-add
  * per dim in dim order (four heads = four independent chains per thread), and the selection is an
  * exact radix select followed by an index-ordered compaction.  What changes is the mapping: a warp
- * per pooled block with the tree in shuffles, a thread per pooled block for the scan with rows
- * fetched as 16-byte loads that the L1 turns into whole lines, and one 1024-thread block per token
- * for the whole selection (4 histogram passes with warp-aggregated shared-memory atomics, prefix
- * scans for the ordered emit) instead of the reference's 12 launches per token.
+ * per pooled block with the tree in shuffles, a thread per pooled block for the scan with each warp's
+ * 32 rows staged in shared memory by coalesced asynchronous copies, and one 1024-thread block per token
+ * for the whole selection (4 histogram passes with shared-memory atomics, one per warp where the lanes agree, over keys
+ * fetched 16 independent loads at a time, the digit picked by a warp scan, ballot ranks and a scan
+ * over the warps for the ordered emit) instead of the reference's 12 launches per token.
  */
 #include <math_constants.h>
 #include <string.h>
@@ -77,42 +78,73 @@ __global__ void __launch_bounds__(128) q4_ix_pool_k(const __half *raw, float *po
     }
 }
 
-/* ---- score: one thread per pooled block, 4 heads = 4 fused-multiply-add chains in dim order */
+/* ---- score: one thread per pooled block, 4 heads = 4 fused-multiply-add chains in dim order.
+ * A warp first brings its 32 rows (512 B each) into shared memory with one 16-byte asynchronous copy
+ * per lane and row -- fully coalesced, 16 KB in flight per warp -- then every lane walks its own row
+ * there.  Rows are 132 floats apart: 16-byte reads of eight consecutive rows fall into eight
+ * different bank groups, so the walk is conflict free; the query is read as a broadcast. */
+constexpr uint32_t SC_ROW_FLOATS = IX_HD + 4;
+constexpr uint32_t SC_SMEM = 4u * 32u * SC_ROW_FLOATS * sizeof(float) + IX_HD * sizeof(float4);
 __global__ void __launch_bounds__(128) q4_ix_score_k(const float *q, const float *pool, float *score, uint32_t n_blocks,
                                                      uint32_t stride, uint32_t n_head, uint32_t pos0, uint32_t ratio,
                                                      const int32_t *pp) {
-    __shared__ float4 qs[IX_HD];   /* [dim] = the 4 heads' values (0 for heads that do not exist) */
-    const uint32_t t = blockIdx.y;
+    extern __shared__ __align__(16) uint8_t sc_smem[];
+    float4 *qs = reinterpret_cast<float4 *>(sc_smem);   /* [dim] = the 4 heads' values (0 for heads that do not exist) */
+    float *tiles = reinterpret_cast<float *>(sc_smem + IX_HD * sizeof(float4));
+    const uint32_t t = blockIdx.y, lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const uint32_t pos = (pp ? (uint32_t)*pp : pos0) + t;
     const uint32_t n_vis = ratio ? (pos + 1u) / ratio : 0u;
     if (pp) n_blocks = n_vis;      /* device position: the bound is derived here */
+    const uint32_t b0 = blockIdx.x * 128u + warp * 32u;       /* this warp's first row */
+    const uint32_t n_rows = b0 < n_vis ? min(32u, n_vis - b0) : 0u;
+    float *tile = tiles + (size_t)warp * 32u * SC_ROW_FLOATS;
+    {
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(tile) + lane * 16u;
+        const float *src = pool + (size_t)b0 * IX_HD + lane * 4u;
+        for (uint32_t r = 0; r < n_rows; r++)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + r * SC_ROW_FLOATS * 4u),
+                         "l"(src + (size_t)r * IX_HD) : "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     {
         const uint32_t d = threadIdx.x;
-        float x[4] = {0.f, 0.f, 0.f, 0.f};
-        for (uint32_t h = 0; h < n_head; h++) x[h] = q[((size_t)t * n_head + h) * IX_HD + d];
-        qs[d] = make_float4(x[0], x[1], x[2], x[3]);
+        const float *qt = q + (size_t)t * n_head * IX_HD + d;
+        qs[d] = make_float4(qt[0], n_head > 1 ? qt[IX_HD] : 0.f, n_head > 2 ? qt[2 * IX_HD] : 0.f,
+                            n_head > 3 ? qt[3 * IX_HD] : 0.f);
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
-    const uint32_t b = blockIdx.x * 128u + threadIdx.x;
+    const uint32_t b = b0 + lane;
     if (b >= n_blocks) return;
     float s = -1.0e30f;
     if (b < n_vis) {
-        const float4 *row = reinterpret_cast<const float4 *>(pool + (size_t)b * IX_HD);
+        const float4 *row = reinterpret_cast<const float4 *>(tile + (size_t)lane * SC_ROW_FLOATS);
         float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll 8
         for (uint32_t i = 0; i < IX_HD / 4; i++) {
-            const float4 k = __ldg(row + i);
+            const float4 k = row[i];
             const float4 q0 = qs[4 * i], q1 = qs[4 * i + 1], q2 = qs[4 * i + 2], q3 = qs[4 * i + 3];
             d0 = __fmaf_rn(q0.x, k.x, d0); d1 = __fmaf_rn(q0.y, k.x, d1); d2 = __fmaf_rn(q0.z, k.x, d2); d3 = __fmaf_rn(q0.w, k.x, d3);
             d0 = __fmaf_rn(q1.x, k.y, d0); d1 = __fmaf_rn(q1.y, k.y, d1); d2 = __fmaf_rn(q1.z, k.y, d2); d3 = __fmaf_rn(q1.w, k.y, d3);
             d0 = __fmaf_rn(q2.x, k.z, d0); d1 = __fmaf_rn(q2.y, k.z, d1); d2 = __fmaf_rn(q2.z, k.z, d2); d3 = __fmaf_rn(q2.w, k.z, d3);
             d0 = __fmaf_rn(q3.x, k.w, d0); d1 = __fmaf_rn(q3.y, k.w, d1); d2 = __fmaf_rn(q3.z, k.w, d2); d3 = __fmaf_rn(q3.w, k.w, d3);
         }
-        const float dots[4] = {d0, d1, d2, d3};
-        s = 0.f;
-        for (uint32_t h = 0; h < n_head; h++) s = __fadd_rn(s, fmaxf(dots[h], 0.f));
+        s = __fadd_rn(0.f, fmaxf(d0, 0.f));          /* s = 0; s += relu(dot_h) in head order */
+        if (n_head > 1) s = __fadd_rn(s, fmaxf(d1, 0.f));
+        if (n_head > 2) s = __fadd_rn(s, fmaxf(d2, 0.f));
+        if (n_head > 3) s = __fadd_rn(s, fmaxf(d3, 0.f));
     }
     score[(size_t)t * stride + b] = s;
+}
+bool score_smem_ready() {
+    static bool done = false;
+    if (!done) {
+        if (!q4i_check(cudaFuncSetAttribute(q4_ix_score_k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SC_SMEM),
+                       "qsa_score smem attribute"))
+            return false;
+        done = true;
+    }
+    return true;
 }
 
 /* ---- selection: one block per token */
@@ -147,12 +179,35 @@ __device__ uint32_t block_excl_scan(uint32_t v, uint32_t &excl, uint32_t *warp_t
     return warp_tot[32];
 }
 
+/* A warp walks its contiguous share of the row in batches of IX_BATCH x 32 keys: the IX_BATCH loads of
+ * a batch are independent (one memory round trip per batch instead of one per key), lane l of load k
+ * holds index base + 32 k + l, so (batch, k, lane) is ascending index order inside the warp. */
+constexpr uint32_t IX_BATCH = 16;
+template <typename F>
+__device__ __forceinline__ void ix_walk(const float *row, uint32_t n_vis, uint32_t per_warp, F f) {
+    const uint32_t lane = threadIdx.x & 31u, w0 = (threadIdx.x >> 5) * per_warp;
+    const uint32_t w1 = min(w0 + per_warp, n_vis);
+    for (uint32_t base = w0; base < w1; base += 32u * IX_BATCH) {
+        uint32_t key[IX_BATCH];
+#pragma unroll
+        for (uint32_t k = 0; k < IX_BATCH; k++) {
+            const uint32_t b = base + 32u * k + lane;
+            key[k] = b < w1 ? ix_key(__ldcg(row + b)) : 0u;
+        }
+#pragma unroll
+        for (uint32_t k = 0; k < IX_BATCH; k++) {
+            const uint32_t b = base + 32u * k + lane;
+            f(b, key[k], b < w1);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topk_k(const float *score, int32_t *sel, uint32_t stride,
                                                               uint32_t k_blk, uint32_t ratio, uint32_t pos0,
                                                               uint32_t width, const int32_t *pp) {
     __shared__ uint32_t hist[256], warp_tot[33], st_prefix, st_hi;
     __shared__ int32_t chosen[IX_MAX_KBLK];
-    const uint32_t t = blockIdx.x, tx = threadIdx.x;
+    const uint32_t t = blockIdx.x, tx = threadIdx.x, lane = tx & 31u;
     const uint32_t pos = (pp ? (uint32_t)*pp : pos0) + t;
     const uint32_t n_vis = ratio ? (pos + 1u) / ratio : 0u;
     const uint32_t need = n_vis < k_blk ? n_vis : k_blk;
@@ -162,59 +217,88 @@ __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topk_k(const float *score
         for (uint32_t w = tx; w < width; w += IX_TK_THREADS) out[w] = w <= pos ? (int32_t)w : -1;
         return;
     }
+    /* contiguous share of each of the 32 warps, a whole number of batches */
+    const uint32_t per_warp = ((n_vis + 31u) / 32u + 32u * IX_BATCH - 1u) / (32u * IX_BATCH) * (32u * IX_BATCH);
+
     /* exact need-th largest key: 4 passes over the 8-bit digits, most significant first */
     if (tx == 0) { st_prefix = 0u; st_hi = 0u; }
     for (int p = 0; p < 4; p++) {
         if (tx < 256) hist[tx] = 0u;
         __syncthreads();
         const uint32_t sh = 24u - 8u * p, pre = st_prefix;
-        for (uint32_t b0 = 0; b0 < n_vis; b0 += IX_TK_THREADS) {
-            const uint32_t b = b0 + tx;
-            const bool live = b < n_vis;
-            const uint32_t u = live ? ix_key(__ldcg(row + b)) : 0u;
+        ix_walk(row, n_vis, per_warp, [&](uint32_t, uint32_t u, bool live) {
             const bool in = live && (p == 0 || (u >> (sh + 8u)) == pre);
-            /* lanes that hit the same bin add once */
-            const uint32_t bin = in ? ((u >> sh) & 255u) : 256u + (tx & 31u);
-            const uint32_t peers = __match_any_sync(0xffffffffu, bin);
-            if (in && (uint32_t)(__ffs(peers) - 1) == (tx & 31u)) atomicAdd(&hist[bin], (uint32_t)__popc(peers));
-        }
-        __syncthreads();
-        if (tx == 0) {
-            const uint32_t target = need - st_hi;
-            uint32_t acc = 0, dg = 0;
-            for (int i = 255; i >= 0; i--) {
-                if (acc + hist[i] >= target) { dg = (uint32_t)i; break; }
-                acc += hist[i];
+            const uint32_t bin = (u >> sh) & 255u;
+            /* Keys often share a digit (the leading digits of non-negative scores, relu zeros, padding):
+             * when every participating lane has the same bin one lane adds the count; otherwise the bins
+             * are spread and each lane adds for itself. */
+            const uint32_t m = __ballot_sync(0xffffffffu, in);
+            if (m) {
+                const uint32_t first = __shfl_sync(0xffffffffu, bin, __ffs(m) - 1);
+                if (__all_sync(0xffffffffu, !in || bin == first)) {
+                    if (lane == (uint32_t)(__ffs(m) - 1)) atomicAdd(&hist[first], (uint32_t)__popc(m));
+                } else if (in) {
+                    atomicAdd(&hist[bin], 1u);
+                }
             }
-            st_hi += acc;
-            st_prefix = (st_prefix << 8) | dg;
+        });
+        __syncthreads();
+        if (tx < 32) {
+            /* digit = the highest bin whose count, added to those above it, reaches the target: lane l owns
+             * bins 255 - 8 l .. 248 - 8 l, a warp scan gives the count above each lane's bins */
+            const uint32_t target = need - st_hi;
+            uint32_t c[8], tot = 0;
+#pragma unroll
+            for (int j = 0; j < 8; j++) { c[j] = hist[255 - 8 * (int)lane - j]; tot += c[j]; }
+            uint32_t incl = tot;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t y = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= (uint32_t)o) incl += y;
+            }
+            uint32_t above = incl - tot;
+            if (above < target && incl >= target) {   /* exactly one lane */
+                uint32_t dg = 0;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    if (above + c[j] >= target) { dg = 255u - 8u * lane - (uint32_t)j; break; }
+                    above += c[j];
+                }
+                st_hi += above;
+                st_prefix = (pre << 8) | dg;
+            }
         }
         __syncthreads();
     }
-    const uint32_t thr = st_prefix;
+    const uint32_t thr = st_prefix, n_gt = st_hi;   /* keys above the threshold: n_gt < need <= n_gt + ties */
+
     /* ordered compaction: blocks above the threshold in ascending index order, then threshold ties in
-     * ascending index order until `need` is full; each thread owns a contiguous slice of the row */
-    const uint32_t slice = (n_vis + IX_TK_THREADS - 1u) / IX_TK_THREADS;
-    const uint32_t c0 = min(tx * slice, n_vis), c1 = min(c0 + slice, n_vis);
+     * ascending index order until `need` is full.  Per-warp counts, a scan over the warps, then ranks
+     * by ballots. */
     uint32_t ng = 0, ne = 0;
-    for (uint32_t b = c0; b < c1; b++) {
-        const uint32_t u = ix_key(__ldcg(row + b));
-        ng += u > thr;
-        ne += u == thr;
-    }
+    ix_walk(row, n_vis, per_warp, [&](uint32_t, uint32_t u, bool live) {
+        ng += __popc(__ballot_sync(0xffffffffu, live && u > thr));
+        ne += __popc(__ballot_sync(0xffffffffu, live && u == thr));
+    });
     uint32_t og, oe;
-    const uint32_t n_gt = block_excl_scan(ng, og, warp_tot);
-    (void)block_excl_scan(ne, oe, warp_tot);
-    for (uint32_t b = c0; b < c1; b++) {
-        const uint32_t u = ix_key(__ldcg(row + b));
-        if (u > thr) {
-            if (og < IX_MAX_KBLK) chosen[og] = (int32_t)b;
-            og++;
-        } else if (u == thr) {
-            if (n_gt + oe < need) chosen[n_gt + oe] = (int32_t)b;
-            oe++;
+    (void)block_excl_scan(lane == 0 ? ng : 0u, og, warp_tot);
+    (void)block_excl_scan(lane == 0 ? ne : 0u, oe, warp_tot);
+    og = __shfl_sync(0xffffffffu, og, 0);
+    oe = __shfl_sync(0xffffffffu, oe, 0);
+    const uint32_t lt = (1u << lane) - 1u;
+    ix_walk(row, n_vis, per_warp, [&](uint32_t b, uint32_t u, bool live) {
+        const bool gt = live && u > thr, eq = live && u == thr;
+        const uint32_t mg = __ballot_sync(0xffffffffu, gt), me = __ballot_sync(0xffffffffu, eq);
+        if (gt) {
+            const uint32_t at = og + __popc(mg & lt);
+            if (at < IX_MAX_KBLK) chosen[at] = (int32_t)b;
+        } else if (eq) {
+            const uint32_t at = n_gt + oe + __popc(me & lt);
+            if (at < need) chosen[at] = (int32_t)b;
         }
-    }
+        og += __popc(mg);
+        oe += __popc(me);
+    });
     __syncthreads();
     const uint32_t ncs = need * ratio;
     for (uint32_t w = tx; w < width; w += IX_TK_THREADS) {
@@ -250,7 +334,8 @@ extern "C" bool q4_hip_qsa_score(const float *q, const float *pool, float *score
                                  uint32_t stride, uint32_t n_head, uint32_t hd, uint32_t pos0, uint32_t ratio) {
     if (!g_q4.ok || !q || !pool || !score || n_tok == 0 || hd != IX_HD || n_head == 0 || n_head > 4) return false;
     if (n_blocks == 0) return true;
-    q4_ix_score_k<<<dim3((n_blocks + 127u) / 128u, n_tok), 128, 0, g_q4.stream>>>(q, pool, score, n_blocks, stride, n_head,
+    if (!score_smem_ready()) return false;
+    q4_ix_score_k<<<dim3((n_blocks + 127u) / 128u, n_tok), 128, SC_SMEM, g_q4.stream>>>(q, pool, score, n_blocks, stride, n_head,
                                                                                  pos0, ratio, nullptr);
     return q4i_check(cudaGetLastError(), "qsa_score launch");
 }
@@ -260,7 +345,8 @@ extern "C" bool q4_hip_qsa_score_d(const float *q, const float *pool, float *sco
                                    uint32_t hd, uint32_t ratio) {
     if (!g_q4.ok || !g_q4.pos_d || !q || !pool || !score || hd != IX_HD || n_head == 0 || n_head > 4 || stride == 0)
         return false;
-    q4_ix_score_k<<<dim3((stride + 127u) / 128u, 1), 128, 0, g_q4.stream>>>(q, pool, score, 0, stride, n_head, 0, ratio,
+    if (!score_smem_ready()) return false;
+    q4_ix_score_k<<<dim3((stride + 127u) / 128u, 1), 128, SC_SMEM, g_q4.stream>>>(q, pool, score, 0, stride, n_head, 0, ratio,
                                                                            g_q4.pos_d);
     return q4i_check(cudaGetLastError(), "qsa_score_d launch");
 }
