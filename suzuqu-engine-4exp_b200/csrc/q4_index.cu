@@ -14,10 +14,11 @@
  * per dim in dim order (four heads = four independent chains per thread), and the selection is an
  * exact radix select followed by an index-ordered compaction.  What changes is the mapping: a warp
  * per pooled block with the tree in shuffles, a thread per pooled block for the scan with each warp's
- * 32 rows staged in shared memory by coalesced asynchronous copies, and one 1024-thread block per token
- * for the whole selection (4 histogram passes with shared-memory atomics, one per warp where the lanes agree, over keys
- * fetched 16 independent loads at a time, the digit picked by a warp scan, ballot ranks and a scan
- * over the warps for the ordered emit) instead of the reference's 12 launches per token.
+ * 32 rows staged in shared memory by coalesced asynchronous copies, and ONE launch per token for the
+ * whole selection instead of the reference's 12: a cluster of 8 blocks with the keys in registers, the
+ * histograms summed through distributed shared memory, the digit picked by a warp scan, ballot ranks
+ * and scans over warps and blocks for the ordered emit (rows longer than 65 536 blocks: one block that
+ * re-reads the row, 16 independent loads at a time).
  */
 #include <math_constants.h>
 #include <string.h>
@@ -202,7 +203,7 @@ __device__ __forceinline__ void ix_walk(const float *row, uint32_t n_vis, uint32
     }
 }
 
-__global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topk_k(const float *score, int32_t *sel, uint32_t stride,
+__global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topk1_k(const float *score, int32_t *sel, uint32_t stride,
                                                               uint32_t k_blk, uint32_t ratio, uint32_t pos0,
                                                               uint32_t width, const int32_t *pp) {
     __shared__ uint32_t hist[256], warp_tot[33], st_prefix, st_hi;
@@ -314,6 +315,200 @@ __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topk_k(const float *score
     }
 }
 
+/* ---- selection by a cluster of 8 blocks (rows of up to 65 536 pooled blocks = ctx 262 144): every
+ * thread keeps its 8 keys in registers (block r, warp w, step i, lane l holds index 8192 r + 256 w +
+ * 32 i + l, so (r, w, i, l) is ascending index order), the per-pass histograms are summed into block
+ * 0 through distributed shared memory, every block picks the digit from that sum, and the ordered
+ * emit ranks by ballots, a scan over the warps and a scan over the blocks.  One cluster barrier per
+ * pass; 8 SMs instead of one. */
+constexpr uint32_t TKC_BLOCKS = 8, TKC_KPT = 8, TKC_MAX_ROW = TKC_BLOCKS * IX_TK_THREADS * TKC_KPT;
+__device__ __forceinline__ uint32_t tkc_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void tkc_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t tkc_remote(const void *p, uint32_t rank) {
+    uint32_t a = (uint32_t)__cvta_generic_to_shared(p), r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ uint32_t tkc_ld(uint32_t ra) {
+    uint32_t v;
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(ra) : "memory");
+    return v;
+}
+__device__ __forceinline__ void tkc_st(uint32_t ra, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(ra), "r"(v) : "memory");
+}
+__device__ __forceinline__ void tkc_red_add(uint32_t ra, uint32_t v) {
+    asm volatile("red.relaxed.cluster.shared::cluster.add.u32 [%0], %1;" ::"r"(ra), "r"(v) : "memory");
+}
+
+__global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topkc_k(const float *score, int32_t *sel, uint32_t stride,
+                                                               uint32_t k_blk, uint32_t ratio, uint32_t pos0,
+                                                               uint32_t width, const int32_t *pp) {
+    __shared__ uint32_t hist[256];
+    __shared__ uint32_t ghist[4][256];            /* block 0's copy is the cluster-wide sum, one per pass */
+    __shared__ uint32_t cta_cnt[TKC_BLOCKS][2];   /* block 0's copy: (above, ties) of every block */
+    __shared__ int32_t chosen[IX_MAX_KBLK];       /* block 0's copy is the list */
+    __shared__ uint32_t warp_tot[33], st_prefix, st_hi;
+    const uint32_t t = blockIdx.y, tx = threadIdx.x, lane = tx & 31u, warp = tx >> 5, rank = tkc_rank();
+    const uint32_t pos = (pp ? (uint32_t)*pp : pos0) + t;
+    const uint32_t n_vis = ratio ? (pos + 1u) / ratio : 0u;
+    const uint32_t need = n_vis < k_blk ? n_vis : k_blk;
+    const float *row = score + (size_t)t * stride;
+    int32_t *out = sel + (size_t)t * width;
+    const uint32_t w_per = (width + TKC_BLOCKS - 1u) / TKC_BLOCKS;
+    const uint32_t w0 = min(rank * w_per, width), w1 = min(w0 + w_per, width);   /* this block's slice of the list */
+    if (need == n_vis) {   /* every complete block fits: the dense prefix (same decision in all blocks) */
+        for (uint32_t w = w0 + tx; w < w1; w += IX_TK_THREADS) out[w] = w <= pos ? (int32_t)w : -1;
+        return;
+    }
+    const uint32_t base = rank * (IX_TK_THREADS * TKC_KPT) + warp * (32u * TKC_KPT) + lane;
+    uint32_t key[TKC_KPT];
+#pragma unroll
+    for (uint32_t i = 0; i < TKC_KPT; i++) {
+        const uint32_t b = base + 32u * i;
+        key[i] = b < n_vis ? ix_key(__ldcg(row + b)) : 0u;
+    }
+    if (rank == 0) {
+        for (uint32_t i = tx; i < 4u * 256u; i += IX_TK_THREADS) (&ghist[0][0])[i] = 0u;
+    }
+    if (tx == 0) { st_prefix = 0u; st_hi = 0u; }
+    tkc_sync();   /* block 0's sums are zero before anyone adds to them */
+
+    for (int p = 0; p < 4; p++) {
+        if (tx < 256) hist[tx] = 0u;
+        __syncthreads();
+        const uint32_t sh = 24u - 8u * p, pre = st_prefix;
+#pragma unroll
+        for (uint32_t i = 0; i < TKC_KPT; i++) {
+            const uint32_t u = key[i];
+            const bool in = base + 32u * i < n_vis && (p == 0 || (u >> (sh + 8u)) == pre);
+            const uint32_t bin = (u >> sh) & 255u;
+            const uint32_t m = __ballot_sync(0xffffffffu, in);
+            if (m) {   /* one add per warp where the lanes agree, else one per lane */
+                const uint32_t first = __shfl_sync(0xffffffffu, bin, __ffs(m) - 1);
+                if (__all_sync(0xffffffffu, !in || bin == first)) {
+                    if (lane == (uint32_t)(__ffs(m) - 1)) atomicAdd(&hist[first], (uint32_t)__popc(m));
+                } else if (in) {
+                    atomicAdd(&hist[bin], 1u);
+                }
+            }
+        }
+        __syncthreads();
+        if (tx < 256 && hist[tx]) tkc_red_add(tkc_remote(&ghist[p][tx], 0), hist[tx]);
+        tkc_sync();
+        if (tx < 32) {
+            /* digit = the highest bin whose count, added to those above it, reaches the target: lane l owns
+             * bins 255 - 8 l .. 248 - 8 l of the cluster-wide sum */
+            const uint32_t target = need - st_hi;
+            uint32_t c[8], tot = 0;
+#pragma unroll
+            for (int j = 0; j < 8; j++) { c[j] = tkc_ld(tkc_remote(&ghist[p][255 - 8 * (int)lane - j], 0)); tot += c[j]; }
+            uint32_t incl = tot;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t y = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= (uint32_t)o) incl += y;
+            }
+            uint32_t above = incl - tot;
+            if (above < target && incl >= target) {   /* exactly one lane */
+                uint32_t dg = 0;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    if (above + c[j] >= target) { dg = 255u - 8u * lane - (uint32_t)j; break; }
+                    above += c[j];
+                }
+                st_hi += above;
+                st_prefix = (pre << 8) | dg;
+            }
+        }
+        __syncthreads();
+    }
+    const uint32_t thr = st_prefix, n_gt = st_hi;
+
+    /* counts: per warp by ballots, per block by a scan over the warps, per cluster through block 0 */
+    uint32_t ng = 0, ne = 0;
+#pragma unroll
+    for (uint32_t i = 0; i < TKC_KPT; i++) {
+        const bool live = base + 32u * i < n_vis;
+        ng += __popc(__ballot_sync(0xffffffffu, live && key[i] > thr));
+        ne += __popc(__ballot_sync(0xffffffffu, live && key[i] == thr));
+    }
+    uint32_t og, oe;
+    const uint32_t tot_g = block_excl_scan(lane == 0 ? ng : 0u, og, warp_tot);
+    const uint32_t tot_e = block_excl_scan(lane == 0 ? ne : 0u, oe, warp_tot);
+    og = __shfl_sync(0xffffffffu, og, 0);
+    oe = __shfl_sync(0xffffffffu, oe, 0);
+    if (tx == 0) {
+        tkc_st(tkc_remote(&cta_cnt[rank][0], 0), tot_g);
+        tkc_st(tkc_remote(&cta_cnt[rank][1], 0), tot_e);
+    }
+    tkc_sync();
+    for (uint32_t r = 0; r < rank; r++) {
+        og += tkc_ld(tkc_remote(&cta_cnt[r][0], 0));
+        oe += tkc_ld(tkc_remote(&cta_cnt[r][1], 0));
+    }
+    /* ordered emit into block 0's list: above the threshold in index order, then ties until `need` is full */
+    const uint32_t lt = (1u << lane) - 1u;
+#pragma unroll
+    for (uint32_t i = 0; i < TKC_KPT; i++) {
+        const uint32_t b = base + 32u * i;
+        const bool live = b < n_vis, gt = live && key[i] > thr, eq = live && key[i] == thr;
+        const uint32_t mg = __ballot_sync(0xffffffffu, gt), me = __ballot_sync(0xffffffffu, eq);
+        if (gt) {
+            const uint32_t at = og + __popc(mg & lt);
+            if (at < IX_MAX_KBLK) tkc_st(tkc_remote(&chosen[at], 0), b);
+        } else if (eq) {
+            const uint32_t at = n_gt + oe + __popc(me & lt);
+            if (at < need) tkc_st(tkc_remote(&chosen[at], 0), b);
+        }
+        og += __popc(mg);
+        oe += __popc(me);
+    }
+    tkc_sync();
+    const uint32_t ncs = need * ratio;
+    for (uint32_t w = w0 + tx; w < w1; w += IX_TK_THREADS) {
+        int32_t v;
+        if (w < ncs) {
+            const uint32_t i = w / ratio, j = w - i * ratio;
+            v = (int32_t)(tkc_ld(tkc_remote(&chosen[i], 0)) * ratio + j);
+        } else {
+            const uint32_t tail = n_vis * ratio + (w - ncs);
+            v = tail <= pos ? (int32_t)tail : -1;
+        }
+        out[w] = v;
+    }
+    tkc_sync();   /* block 0's shared memory stays until every block has read the list */
+}
+
+/* rows that fit the cluster kernel go there, longer ones to the single block */
+bool launch_topk(const float *score, int32_t *sel, uint32_t n_tok, uint32_t stride, uint32_t k_blk, uint32_t ratio,
+                 uint32_t pos0, uint32_t width, const int32_t *pp) {
+    if (stride <= TKC_MAX_ROW) {
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3(TKC_BLOCKS, n_tok);
+        cfg.blockDim = dim3(IX_TK_THREADS);
+        cfg.stream = g_q4.stream;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = TKC_BLOCKS;
+        at[0].val.clusterDim.y = 1;
+        at[0].val.clusterDim.z = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        return q4i_check(cudaLaunchKernelEx(&cfg, q4_ix_topkc_k, score, sel, stride, k_blk, ratio, pos0, width, pp),
+                         "qsa_topk launch");
+    }
+    q4_ix_topk1_k<<<n_tok, IX_TK_THREADS, 0, g_q4.stream>>>(score, sel, stride, k_blk, ratio, pos0, width, pp);
+    return q4i_check(cudaGetLastError(), "qsa_topk launch");
+}
+
 }  // namespace
 
 /* ======================================================================= reference ABI ===== */
@@ -354,12 +549,10 @@ extern "C" bool q4_hip_qsa_topk(const float *score, int32_t *sel, uint32_t n_tok
                                 uint32_t k_blk, uint32_t ratio, uint32_t pos0, uint32_t width) {
     (void)n_blocks;
     if (!g_q4.ok || !score || !sel || n_tok == 0 || k_blk == 0 || k_blk > IX_MAX_KBLK || width == 0) return false;
-    q4_ix_topk_k<<<n_tok, IX_TK_THREADS, 0, g_q4.stream>>>(score, sel, stride, k_blk, ratio, pos0, width, nullptr);
-    return q4i_check(cudaGetLastError(), "qsa_topk launch");
+    return launch_topk(score, sel, n_tok, stride, k_blk, ratio, pos0, width, nullptr);
 }
 extern "C" bool q4_hip_qsa_topk_d(const float *score, int32_t *sel, uint32_t stride, uint32_t k_blk, uint32_t ratio,
                                   uint32_t width) {
     if (!g_q4.ok || !g_q4.pos_d || !score || !sel || k_blk == 0 || k_blk > IX_MAX_KBLK || width == 0) return false;
-    q4_ix_topk_k<<<1, IX_TK_THREADS, 0, g_q4.stream>>>(score, sel, stride, k_blk, ratio, 0, width, g_q4.pos_d);
-    return q4i_check(cudaGetLastError(), "qsa_topk_d launch");
+    return launch_topk(score, sel, 1, stride, k_blk, ratio, 0, width, g_q4.pos_d);
 }
