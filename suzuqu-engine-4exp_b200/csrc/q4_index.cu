@@ -80,64 +80,79 @@ __global__ void __launch_bounds__(128) q4_ix_pool_k(const __half *raw, float *po
 }
 
 /* ---- score: one thread per pooled block, 4 heads = 4 fused-multiply-add chains in dim order.
- * A warp first brings its 32 rows (512 B each) into shared memory with one 16-byte asynchronous copy
- * per lane and row -- fully coalesced, 16 KB in flight per warp -- then every lane walks its own row
- * there.  Rows are 132 floats apart: 16-byte reads of eight consecutive rows fall into eight
- * different bank groups, so the walk is conflict free; the query is read as a broadcast. */
-constexpr uint32_t SC_ROW_FLOATS = IX_HD + 4;
-constexpr uint32_t SC_SMEM = 4u * 32u * SC_ROW_FLOATS * sizeof(float) + IX_HD * sizeof(float4);
-__global__ void __launch_bounds__(128) q4_ix_score_k(const float *q, const float *pool, float *score, uint32_t n_blocks,
-                                                     uint32_t stride, uint32_t n_head, uint32_t pos0, uint32_t ratio,
-                                                     const int32_t *pp) {
+ * Persistent warps: a warp takes every n-th tile of 32 rows (512 B each), brings the next tile into
+ * the other of its two shared-memory buffers with one 16-byte asynchronous copy per lane and row --
+ * fully coalesced, 16 KB in flight per warp while the previous tile is being scored -- and every lane
+ * walks its own row there.  Rows are 132 floats apart: 16-byte reads of eight consecutive rows fall
+ * into eight different bank groups, so the walk is conflict free; the query is read as a broadcast. */
+constexpr uint32_t SC_ROW_FLOATS = IX_HD + 4, SC_WARPS = 2;
+constexpr uint32_t SC_TILE_BYTES = 32u * SC_ROW_FLOATS * sizeof(float);
+constexpr uint32_t SC_SMEM = SC_WARPS * 2u * SC_TILE_BYTES + IX_HD * sizeof(float4);
+__global__ void __launch_bounds__(SC_WARPS * 32) q4_ix_score_k(const float *q, const float *pool, float *score,
+                                                               uint32_t n_blocks, uint32_t stride, uint32_t n_head,
+                                                               uint32_t pos0, uint32_t ratio, const int32_t *pp) {
     extern __shared__ __align__(16) uint8_t sc_smem[];
     float4 *qs = reinterpret_cast<float4 *>(sc_smem);   /* [dim] = the 4 heads' values (0 for heads that do not exist) */
-    float *tiles = reinterpret_cast<float *>(sc_smem + IX_HD * sizeof(float4));
     const uint32_t t = blockIdx.y, lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const uint32_t pos = (pp ? (uint32_t)*pp : pos0) + t;
     const uint32_t n_vis = ratio ? (pos + 1u) / ratio : 0u;
     if (pp) n_blocks = n_vis;      /* device position: the bound is derived here */
-    const uint32_t b0 = blockIdx.x * 128u + warp * 32u;       /* this warp's first row */
-    const uint32_t n_rows = b0 < n_vis ? min(32u, n_vis - b0) : 0u;
-    float *tile = tiles + (size_t)warp * 32u * SC_ROW_FLOATS;
-    {
-        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(tile) + lane * 16u;
-        const float *src = pool + (size_t)b0 * IX_HD + lane * 4u;
-        for (uint32_t r = 0; r < n_rows; r++)
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + r * SC_ROW_FLOATS * 4u),
-                         "l"(src + (size_t)r * IX_HD) : "memory");
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    }
-    {
-        const uint32_t d = threadIdx.x;
+    for (uint32_t d = threadIdx.x; d < IX_HD; d += SC_WARPS * 32u) {
         const float *qt = q + (size_t)t * n_head * IX_HD + d;
         qs[d] = make_float4(qt[0], n_head > 1 ? qt[IX_HD] : 0.f, n_head > 2 ? qt[2 * IX_HD] : 0.f,
                             n_head > 3 ? qt[3 * IX_HD] : 0.f);
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
-    const uint32_t b = b0 + lane;
-    if (b >= n_blocks) return;
-    float s = -1.0e30f;
-    if (b < n_vis) {
-        const float4 *row = reinterpret_cast<const float4 *>(tile + (size_t)lane * SC_ROW_FLOATS);
-        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
-#pragma unroll 8
-        for (uint32_t i = 0; i < IX_HD / 4; i++) {
-            const float4 k = row[i];
-            const float4 q0 = qs[4 * i], q1 = qs[4 * i + 1], q2 = qs[4 * i + 2], q3 = qs[4 * i + 3];
-            d0 = __fmaf_rn(q0.x, k.x, d0); d1 = __fmaf_rn(q0.y, k.x, d1); d2 = __fmaf_rn(q0.z, k.x, d2); d3 = __fmaf_rn(q0.w, k.x, d3);
-            d0 = __fmaf_rn(q1.x, k.y, d0); d1 = __fmaf_rn(q1.y, k.y, d1); d2 = __fmaf_rn(q1.z, k.y, d2); d3 = __fmaf_rn(q1.w, k.y, d3);
-            d0 = __fmaf_rn(q2.x, k.z, d0); d1 = __fmaf_rn(q2.y, k.z, d1); d2 = __fmaf_rn(q2.z, k.z, d2); d3 = __fmaf_rn(q2.w, k.z, d3);
-            d0 = __fmaf_rn(q3.x, k.w, d0); d1 = __fmaf_rn(q3.y, k.w, d1); d2 = __fmaf_rn(q3.z, k.w, d2); d3 = __fmaf_rn(q3.w, k.w, d3);
+    const uint32_t buf0 = (uint32_t)__cvta_generic_to_shared(sc_smem + IX_HD * sizeof(float4)) + warp * 2u * SC_TILE_BYTES;
+    const uint32_t lim = min(n_blocks, n_vis);                       /* rows to score */
+    const uint32_t n_tiles = (lim + 31u) / 32u;
+    const uint32_t step = gridDim.x * SC_WARPS, first = blockIdx.x * SC_WARPS + warp;
+    auto fetch = [&](uint32_t tile, uint32_t which) {
+        if (tile < n_tiles) {
+            const uint32_t r0 = tile * 32u, rows = min(32u, lim - r0);
+            const uint32_t dst = buf0 + which * SC_TILE_BYTES + lane * 16u;
+            const float *src = pool + (size_t)r0 * IX_HD + lane * 4u;
+            for (uint32_t r = 0; r < rows; r++)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + r * SC_ROW_FLOATS * 4u),
+                             "l"(src + (size_t)r * IX_HD) : "memory");
         }
-        s = __fadd_rn(0.f, fmaxf(d0, 0.f));          /* s = 0; s += relu(dot_h) in head order */
-        if (n_head > 1) s = __fadd_rn(s, fmaxf(d1, 0.f));
-        if (n_head > 2) s = __fadd_rn(s, fmaxf(d2, 0.f));
-        if (n_head > 3) s = __fadd_rn(s, fmaxf(d3, 0.f));
+        asm volatile("cp.async.commit_group;" ::: "memory");   /* one group per call keeps the wait count uniform */
+    };
+    fetch(first, 0);
+    uint32_t which = 0;
+    for (uint32_t tile = first; tile < n_tiles; tile += step, which ^= 1u) {
+        fetch(tile + step, which ^ 1u);
+        asm volatile("cp.async.wait_group 1;" ::: "memory");   /* this tile has landed, the next may be in flight */
+        __syncwarp();
+        const uint32_t b = tile * 32u + lane;
+        if (b < lim) {
+            const uint32_t row = buf0 + which * SC_TILE_BYTES + lane * SC_ROW_FLOATS * 4u;
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll 8
+            for (uint32_t i = 0; i < IX_HD / 4; i++) {
+                float4 k;
+                asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(k.x), "=f"(k.y), "=f"(k.z), "=f"(k.w) : "r"(row + 16u * i));
+                const float4 q0 = qs[4 * i], q1 = qs[4 * i + 1], q2 = qs[4 * i + 2], q3 = qs[4 * i + 3];
+                d0 = __fmaf_rn(q0.x, k.x, d0); d1 = __fmaf_rn(q0.y, k.x, d1); d2 = __fmaf_rn(q0.z, k.x, d2); d3 = __fmaf_rn(q0.w, k.x, d3);
+                d0 = __fmaf_rn(q1.x, k.y, d0); d1 = __fmaf_rn(q1.y, k.y, d1); d2 = __fmaf_rn(q1.z, k.y, d2); d3 = __fmaf_rn(q1.w, k.y, d3);
+                d0 = __fmaf_rn(q2.x, k.z, d0); d1 = __fmaf_rn(q2.y, k.z, d1); d2 = __fmaf_rn(q2.z, k.z, d2); d3 = __fmaf_rn(q2.w, k.z, d3);
+                d0 = __fmaf_rn(q3.x, k.w, d0); d1 = __fmaf_rn(q3.y, k.w, d1); d2 = __fmaf_rn(q3.z, k.w, d2); d3 = __fmaf_rn(q3.w, k.w, d3);
+            }
+            float sc = __fadd_rn(0.f, fmaxf(d0, 0.f));          /* s = 0; s += relu(dot_h) in head order */
+            if (n_head > 1) sc = __fadd_rn(sc, fmaxf(d1, 0.f));
+            if (n_head > 2) sc = __fadd_rn(sc, fmaxf(d2, 0.f));
+            if (n_head > 3) sc = __fadd_rn(sc, fmaxf(d3, 0.f));
+            score[(size_t)t * stride + b] = sc;
+        }
+        __syncwarp();   /* every lane is done with this buffer before the fetch after next refills it */
     }
-    score[(size_t)t * stride + b] = s;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    /* blocks the token cannot see (host-position form only): -1e30 */
+    for (uint32_t b = n_vis + blockIdx.x * (SC_WARPS * 32u) + threadIdx.x; b < n_blocks; b += gridDim.x * SC_WARPS * 32u)
+        score[(size_t)t * stride + b] = -1.0e30f;
 }
-bool score_smem_ready() {
+bool score_launch(const float *q, const float *pool, float *score, uint32_t n_tok, uint32_t n_blocks, uint32_t stride,
+                  uint32_t n_head, uint32_t pos0, uint32_t ratio, const int32_t *pp) {
     static bool done = false;
     if (!done) {
         if (!q4i_check(cudaFuncSetAttribute(q4_ix_score_k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SC_SMEM),
@@ -145,7 +160,16 @@ bool score_smem_ready() {
             return false;
         done = true;
     }
-    return true;
+    /* persistent grid: 3 blocks of 2 warps per SM share 227 KB; fewer when the row is short */
+    const uint32_t rows = pp ? stride : n_blocks;
+    uint32_t gx = (uint32_t)g_q4.sm_count * 3u;
+    const uint32_t need = (rows + SC_WARPS * 32u - 1u) / (SC_WARPS * 32u);
+    if (n_tok > 1) gx = (gx + n_tok - 1u) / n_tok;
+    if (gx > need) gx = need;
+    if (gx < 1) gx = 1;
+    q4_ix_score_k<<<dim3(gx, n_tok), SC_WARPS * 32, SC_SMEM, g_q4.stream>>>(q, pool, score, n_blocks, stride, n_head, pos0,
+                                                                            ratio, pp);
+    return q4i_check(cudaGetLastError(), "qsa_score launch");
 }
 
 /* ---- selection: one block per token */
@@ -529,10 +553,7 @@ extern "C" bool q4_hip_qsa_score(const float *q, const float *pool, float *score
                                  uint32_t stride, uint32_t n_head, uint32_t hd, uint32_t pos0, uint32_t ratio) {
     if (!g_q4.ok || !q || !pool || !score || n_tok == 0 || hd != IX_HD || n_head == 0 || n_head > 4) return false;
     if (n_blocks == 0) return true;
-    if (!score_smem_ready()) return false;
-    q4_ix_score_k<<<dim3((n_blocks + 127u) / 128u, n_tok), 128, SC_SMEM, g_q4.stream>>>(q, pool, score, n_blocks, stride, n_head,
-                                                                                 pos0, ratio, nullptr);
-    return q4i_check(cudaGetLastError(), "qsa_score launch");
+    return score_launch(q, pool, score, n_tok, n_blocks, stride, n_head, pos0, ratio, nullptr);
 }
 /* Device position (graph-captured decode): the grid covers `stride` blocks, the bound comes from the
  * position word inside the kernel. */
@@ -540,10 +561,7 @@ extern "C" bool q4_hip_qsa_score_d(const float *q, const float *pool, float *sco
                                    uint32_t hd, uint32_t ratio) {
     if (!g_q4.ok || !g_q4.pos_d || !q || !pool || !score || hd != IX_HD || n_head == 0 || n_head > 4 || stride == 0)
         return false;
-    if (!score_smem_ready()) return false;
-    q4_ix_score_k<<<dim3((stride + 127u) / 128u, 1), 128, SC_SMEM, g_q4.stream>>>(q, pool, score, 0, stride, n_head, 0, ratio,
-                                                                           g_q4.pos_d);
-    return q4i_check(cudaGetLastError(), "qsa_score_d launch");
+    return score_launch(q, pool, score, 1, 0, stride, n_head, 0, ratio, g_q4.pos_d);
 }
 extern "C" bool q4_hip_qsa_topk(const float *score, int32_t *sel, uint32_t n_tok, uint32_t n_blocks, uint32_t stride,
                                 uint32_t k_blk, uint32_t ratio, uint32_t pos0, uint32_t width) {
