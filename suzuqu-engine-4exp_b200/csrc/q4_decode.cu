@@ -877,7 +877,9 @@ q4_decode_k(const DecParams P) {
         int32_t pa = my_pos(0), pb = my_pos(1), pc = my_pos(2), pd = my_pos(3), pe = my_pos(4), pf = my_pos(5);
         Q4_STAMP_DEP(8, max_kv);
         Q4_STAMP_DEP(9, pa | pb);
+        Q4_STAMP(12);
         issue(0, pa);
+        Q4_STAMP(13);
         issue(1, pb);
         Q4_STAMP(10);
         pa = pc; pb = pd;      /* next iteration's stages */

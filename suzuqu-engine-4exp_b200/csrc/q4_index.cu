@@ -426,13 +426,15 @@ __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topkc_k(const float *scor
         __syncthreads();
         if (tx < 256 && hist[tx]) tkc_red_add(tkc_remote(&ghist[p][tx], 0), hist[tx]);
         tkc_sync();
+        if (tx < 256) hist[tx] = tkc_ld(tkc_remote(&ghist[p][tx], 0));   /* the cluster-wide sum, one load per thread */
+        __syncthreads();
         if (tx < 32) {
             /* digit = the highest bin whose count, added to those above it, reaches the target: lane l owns
              * bins 255 - 8 l .. 248 - 8 l of the cluster-wide sum */
             const uint32_t target = need - st_hi;
             uint32_t c[8], tot = 0;
 #pragma unroll
-            for (int j = 0; j < 8; j++) { c[j] = tkc_ld(tkc_remote(&ghist[p][255 - 8 * (int)lane - j], 0)); tot += c[j]; }
+            for (int j = 0; j < 8; j++) { c[j] = hist[255 - 8 * (int)lane - j]; tot += c[j]; }
             uint32_t incl = tot;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
