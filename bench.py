@@ -282,12 +282,29 @@ class Group:
             for s, c in enumerate(self.ctxs):
                 for kh in range(N_KVH):
                     idx[layer, s, kh] = selection(rng, c)
-        self.idx_h = torch.from_numpy(idx).pin_memory()
-        self.q_h = torch.randn(N_LAYERS, n, N_HEAD, HD).to(torch.bfloat16).pin_memory()
-        self.k_h = torch.randn(N_LAYERS, n, KVW).pin_memory()
-        self.v_h = torch.randn(N_LAYERS, n, KVW).pin_memory()
+        # The step's inputs live in ONE pinned host buffer and ONE device buffer (q | k | v | lists, each part
+        # 256-byte aligned), so the upload of a step is a single copy; the tensors below are views into them.
+        parts = [("q", torch.bfloat16, (N_LAYERS, n, N_HEAD, HD)), ("k", torch.float32, (N_LAYERS, n, KVW)),
+                 ("v", torch.float32, (N_LAYERS, n, KVW)), ("idx", torch.int32, (N_LAYERS, n, N_KVH, WIDTH))]
+        offs, total = {}, 0
+        for name, dt, shape in parts:
+            offs[name] = total
+            total += (int(np.prod(shape)) * torch.empty(0, dtype=dt).element_size() + 255) // 256 * 256
+        self.in_h = torch.empty(total, dtype=torch.uint8).pin_memory()
+        self.in_d = torch.empty(total, dtype=torch.uint8, device="cuda")
+
+        def view(buf, name, dt, shape):
+            nbytes = int(np.prod(shape)) * torch.empty(0, dtype=dt).element_size()
+            return buf[offs[name]:offs[name] + nbytes].view(dt).view(*shape)
+        for name, dt, shape in parts:
+            setattr(self, name + "_h", view(self.in_h, name, dt, shape))
+            setattr(self, name, view(self.in_d, name, dt, shape))
+        self.idx_h.copy_(torch.from_numpy(idx))
+        self.q_h.copy_(torch.randn(N_LAYERS, n, N_HEAD, HD).to(torch.bfloat16))
+        self.k_h.copy_(torch.randn(N_LAYERS, n, KVW))
+        self.v_h.copy_(torch.randn(N_LAYERS, n, KVW))
+        self.in_d.copy_(self.in_h)
         self.out_h = torch.empty(N_LAYERS, n, N_HEAD, HD).pin_memory()
-        self.idx, self.q, self.k, self.v = self.idx_h.cuda(), self.q_h.cuda(), self.k_h.cuda(), self.v_h.cuda()
         self.out = torch.empty(N_LAYERS, n, N_HEAD, HD, device="cuda")
         self.t = 0
         self.graph = None
@@ -317,8 +334,7 @@ class Group:
         previous step that read these device buffers"""
         if self.ev_comp is not None:
             cs.wait_event(self.ev_comp)
-        for d, h in ((self.q, self.q_h), (self.k, self.k_h), (self.v, self.v_h), (self.idx, self.idx_h)):
-            assert L.q4_hip_copy_h2d(d.data_ptr(), h.data_ptr(), h.numel() * h.element_size())
+        assert L.q4_hip_copy_h2d(self.in_d.data_ptr(), self.in_h.data_ptr(), self.in_h.numel())
         self.ev_in = torch.cuda.Event()
         self.ev_in.record(cs)
 
@@ -337,7 +353,7 @@ class Group:
         self.ev_done.record(ds)
 
     def e2e_bytes(self):
-        h2d = sum(h.numel() * h.element_size() for h in (self.q_h, self.k_h, self.v_h, self.idx_h)) + 4 * self.n
+        h2d = self.in_h.numel() + 4 * self.n          # the packed inputs + the positions
         return h2d, self.out_h.numel() * 4
 
     def algorithmic_bytes_per_layer(self):
@@ -488,8 +504,53 @@ def extras_indexer(torch, q4gpu, L, ext, peak_gbs):
         timed(torch, ext, one, 3)
         res[name] = 1e6 * timed(torch, ext, one, 10) / (10 * N_LAYERS)
         L.q4_hip_graph_free(gr)
+    # ---- the whole decode-attention step of one session at ctx 262144, selection included: per layer score,
+    # select, then the fused append + sparse decode over the list just produced (one list shared by both kv
+    # heads, as the reference's); 24 graphs with different indexer queries rotate so that the gathered rows
+    # (13 MB per graph) do not stay in L2
+    R = 24
+    st = q4gpu.KVStore(N_LAYERS, N_KVH, HD, pos + 1, q4gpu.KIND_Q8)
+    q4gpu.use_torch_stream()
+    fill_store(torch, st, pos + 1)
+    torch.cuda.synchronize()
+    L.q4_gpu_set_stream(None)
+    qix = torch.randn(R, N_LAYERS, n_head, HD, device="cuda")
+    qa = torch.randn(N_LAYERS, N_HEAD, HD, device="cuda").to(torch.bfloat16)
+    knew = torch.randn(N_LAYERS, KVW, device="cuda")
+    vnew = torch.randn(N_LAYERS, KVW, device="cuda")
+    out = torch.empty(N_LAYERS, N_HEAD, HD, device="cuda")
+    torch.cuda.synchronize()
+    L.q4_hip_pos_push(pos)
+
+    def layer_step(r, l):
+        assert L.q4_hip_qsa_score_d(qix[r, l].data_ptr(), pool[l].data_ptr(), score[l].data_ptr(), nb, n_head, HD, ratio)
+        assert L.q4_hip_qsa_topk_d(score[l].data_ptr(), sel[l].data_ptr(), nb, k_blk, ratio, WIDTH)
+        st.append_decode_d(l, knew[l], vnew[l], qa[l], out[l], N_HEAD, SCALE, idx=sel[l], width=WIDTH, idx_kvh_stride=0,
+                           q_bf16=True)
+    graphs = []
+    for r in range(R):
+        if r == 0:
+            for l in range(N_LAYERS):
+                layer_step(r, l)
+        assert L.q4_hip_graph_begin() == 1
+        for l in range(N_LAYERS):
+            layer_step(r, l)
+        gr = L.q4_hip_graph_end()
+        assert gr
+        graphs.append(gr)
+
+    def one(i):
+        assert L.q4_hip_graph_launch(graphs[i % R])
+    timed(torch, ext, one, R)
+    res["select_plus_attend_us_per_layer"] = 1e6 * timed(torch, ext, one, 2 * R) / (2 * R * N_LAYERS)
+    status = L.q4_gpu_last_error()
+    assert status == 0, "device status %#x" % status
+    for gr in graphs:
+        L.q4_hip_graph_free(gr)
+    st.close()
     by = nb * HD * 4
-    res.update({"workload": "QSA indexer, ctx 262144: 65536 pooled blocks x 4 heads scored, exact top-512 + tail -> 2051 positions",
+    res.update({"workload": "QSA indexer, ctx 262144: 65536 pooled blocks x 4 heads scored, exact top-512 + tail -> 2051 positions; "
+                            "select_plus_attend = score + select + fused append + sparse decode over the produced list",
                 "pool_bytes_per_layer": by, "score_gbs": by / res["score_us_per_layer"] / 1e3,
                 "score_frac_of_measured_hbm": by / res["score_us_per_layer"] / 1e3 / peak_gbs})
     return res

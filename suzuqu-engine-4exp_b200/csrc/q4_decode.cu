@@ -51,7 +51,7 @@ constexpr uint32_t DEC_GROUP = 16;   /* records merged per level of the two-leve
 
 struct DecParams {
     Q4Cache one;
-    const Q4Cache *const *many;
+    const Q4Cache *many;
     uint32_t layer, n_head, n_kvh, gqa;
     const void *q;
     int q_bf16;
@@ -568,7 +568,7 @@ q4_decode_k(const DecParams P) {
     const uint32_t split = blockIdx.x, kh = blockIdx.y, u = blockIdx.z;
     const uint32_t S = P.S;
 
-    const Q4Cache C = P.many ? *P.many[u] : P.one;
+    const Q4Cache C = P.many ? P.many[u] : P.one;
     /* Programmatic dependent launch: the blocks of this launch may already be resident while the previous
      * kernel of the stream drains.  Only the cache view above (written when the store was created or bound)
      * is read before this point; positions, lists, queries and rows are read after it. */

@@ -124,7 +124,7 @@ void q4i_prefill_release();
 /* decode attention launcher (q4_decode.cu) */
 struct Q4DecodeArgs {
     Q4Cache one;                 /* used when many == nullptr */
-    const Q4Cache *const *many;  /* device array of device Q4Cache pointers, one per session */
+    const Q4Cache *many;         /* device array of cache views, one per session */
     int layout;                  /* LAY_* */
     uint32_t layer, n_units;     /* units = sessions (many) or tokens (one) */
     uint32_t n_head, n_kvh, hd;

@@ -21,7 +21,7 @@ namespace {
 
 struct AppendParams {
     Q4Cache one;
-    const Q4Cache *const *many;   /* one cache per row (batched sessions) */
+    const Q4Cache *many;          /* one cache view per row (batched sessions), device array */
     uint32_t layer, n_rows, n_kvh, hd;
     const float *k, *v;           /* [n_rows][n_kvh*hd] */
     const int32_t *pos;           /* device positions (per row if many, else one word) or null */
@@ -76,7 +76,7 @@ __global__ void q4_append_k(const AppendParams P) {
     float d = 0.f, id = 0.f;
     if (LAY == LAY_Q8P || LAY == LAY_Q8R) q4d_block_scale(x, d, id);
     if (!live) return;
-    const Q4Cache C = P.many ? *P.many[r] : P.one;
+    const Q4Cache C = P.many ? P.many[r] : P.one;
     const uint32_t p = P.pos ? (uint32_t)P.pos[P.many ? r : 0] + (P.many ? 0u : r) : P.pos0 + r;
     if (p >= C.max_kv) {
         if (w == 0) atomicOr(P.err, (uint32_t)Q4E_RANGE);
@@ -469,8 +469,7 @@ extern "C" bool q4_gpu_kv_decode_partial(const q4_gpu_kv *kv, uint32_t layer, co
 struct q4_gpu_batch {
     uint32_t max_sessions, n;
     q4_gpu_kv **kv;
-    const Q4Cache **h_views;      /* pinned mirror of the device pointer table */
-    const Q4Cache **d_views;
+    Q4Cache *d_views;             /* device array of the bound stores' views (one load, no pointer chase) */
     int32_t *pos_d, *pos_h;       /* pos_h: pinned ring of 8 uploads, each slot guarded by an event */
     cudaEvent_t pos_ev[8];
     uint32_t ring, max_pos;
@@ -482,8 +481,7 @@ extern "C" q4_gpu_batch *q4_gpu_batch_create(uint32_t max_sessions) {
     if (!b) return nullptr;
     b->max_sessions = max_sessions;
     b->kv = (q4_gpu_kv **)calloc(max_sessions, sizeof(q4_gpu_kv *));
-    bool ok = b->kv && cudaMallocHost(&b->h_views, sizeof(Q4Cache *) * max_sessions) == cudaSuccess &&
-              cudaMalloc(&b->d_views, sizeof(Q4Cache *) * max_sessions) == cudaSuccess &&
+    bool ok = b->kv && cudaMalloc(&b->d_views, sizeof(Q4Cache) * max_sessions) == cudaSuccess &&
               cudaMalloc(&b->pos_d, sizeof(int32_t) * max_sessions) == cudaSuccess &&
               cudaMallocHost(&b->pos_h, sizeof(int32_t) * max_sessions * 8) == cudaSuccess;
     if (ok) ok = cudaMemset(b->pos_d, 0, sizeof(int32_t) * max_sessions) == cudaSuccess;
@@ -495,12 +493,11 @@ extern "C" q4_gpu_batch *q4_gpu_batch_create(uint32_t max_sessions) {
         q4_gpu_batch_destroy(b);
         return nullptr;
     }
-    memset(b->h_views, 0, sizeof(Q4Cache *) * max_sessions);
+    if (cudaMemset(b->d_views, 0, sizeof(Q4Cache) * max_sessions) != cudaSuccess) (void)cudaGetLastError();
     return b;
 }
 extern "C" void q4_gpu_batch_destroy(q4_gpu_batch *b) {
     if (!b) return;
-    if (b->h_views) cudaFreeHost(b->h_views);
     if (b->d_views) cudaFree(b->d_views);
     if (b->pos_d) cudaFree(b->pos_d);
     if (b->pos_h) cudaFreeHost(b->pos_h);
@@ -519,10 +516,10 @@ extern "C" bool q4_gpu_batch_bind(q4_gpu_batch *b, uint32_t slot, q4_gpu_kv *kv)
                           "batch_bind: stores of one batch must share shape and kind");
     }
     b->kv[slot] = kv;
-    b->h_views[slot] = kv->d_view;
     if (slot + 1 > b->n) b->n = slot + 1;
-    if (!q4i_check(cudaMemcpyAsync(b->d_views + slot, b->h_views + slot, sizeof(Q4Cache *), cudaMemcpyHostToDevice,
-                                   g_q4.stream), "batch_bind upload"))
+    /* device-to-device from the store's own device copy of its view: no host buffer to keep alive */
+    if (!q4i_check(cudaMemcpyAsync(b->d_views + slot, kv->d_view, sizeof(Q4Cache), cudaMemcpyDeviceToDevice, g_q4.stream),
+                   "batch_bind upload"))
         return false;
     return q4i_check(cudaStreamSynchronize(g_q4.stream), "batch_bind sync");
 }
