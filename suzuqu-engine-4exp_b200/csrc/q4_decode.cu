@@ -882,8 +882,21 @@ q4_decode_k(const DecParams P) {
         Q4_STAMP(13);
         issue(1, pb);
         Q4_STAMP(10);
-        pa = pc; pb = pd;      /* next iteration's stages */
-        pc = pe; pd = pf;      /* the ones after: list entries are fetched two iterations ahead */
+        /* A warp with at most four tiles (the single-session decode, small batches) fills the whole ring
+         * before the queries are prepared: its list is then entirely in flight after one round of list
+         * loads.  With more tiles per warp that doubles the burst at the start of the kernel and costs
+         * more than it saves (measured at 64 sessions), so there the second pair waits for the loop. */
+        uint32_t next = 2;                   /* next tile to issue */
+        if (n_even <= 4) {
+            issue(2, pc);
+            issue(3, pd);
+            next = 4;
+            pa = pe; pb = pf;
+            pc = my_pos(6); pd = my_pos(7);
+        } else {
+            pa = pc; pb = pd;                /* the stages the first iteration issues */
+            pc = pe; pd = pf;                /* the ones after: list entries are fetched two iterations ahead */
+        }
 
         /* Q fragments with scale * log2(e) folded in, rounded to fp16 once; and, per 32-wide block,
          * -1152 * sum(q): K codes enter the MMA as the fp16 numbers 1152 + code (one byte permute per
@@ -933,11 +946,14 @@ q4_decode_k(const DecParams P) {
 
         Q4_STAMP_DEP(11, qs[0][0][0]);
         for (uint32_t it = 0; it < n_even; it += 2) {
-            issue(it + 2, pa);
-            issue(it + 3, pb);
-            pa = pc; pb = pd;
-            pc = my_pos(it + 6);                 /* consumed by the issue two iterations from now */
-            pd = my_pos(it + 7);
+            if (next == it + 2) {                    /* refill the two stages the previous iteration consumed */
+                issue(next, pa);
+                issue(next + 1, pb);
+                next += 2;
+                pa = pc; pb = pd;
+                pc = my_pos(next + 2);               /* consumed by the issue two iterations from now */
+                pd = my_pos(next + 3);
+            }
             cp_async_wait<2>();                  /* all but the two newest stages have landed */
             __syncwarp();
 #ifdef Q4_DEC_TIMING
