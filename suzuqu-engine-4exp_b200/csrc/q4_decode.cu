@@ -48,6 +48,7 @@ constexpr int DEC_WARPS = 4;
 constexpr int DEC_THREADS = DEC_WARPS * 32;
 constexpr uint32_t DEC_MAX_SPLIT = 256;
 constexpr uint32_t DEC_GROUP = 16;   /* records merged per level of the two-level merge */
+constexpr uint32_t DEC_CLUSTER_MAX = 16;   /* most splits of a unit that merge through one cluster (8 is the portable size) */
 
 struct DecParams {
     Q4Cache one;
@@ -304,7 +305,7 @@ __device__ __forceinline__ float ld_cluster(uint32_t a) {
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(a) : "memory");
     return v;
 }
-/* When the splits of a unit are the blocks of one cluster (at most 8), every block leaves its record
+/* When the splits of a unit are the blocks of one cluster (at most 16), every block leaves its record
  * in its own shared memory and block r merges heads r, r+S, .. by reading all S records through
  * distributed shared memory: no scratch, no atomics, no global round trips.  Called between two
  * cluster barriers (records complete before, nobody exits while peers still read after).  (Clusters of 8
@@ -314,10 +315,10 @@ template <int HD, int HEADS>
 __device__ __noinline__ void cluster_merge(uint32_t rec_saddr, uint32_t S, uint32_t rank, const MergeOut mo) {
     constexpr int REC = HD + 4;
     for (uint32_t h = rank; h < mo.gqa; h += S) {
-        float m[8], l[8];
+        float m[DEC_CLUSTER_MAX], l[DEC_CLUSTER_MAX];
         float M = -CUDART_INF_F;
 #pragma unroll
-        for (uint32_t s = 0; s < 8; s++) {
+        for (uint32_t s = 0; s < DEC_CLUSTER_MAX; s++) {
             m[s] = -CUDART_INF_F;
             l[s] = 0.f;
             if (s < S) {
@@ -330,18 +331,18 @@ __device__ __noinline__ void cluster_merge(uint32_t rec_saddr, uint32_t S, uint3
         const float Mu = M == -CUDART_INF_F ? 0.f : M;
         float L = 0.f;
 #pragma unroll
-        for (uint32_t s = 0; s < 8; s++) {
+        for (uint32_t s = 0; s < DEC_CLUSTER_MAX; s++) {
             m[s] = ex2(m[s] - Mu);
             L = fmaf(m[s], l[s], L);
         }
         for (uint32_t d = threadIdx.x; d < (uint32_t)HD; d += DEC_THREADS) {
-            float a[8];
+            float a[DEC_CLUSTER_MAX];
 #pragma unroll
-            for (uint32_t s = 0; s < 8; s++)
+            for (uint32_t s = 0; s < DEC_CLUSTER_MAX; s++)
                 a[s] = s < S ? ld_cluster(map_to_rank(rec_saddr + (h * REC + d) * 4, s)) : 0.f;
             float A = 0.f;
 #pragma unroll
-            for (uint32_t s = 0; s < 8; s++) A = fmaf(m[s], a[s], A);
+            for (uint32_t s = 0; s < DEC_CLUSTER_MAX; s++) A = fmaf(m[s], a[s], A);
             if (mo.part_out) {
                 float *pr = mo.part_out + (mo.row0 + h) * (HD + 2);
                 if (d == 0) {
@@ -1324,6 +1325,15 @@ bool launch(const DecParams &p, dim3 grid) {
     cfg.stream = g_q4.stream;
     cudaLaunchAttribute at[2];
     unsigned n_at = 0;
+    if (p.cluster > 8) {
+        static bool big_ok = false;   /* clusters above the portable size need the kernel's consent */
+        if (!big_ok) {
+            if (!q4i_check(cudaFuncSetAttribute(q4_decode_k<LAY, HD, NHT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1),
+                           "decode cluster-size attribute"))
+                return false;
+            big_ok = true;
+        }
+    }
     if (p.cluster) {
         at[n_at].id = cudaLaunchAttributeClusterDimension;
         at[n_at].val.clusterDim.x = p.cluster;
@@ -1394,7 +1404,8 @@ bool q4i_decode(const Q4DecodeArgs &a) {
     if (S > DEC_GROUP && S < 2 * DEC_GROUP) S = DEC_GROUP;   /* one merge level instead of two */
     if (S < 1) S = 1;
     /* Short lists (a few hundred tiles per unit) are bound by the latency of the merge, not by bandwidth:
-     * at most 8 splits, launched as one cluster per unit, merge through distributed shared memory. */
+     * at most 8 splits (16 when only a few units are in flight), launched as one cluster per unit, merge
+     * through distributed shared memory. */
     static int use_cluster = -1;
     if (use_cluster < 0) {
         const char *e = getenv("Q4_DEC_CLUSTER");
@@ -1403,7 +1414,11 @@ bool q4i_decode(const Q4DecodeArgs &a) {
     uint32_t cluster = 0;   /* blocks per cluster; 0 = plain launch with the merge in global memory */
     if (a.xchg) Q4_REQUIRE(a.n_units == 1 && a.out && !a.part_out && !a.many, "decode: exchange mode is for one token of one session");
     if (use_cluster && !a.scratch_part && !a.xchg && (S <= 8 || steps <= 512)) {
-        if (S > 8) S = 8;
+        /* a few units only (single session, small batch): clusters of 16 halve each warp's share again;
+         * every warp keeps at least two tiles */
+        const uint32_t cmax = (units * DEC_CLUSTER_MAX <= (uint32_t)g_q4.sm_count * 2u && steps >= 8u * DEC_CLUSTER_MAX)
+                                  ? DEC_CLUSTER_MAX : 8u;
+        if (S > cmax) S = cmax;
         cluster = S > 1 ? S : 0u;
     }
 
