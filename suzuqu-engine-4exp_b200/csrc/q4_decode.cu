@@ -219,6 +219,40 @@ __device__ __noinline__ void merge_records(const float *recs, uint32_t count, bo
     constexpr int REC = HD + 4;
     __shared__ float s_w[DEC_GROUP * 16], s_l[DEC_GROUP * 16], s_M[16], s_L[16];
     const uint32_t gqa = mo.gqa;
+    if (!global && count == DEC_WARPS && dst_rec) {
+        /* The block's own four warp records, in shared memory: every thread recomputes the four weights
+         * of its head (no shared weights, no barriers in between) and writes its 4 dims of the block
+         * record.  This runs once in every block of every launch. */
+        for (uint32_t i = threadIdx.x; i < gqa * (HD / 4); i += DEC_THREADS) {
+            const uint32_t h = i / (HD / 4), d = (i % (HD / 4)) * 4;
+            float2 ml[DEC_WARPS];
+            float4 x[DEC_WARPS];
+#pragma unroll
+            for (int k = 0; k < DEC_WARPS; k++) {
+                const float *r = recs + ((size_t)k * HEADS + h) * REC;
+                ml[k] = *reinterpret_cast<const float2 *>(r + HD);
+                x[k] = *reinterpret_cast<const float4 *>(r + d);
+            }
+            float M = -CUDART_INF_F;
+#pragma unroll
+            for (int k = 0; k < DEC_WARPS; k++) M = fmaxf(M, ml[k].x);
+            const float Mu = M == -CUDART_INF_F ? 0.f : M;
+            float L = 0.f;
+            float4 A = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int k = 0; k < DEC_WARPS; k++) {
+                const float w = ex2(ml[k].x - Mu);
+                L = fmaf(w, ml[k].y, L);
+                A.x = fmaf(w, x[k].x, A.x); A.y = fmaf(w, x[k].y, A.y);
+                A.z = fmaf(w, x[k].z, A.z); A.w = fmaf(w, x[k].w, A.w);
+            }
+            float *o = dst_rec + (size_t)h * REC;
+            *reinterpret_cast<float4 *>(o + d) = A;
+            if (d == 0) { o[HD] = M; o[HD + 1] = L; }
+        }
+        __syncthreads();
+        return;
+    }
     for (uint32_t i = threadIdx.x; i < count * HEADS; i += DEC_THREADS) {
         const float2 *r = reinterpret_cast<const float2 *>(recs + (size_t)i * REC + HD);
         const float2 ml = global ? __ldcg(r) : *r;   /* one round trip for every m and l */
