@@ -73,6 +73,7 @@ struct DecParams {
     uint32_t xchg_phase;
     const float *new_k, *new_v;   /* fused append of the newest row (native q8_0 store), or null */
     uint32_t pdl;                 /* launched with programmatic stream serialization */
+    uint32_t push_bytes;          /* > 0: the launch carries this much extra shared memory and merges by pushing */
 };
 
 /* ---- small device helpers ---------------------------------------------------------------- */
@@ -377,6 +378,69 @@ __device__ __noinline__ void cluster_merge(uint32_t rec_saddr, uint32_t S, uint3
             float A = 0.f;
 #pragma unroll
             for (uint32_t s = 0; s < DEC_CLUSTER_MAX; s++) A = fmaf(m[s], a[s], A);
+            if (mo.part_out) {
+                float *pr = mo.part_out + (mo.row0 + h) * (HD + 2);
+                if (d == 0) {
+                    pr[0] = L > 0.f ? M * 0.6931471805599453f : 0.f;
+                    pr[1] = L;
+                }
+                pr[2 + d] = A;
+            } else {
+                float o = L > 0.f ? A / L : 0.f;
+                const size_t off = (mo.row0 + h) * HD + d;
+                if (mo.gate) o *= 1.f / (1.f + __expf(-mo.gate[off]));
+                mo.out[off] = o;
+            }
+        }
+    }
+}
+
+/* Push form of the cluster merge, for launches that carry extra shared memory for it (a few units in
+ * flight, clusters of more than 8 blocks): every block stores head h of its record into the receive
+ * area of block h % S (slot (h / S) * S + own rank) through distributed shared memory, one cluster
+ * barrier makes the stores visible, and every block merges the heads it owns from its OWN shared
+ * memory.  Nobody reads a peer's memory after the barrier, so the second barrier of the pull form (and
+ * the ~1 us it adds to a 9 us kernel) is not needed; the receive area lies behind the ring, so a fast
+ * peer may push while this block is still in its position loop. */
+template <int HD, int HEADS>
+__device__ __noinline__ void cluster_push_merge(const float *own, const float *recv, uint32_t S, uint32_t rank,
+                                                const MergeOut mo) {
+    constexpr int REC = HD + 4;
+    const uint32_t recv_saddr = (uint32_t)__cvta_generic_to_shared(recv);
+    for (uint32_t i = threadIdx.x; i < mo.gqa * (REC / 4); i += DEC_THREADS) {
+        const uint32_t h = i / (REC / 4), c = i % (REC / 4);
+        const float4 v = *reinterpret_cast<const float4 *>(own + (size_t)h * REC + 4 * c);
+        const uint32_t dst = map_to_rank(recv_saddr + ((((h / S) * S + rank) * REC) + 4 * c) * 4, h % S);
+        asm volatile("st.shared::cluster.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+    }
+    cluster_sync_all();
+    for (uint32_t h = rank, j = 0; h < mo.gqa; h += S, j++) {
+        const float *base = recv + (size_t)j * S * REC;
+        float m[DEC_CLUSTER_MAX], l[DEC_CLUSTER_MAX];
+        float M = -CUDART_INF_F;
+#pragma unroll
+        for (uint32_t s = 0; s < DEC_CLUSTER_MAX; s++) {
+            m[s] = -CUDART_INF_F;
+            l[s] = 0.f;
+            if (s < S) {
+                const float2 ml = *reinterpret_cast<const float2 *>(base + (size_t)s * REC + HD);
+                m[s] = ml.x;
+                l[s] = ml.y;
+            }
+            M = fmaxf(M, m[s]);
+        }
+        const float Mu = M == -CUDART_INF_F ? 0.f : M;
+        float L = 0.f;
+#pragma unroll
+        for (uint32_t s = 0; s < DEC_CLUSTER_MAX; s++) {
+            m[s] = ex2(m[s] - Mu);
+            L = fmaf(m[s], l[s], L);
+        }
+        for (uint32_t d = threadIdx.x; d < (uint32_t)HD; d += DEC_THREADS) {
+            float A = 0.f;
+#pragma unroll
+            for (uint32_t s = 0; s < DEC_CLUSTER_MAX; s++)
+                if (s < S) A = fmaf(m[s], base[(size_t)s * REC + d], A);
             if (mo.part_out) {
                 float *pr = mo.part_out + (mo.row0 + h) * (HD + 2);
                 if (d == 0) {
@@ -1263,6 +1327,11 @@ q4_decode_k(const DecParams P) {
         float *own = reinterpret_cast<float *>(smem_raw + Cfg::EPI_BYTES);
         merge_records<HD, HEADS>(sm, DEC_WARPS, false, own, mo);
         Q4_STAMP(3);
+        if (P.push_bytes) {
+            cluster_push_merge<HD, HEADS>(own, reinterpret_cast<const float *>(smem_raw + Cfg::SMEM), S, cluster_ctarank(), mo);
+            Q4_STAMP(6);
+            return;
+        }
         cluster_sync_all();
         Q4_STAMP(4);
         cluster_merge<HD, HEADS>((uint32_t)__cvta_generic_to_shared(own), S, cluster_ctarank(), mo);
@@ -1342,15 +1411,18 @@ __global__ void q4_lse_merge_k(const float *parts, uint32_t n_parts, uint32_t n_
 
 template <int LAY, int HD, int NHT>
 bool launch(const DecParams &p, dim3 grid) {
-    constexpr size_t smem = DecCfg<LAY, HD, NHT>::SMEM;
+    constexpr size_t smem_base = DecCfg<LAY, HD, NHT>::SMEM;
+    /* room for the receive area of the push merge: at most 2 heads x 16 records per block */
+    constexpr size_t smem_max = smem_base + 2u * DEC_CLUSTER_MAX * (HD + 4) * sizeof(float);
     static bool attr_done = false;
-    if (!attr_done && smem > 48 * 1024) {
+    if (!attr_done && smem_max > 48 * 1024) {
         if (!q4i_check(cudaFuncSetAttribute(q4_decode_k<LAY, HD, NHT>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max),
                        "decode smem attribute"))
             return false;
     }
     attr_done = true;
+    const size_t smem = smem_base + p.push_bytes;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = grid;
@@ -1496,6 +1568,10 @@ bool q4i_decode(const Q4DecodeArgs &a) {
     p.scale_log2e = a.scale * 1.4426950408889634f;
     p.S = S;
     p.cluster = cluster;
+    /* the push merge needs extra shared memory: only where every block has an SM to itself, so that it
+     * costs no occupancy (at 8 sessions x 16 blocks it pushed the clusters into a second wave) */
+    p.push_bytes = (cluster > 8 && units * cluster <= (uint32_t)g_q4.sm_count)
+                       ? ((gqa + cluster - 1u) / cluster) * cluster * (a.hd + 4u) * (uint32_t)sizeof(float) : 0u;
     p.debug = 0;
 #ifdef Q4_DEC_TIMING
     {
