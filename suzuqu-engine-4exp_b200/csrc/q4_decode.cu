@@ -48,6 +48,7 @@ constexpr int DEC_WARPS = 4;
 constexpr int DEC_THREADS = DEC_WARPS * 32;
 constexpr uint32_t DEC_MAX_SPLIT = 256;
 constexpr uint32_t DEC_GROUP = 16;   /* records merged per level of the two-level merge */
+constexpr uint32_t MERGE_SCRATCH_FLOATS = 2 * DEC_GROUP * 16 + 32;   /* weights, sums, per-head max and total */
 constexpr uint32_t DEC_CLUSTER_MAX = 16;   /* most splits of a unit that merge through one cluster (8 is the portable size) */
 
 struct DecParams {
@@ -216,9 +217,9 @@ __device__ __noinline__ bool arrive_last(uint32_t *ctr, uint32_t expected) {
  * instruction once. */
 template <int HD, int HEADS>
 __device__ __noinline__ void merge_records(const float *recs, uint32_t count, bool global, float *dst_rec,
-                                           const MergeOut mo) {
+                                           const MergeOut mo, float *scratch /* MERGE_SCRATCH_FLOATS of shared memory */) {
     constexpr int REC = HD + 4;
-    __shared__ float s_w[DEC_GROUP * 16], s_l[DEC_GROUP * 16], s_M[16], s_L[16];
+    float *s_w = scratch, *s_l = scratch + DEC_GROUP * 16, *s_M = scratch + 2 * DEC_GROUP * 16, *s_L = s_M + 16;
     const uint32_t gqa = mo.gqa;
     if (!global && count == DEC_WARPS && dst_rec) {
         /* The block's own four warp records, in shared memory: every thread recomputes the four weights
@@ -636,7 +637,8 @@ struct DecCfg {
     static constexpr size_t EPI_BYTES = (size_t)DEC_WARPS * HEADS * REC * sizeof(float);
     static constexpr size_t RING_BYTES = STAGED ? (size_t)DEC_WARPS * RING_STAGES * RING_STAGE_BYTES : 0;
     static constexpr size_t REC_BYTES = (size_t)HEADS * REC * sizeof(float);   /* the block's merged record */
-    static constexpr size_t SMEM = EPI_BYTES + REC_BYTES > RING_BYTES ? EPI_BYTES + REC_BYTES : RING_BYTES;
+    static constexpr size_t TAIL_BYTES = EPI_BYTES + REC_BYTES + MERGE_SCRATCH_FLOATS * sizeof(float);   /* after the loop */
+    static constexpr size_t SMEM = TAIL_BYTES > RING_BYTES ? TAIL_BYTES : RING_BYTES;
     static constexpr int MIN_BLOCKS = STAGED ? (NHT == 1 ? 3 : 2) : (HD * NHT <= 128 ? 3 : 1);
 };
 
@@ -1316,16 +1318,17 @@ q4_decode_k(const DecParams P) {
     mo.out = P.out; mo.part_out = P.part_out; mo.gate = P.gate;
     mo.row0 = (size_t)u * P.n_head + (size_t)kh * P.gqa;
     mo.gqa = P.gqa;
+    float *mscr = reinterpret_cast<float *>(smem_raw + Cfg::EPI_BYTES + Cfg::REC_BYTES);   /* scratch of the merges */
     /* exchange mode: the unit's last merge leaves this rank's record here instead of finalising */
     float *fin = P.xchg ? reinterpret_cast<float *>(smem_raw + Cfg::EPI_BYTES) : nullptr;
     if (S == 1) {
-        merge_records<HD, HEADS>(sm, DEC_WARPS, false, fin, mo);
+        merge_records<HD, HEADS>(sm, DEC_WARPS, false, fin, mo, mscr);
         if (fin) xchg_finish<HD, HEADS>(P.xchg, P.xchg_phase, (uint32_t)unit, fin, mo, P.err);
         return;
     }
     if (P.cluster) {
         float *own = reinterpret_cast<float *>(smem_raw + Cfg::EPI_BYTES);
-        merge_records<HD, HEADS>(sm, DEC_WARPS, false, own, mo);
+        merge_records<HD, HEADS>(sm, DEC_WARPS, false, own, mo, mscr);
         Q4_STAMP(3);
         if (P.push_bytes) {
             cluster_push_merge<HD, HEADS>(own, reinterpret_cast<const float *>(smem_raw + Cfg::SMEM), S, cluster_ctarank(), mo);
@@ -1357,7 +1360,7 @@ q4_decode_k(const DecParams P) {
     uint32_t expected = grp_size;
     bool last = false;
     for (int level = 0;; level++) {
-        merge_records<HD, HEADS>(src, count, global, dst, mo);
+        merge_records<HD, HEADS>(src, count, global, dst, mo, mscr);
         Q4_STAMP(3 + level);
         if (last) {                                        /* finalised, or this rank's record is complete */
             if (fin) xchg_finish<HD, HEADS>(P.xchg, P.xchg_phase, (uint32_t)unit, fin, mo, P.err);
@@ -1410,7 +1413,7 @@ __global__ void q4_lse_merge_k(const float *parts, uint32_t n_parts, uint32_t n_
 }
 
 template <int LAY, int HD, int NHT>
-bool launch(const DecParams &p, dim3 grid) {
+bool launch(const DecParams &p_in, dim3 grid) {
     constexpr size_t smem_base = DecCfg<LAY, HD, NHT>::SMEM;
     /* room for the receive area of the push merge: at most 2 heads x 16 records per block */
     constexpr size_t smem_max = smem_base + 2u * DEC_CLUSTER_MAX * (HD + 4) * sizeof(float);
@@ -1422,6 +1425,39 @@ bool launch(const DecParams &p, dim3 grid) {
             return false;
     }
     attr_done = true;
+    /* The push merge needs extra shared memory; it is used only if that leaves the grid in one wave
+     * (at 8 sessions x 16 blocks the extra 8 KB pushed the clusters into a second wave). */
+    DecParams p = p_in;
+    if (p.push_bytes) {
+        static uint32_t cached_bytes = 0, cached_cluster = 0;
+        static int cached_clusters = 0;
+        if (cached_bytes != p.push_bytes || cached_cluster != p.cluster) {
+            if (p.cluster > 8)
+                (void)cudaFuncSetAttribute(q4_decode_k<LAY, HD, NHT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            cudaLaunchConfig_t qc;
+            memset(&qc, 0, sizeof(qc));
+            qc.gridDim = grid;
+            qc.blockDim = dim3(DEC_THREADS);
+            qc.dynamicSmemBytes = smem_base + p.push_bytes;
+            cudaLaunchAttribute qa[1];
+            qa[0].id = cudaLaunchAttributeClusterDimension;
+            qa[0].val.clusterDim.x = p.cluster;
+            qa[0].val.clusterDim.y = 1;
+            qa[0].val.clusterDim.z = 1;
+            qc.attrs = qa;
+            qc.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, q4_decode_k<LAY, HD, NHT>, &qc) != cudaSuccess) {
+                (void)cudaGetLastError();
+                n = 0;
+            }
+            cached_bytes = p.push_bytes;
+            cached_cluster = p.cluster;
+            cached_clusters = n;
+        }
+        const uint64_t clusters = (uint64_t)grid.x * grid.y * grid.z / p.cluster;
+        if (clusters > (uint64_t)cached_clusters) p.push_bytes = 0;
+    }
     const size_t smem = smem_base + p.push_bytes;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
@@ -1568,10 +1604,8 @@ bool q4i_decode(const Q4DecodeArgs &a) {
     p.scale_log2e = a.scale * 1.4426950408889634f;
     p.S = S;
     p.cluster = cluster;
-    /* the push merge needs extra shared memory: only where every block has an SM to itself, so that it
-     * costs no occupancy (at 8 sessions x 16 blocks it pushed the clusters into a second wave) */
-    p.push_bytes = (cluster > 8 && units * cluster <= (uint32_t)g_q4.sm_count)
-                       ? ((gqa + cluster - 1u) / cluster) * cluster * (a.hd + 4u) * (uint32_t)sizeof(float) : 0u;
+    /* the push merge needs extra shared memory; the launcher drops it where that would cost a wave */
+    p.push_bytes = cluster > 1 ? ((gqa + cluster - 1u) / cluster) * cluster * (a.hd + 4u) * (uint32_t)sizeof(float) : 0u;
     p.debug = 0;
 #ifdef Q4_DEC_TIMING
     {
