@@ -698,31 +698,25 @@ q4_decode_k(const DecParams P) {
     const uint32_t tok_stride = C.tok_stride, s_tok_stride = C.s_tok_stride;
     const uint32_t max_kv = C.max_kv;
 
-    /* ---- fused append: the newest row of this (session, kv head) is quantised and stored here, by
-     * every split of the unit (identical bytes), before any row is read: a block's own stores are ordered
-     * before its later reads by the barrier, so no split depends on another block having written.  8
-     * lanes per 32-value block, the first hd/4 threads take the K row and the next hd/4 the V row. */
+    /* ---- fused append, first half: the load of the unit's new K/V row is issued here, next to the
+     * loads of the list entries below, so that the two round trips overlap; the row is quantised and
+     * stored just before the first cache row is read.  8 lanes per 32-value block, the first hd/4
+     * threads take the K row and the next hd/4 the V row. */
+    float4 ap_x = make_float4(0.f, 0.f, 0.f, 0.f);
+    bool ap_which = false, ap_live = false;
+    uint32_t ap_b = 0, ap_sub = 0;
     if constexpr (Cfg::STAGED) {   /* rows are read with cp.async (coherent at L2), never through the read-only path */
         if (P.new_k) {
             constexpr uint32_t QL = HD / 4;
             const uint32_t tid = threadIdx.x;
-            const bool which = tid >= QL, live = tid < 2 * QL && newest < max_kv;
-            const uint32_t w = which ? tid - QL : tid, b = w >> 3, sub = w & 7u;
-            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (live)
-                x = *reinterpret_cast<const float4 *>((which ? P.new_v : P.new_k) +
-                                                      ((size_t)u * P.n_kvh + kh) * HD + b * 32 + sub * 4);
-            float d, id;
-            q4d_block_scale(x, d, id);
-            if (live) {
-                uint8_t *row = const_cast<uint8_t *>(which ? vbase : kbase) + (uint64_t)newest * tok_stride;
-                *reinterpret_cast<uint32_t *>(row + b * 32 + sub * 4) = q4d_quant4(x, id);
-                if (sub == 0)
-                    reinterpret_cast<__half *>(const_cast<uint8_t *>(sbase) + (uint64_t)newest * s_tok_stride)[(which ? NB : 0) + b] =
-                        __float2half_rn(d);
-            }
-            if (newest >= max_kv && tid == 0) atomicOr(P.err, (uint32_t)Q4E_RANGE);
-            __syncthreads();
+            ap_which = tid >= QL;
+            ap_live = tid < 2 * QL && newest < max_kv;
+            const uint32_t w = ap_which ? tid - QL : tid;
+            ap_b = w >> 3;
+            ap_sub = w & 7u;
+            if (ap_live)
+                ap_x = *reinterpret_cast<const float4 *>((ap_which ? P.new_v : P.new_k) +
+                                                         ((size_t)u * P.n_kvh + kh) * HD + ap_b * 32 + ap_sub * 4);
         }
     }
 
@@ -976,6 +970,22 @@ q4_decode_k(const DecParams P) {
             cp_async_commit();   /* one group per stage, empty or not, keeps the wait count uniform */
         };
         int32_t pa = my_pos(0), pb = my_pos(1), pc = my_pos(2), pd = my_pos(3), pe = my_pos(4), pf = my_pos(5);
+        /* ---- fused append, second half: every split of the unit quantises and stores the unit's newest
+         * row (identical bytes), before any row is read: a block's own stores are ordered before its later
+         * reads by the barrier, so no split depends on another block having written. */
+        if (P.new_k) {
+            float d, id;
+            q4d_block_scale(ap_x, d, id);
+            if (ap_live) {
+                uint8_t *row = const_cast<uint8_t *>(ap_which ? vbase : kbase) + (uint64_t)newest * tok_stride;
+                *reinterpret_cast<uint32_t *>(row + ap_b * 32 + ap_sub * 4) = q4d_quant4(ap_x, id);
+                if (ap_sub == 0)
+                    reinterpret_cast<__half *>(const_cast<uint8_t *>(sbase) + (uint64_t)newest * s_tok_stride)[(ap_which ? NB : 0) + ap_b] =
+                        __float2half_rn(d);
+            }
+            if (newest >= max_kv && threadIdx.x == 0) atomicOr(P.err, (uint32_t)Q4E_RANGE);
+            __syncthreads();
+        }
         Q4_STAMP_DEP(8, max_kv);
         Q4_STAMP_DEP(9, pa | pb);
         Q4_STAMP(12);
