@@ -587,6 +587,90 @@ def extras_dense(torch, q4gpu, L, ext, peak_gbs, kinds=("q8_0", "f16", "f32")):
     return res
 
 
+def extras_snapshot(torch, q4gpu, L, ext):
+    """session prefix save / restore at configs[3]'s mean context (66048 rows x 12 layers, q8_0): bulk strided
+    copies to a device pool and to pinned host memory, and the reference session-file byte order streamed
+    through a file descriptor (an in-memory file, so the figure is the library's, not a disk's)"""
+    n_kv, max_kv = 66048, 131072
+    st = q4gpu.KVStore(N_LAYERS, N_KVH, HD, max_kv, q4gpu.KIND_Q8)
+    q4gpu.use_torch_stream()
+    fill_store(torch, st, n_kv)
+    torch.cuda.synchronize()
+    L.q4_gpu_set_stream(None)
+    by = st.snapshot_bytes(n_kv)
+    pool = torch.empty(4, by, dtype=torch.uint8, device="cuda")     # 4 slots > L2 between two uses of one
+    host = torch.empty(by, dtype=torch.uint8).pin_memory()
+    res = {"workload": "one session, %d rows x %d layers q8_0 (K and V)" % (n_kv, N_LAYERS), "bytes": by}
+    for name, fn, reps, moved in (
+            ("save_device", lambda i: st.save(n_kv, pool[i % 4]), 8, 2 * by),
+            ("restore_device", lambda i: st.restore(n_kv, pool[i % 4]), 8, 2 * by),
+            ("save_pinned_host", lambda i: st.save(n_kv, host, host=True), 3, by),
+            ("restore_pinned_host", lambda i: st.restore(n_kv, host, host=True), 3, by)):
+        timed(torch, ext, fn, 2)
+        dt = timed(torch, ext, fn, reps) / reps
+        res[name] = {"ms": dt * 1e3, "gbs": moved / dt / 1e9}
+    fd = os.memfd_create("q4_session_kv")
+    try:
+        st.write_fd(n_kv, fd)                                        # warm-up: staging buffers, page faults
+        os.lseek(fd, 0, os.SEEK_SET)
+        t0 = time.perf_counter()
+        st.write_fd(n_kv, fd)
+        t1 = time.perf_counter()
+        file_bytes = os.lseek(fd, 0, os.SEEK_CUR)
+        os.lseek(fd, 0, os.SEEK_SET)
+        st.read_fd(n_kv, fd)
+        os.lseek(fd, 0, os.SEEK_SET)
+        t2 = time.perf_counter()
+        st.read_fd(n_kv, fd)
+        t3 = time.perf_counter()
+    finally:
+        os.close(fd)
+    res["write_fd"] = {"ms": (t1 - t0) * 1e3, "gbs": file_bytes / (t1 - t0) / 1e9, "file_bytes": file_bytes}
+    res["read_fd"] = {"ms": (t3 - t2) * 1e3, "gbs": file_bytes / (t3 - t2) / 1e9}
+    st.close()
+    return res
+
+
+def extras_sparse_prefill(torch, q4gpu, L, ext, peak_gbs):
+    """sparse prefill (the n_tok > 1 indexed form): 512 queries at the end of a 262144-row context, each
+    with its own 2051-entry list per kv head (4 sink + 1024 recent + 1023 spread over the rest, one random
+    row per stratum), one launch per layer on the q8_0 store"""
+    ctx, n_tok = 262144, 512
+    st = q4gpu.KVStore(N_LAYERS, N_KVH, HD, ctx, q4gpu.KIND_Q8)
+    q4gpu.use_torch_stream()
+    fill_store(torch, st, ctx)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(SEED + 9)
+    pos = torch.arange(ctx - n_tok, ctx, device="cuda").view(n_tok, 1, 1)             # the query's own row
+    sink = torch.arange(4, device="cuda").view(1, 1, 4).expand(n_tok, N_KVH, 4)
+    recent = pos - 1023 + torch.arange(1024, device="cuda").view(1, 1, 1024)
+    span = (pos - 1023 - 4).to(torch.float64)                                          # rows [4, pos - 1023)
+    u = torch.rand(n_tok, N_KVH, 1023, device="cuda", dtype=torch.float64, generator=gen)
+    spread = 4 + ((torch.arange(1023, device="cuda").view(1, 1, 1023) + u) * span / 1023).long()
+    idx = torch.cat([sink, spread, recent.expand(n_tok, N_KVH, 1024)], 2).to(torch.int32).contiguous()
+    assert idx.shape[2] == WIDTH and int(idx.max()) < ctx and int(idx.min()) >= 0
+    q = torch.randn(N_LAYERS, n_tok, N_HEAD, HD, device="cuda").to(torch.bfloat16)
+    out = torch.empty(N_LAYERS, n_tok, N_HEAD, HD, device="cuda")
+    torch.cuda.synchronize()
+    L.q4_gpu_set_stream(None)
+
+    def one(i):
+        layer = i % N_LAYERS
+        st.decode_idx_n(layer, q[layer], out[layer], N_HEAD, SCALE, idx, WIDTH, n_tok,
+                        idx_tok_stride=N_KVH * WIDTH, idx_kvh_stride=WIDTH, q_bf16=True)
+    timed(torch, ext, one, N_LAYERS)
+    n = 2 * N_LAYERS
+    dt = timed(torch, ext, one, n) / n
+    gathered = n_tok * N_KVH * WIDTH * 272
+    distinct = int(torch.unique(idx[:, 0]).numel() + torch.unique(idx[:, 1]).numel()) * 272
+    st.close()
+    return {"workload": "512 queries x 2051 rows per kv head over ctx 262144, q8_0, one launch per layer",
+            "us_per_layer": dt * 1e6, "us_per_query": dt * 1e6 / n_tok, "gathered_bytes_per_layer": gathered,
+            "distinct_row_bytes_per_layer": distinct, "gathered_gbs": gathered / dt / 1e9,
+            "distinct_gbs": distinct / dt / 1e9, "distinct_frac_of_measured_hbm": distinct / dt / 1e9 / peak_gbs,
+            "note": "lists of neighbouring queries overlap, so most gathers hit L2; the HBM floor is the distinct rows"}
+
+
 def run_seqshard(args, torch, q4gpu, L, dist, rank, world, peak_gbs):
     """configs[4]: one session at ctx 262144, dense attention; rank r owns an even contiguous slice of the
     rows and attends them; the (acc, m, l) records are exchanged and merged on every rank, either inside the
@@ -697,7 +781,7 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--groups", type=int, default=0, help="replicas of the session group (0 = enough to defeat L2)")
     ap.add_argument("--ctx-max", type=int, default=131072, help="upper end of the context-length draw (profiling: small)")
-    ap.add_argument("--only", default="", choices=["", "single", "dense", "prefill", "indexer"],
+    ap.add_argument("--only", default="", choices=["", "single", "dense", "prefill", "indexer", "snapshot", "sparse_prefill"],
                     help="run just one of the ctx-262144 extras (for profiler captures)")
     ap.add_argument("--dense-kinds", default="q8_0,f16,f32")
     ap.add_argument("--mode", default="sessions", choices=["sessions", "seqshard"],
@@ -748,6 +832,10 @@ def main():
             res = extras_prefill(torch, q4gpu, L, ext, peaks)
         elif args.only == "indexer":
             res = extras_indexer(torch, q4gpu, L, ext, peak_gbs)
+        elif args.only == "snapshot":
+            res = extras_snapshot(torch, q4gpu, L, ext)
+        elif args.only == "sparse_prefill":
+            res = extras_sparse_prefill(torch, q4gpu, L, ext, peak_gbs)
         else:
             res = extras_dense(torch, q4gpu, L, ext, peak_gbs, args.dense_kinds.split(","))
         print(json.dumps({"only": args.only, "result": res}), flush=True)
@@ -868,6 +956,8 @@ def main():
         line["dense_ctx262144"] = extras_dense(torch, q4gpu, L, ext, peak_gbs)
         line["prefill_8192_over_16384"] = extras_prefill(torch, q4gpu, L, ext, peaks)
         line["indexer_ctx262144"] = extras_indexer(torch, q4gpu, L, ext, peak_gbs)
+        line["sparse_prefill_512_ctx262144"] = extras_sparse_prefill(torch, q4gpu, L, ext, peak_gbs)
+        line["session_snapshot"] = extras_snapshot(torch, q4gpu, L, ext)
         line["cpu_baseline"] = cpu_baseline(ctxs, args.cpu_seconds)
     print(json.dumps(line), flush=True)
     if dist is not None:

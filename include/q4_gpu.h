@@ -256,6 +256,16 @@ bool q4_gpu_kv_decode_noalloc(const q4_gpu_kv *kv, uint32_t layer, const void *q
                               const float *gate, float *out, uint32_t n_head, const int32_t *idx,
                               uint32_t width, uint32_t idx_kvh_stride, uint32_t n_kv, float scale);
 
+/* Sparse prefill on the store: n_tok queries q [n_tok][n_head][hd], each attending the rows its own list
+ * names, idx[t * idx_tok_stride + kv_head * idx_kvh_stride + j] (j < width, -1 = skip; idx_kvh_stride 0 =
+ * one list per token shared by the kv heads, the reference's form); out [n_tok][n_head][hd], gate
+ * likewise or NULL.  The n_tok > 1 case of q4_hip_qsa_decode_idx (src/q4.h:911-915; gqa_prefill_k<KIND,
+ * true>, src/q4_rocm.cu:7319,7342-7357) on the library-owned store, one launch. */
+bool q4_gpu_kv_decode_idx_n(const q4_gpu_kv *kv, uint32_t layer, const void *q, int q_bf16,
+                            const float *gate, float *out, uint32_t n_head, const int32_t *idx,
+                            uint32_t width, uint32_t idx_kvh_stride, uint32_t idx_tok_stride,
+                            uint32_t n_tok, float scale);
+
 /* Same, but stops before normalisation: part[n_head][hd+2] = {m, l, acc[hd]} over this store's
  * rows, the record of src/q4_rocm.cu:6780,6957-6963 -- the payload exchanged between GPUs when one
  * sequence is sharded by position. */

@@ -208,6 +208,36 @@ __device__ __noinline__ bool arrive_last(uint32_t *ctr, uint32_t expected) {
     return last;
 }
 
+/* what a merge does with 4 dims of one head: a record for the next level, the public record
+ * {m (natural-log units), l, acc[HD]}, or the final out = acc / l * sigmoid(gate) */
+template <int HD>
+__device__ __forceinline__ void merge_store(float *dst_rec, const MergeOut &mo, uint32_t h, uint32_t d, float M, float L,
+                                            float4 A) {
+    constexpr int REC = HD + 4;
+    if (dst_rec) {
+        float *o = dst_rec + (size_t)h * REC;
+        *reinterpret_cast<float4 *>(o + d) = A;
+        if (d == 0) { o[HD] = M; o[HD + 1] = L; }
+    } else if (mo.part_out) {
+        float *pr = mo.part_out + (mo.row0 + h) * (HD + 2);
+        if (d == 0) {
+            pr[0] = L > 0.f ? M * 0.6931471805599453f : 0.f;
+            pr[1] = L;
+        }
+        pr[2 + d] = A.x; pr[3 + d] = A.y; pr[4 + d] = A.z; pr[5 + d] = A.w;
+    } else {
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        float4 o = make_float4(A.x * inv, A.y * inv, A.z * inv, A.w * inv);
+        const size_t off = (mo.row0 + h) * HD + d;
+        if (mo.gate) {
+            const float4 gt = *reinterpret_cast<const float4 *>(mo.gate + off);
+            o.x *= 1.f / (1.f + __expf(-gt.x)); o.y *= 1.f / (1.f + __expf(-gt.y));
+            o.z *= 1.f / (1.f + __expf(-gt.z)); o.w *= 1.f / (1.f + __expf(-gt.w));
+        }
+        *reinterpret_cast<float4 *>(mo.out + off) = o;
+    }
+}
+
 /* Merge `count` (<= DEC_GROUP) records spaced HEADS*REC floats apart (log2-domain max).  Weights are
  * computed once per (record, head); then every thread owns 4 output dims of some heads and streams
  * the accumulators with 8 independent 16-byte loads in flight.  dst_rec != null stores a merged
@@ -255,6 +285,40 @@ __device__ __noinline__ void merge_records(const float *recs, uint32_t count, bo
         __syncthreads();
         return;
     }
+    if (global) {
+        /* Records of other blocks, in global memory (L2): one batch of independent loads per output item
+         * -- all (m, l) pairs and all accumulator slices -- and the weights recomputed per thread, so a
+         * merge level costs one memory round trip per item and no barrier.  Only the last block to arrive
+         * at a level runs this. */
+        for (uint32_t i = threadIdx.x; i < gqa * (HD / 4); i += DEC_THREADS) {
+            const uint32_t h = i / (HD / 4), d = (i % (HD / 4)) * 4;
+            float2 ml[DEC_GROUP];
+            float4 x[DEC_GROUP];
+#pragma unroll
+            for (uint32_t k = 0; k < DEC_GROUP; k++) {
+                const float *r = recs + ((size_t)min(k, count - 1u) * HEADS + h) * REC;
+                ml[k] = __ldcg(reinterpret_cast<const float2 *>(r + HD));
+                x[k] = __ldcg(reinterpret_cast<const float4 *>(r + d));
+            }
+            float M = -CUDART_INF_F;
+#pragma unroll
+            for (uint32_t k = 0; k < DEC_GROUP; k++)
+                if (k < count) M = fmaxf(M, ml[k].x);
+            const float Mu = M == -CUDART_INF_F ? 0.f : M;
+            float L = 0.f;
+            float4 A = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (uint32_t k = 0; k < DEC_GROUP; k++) {
+                const float w = k < count ? ex2(ml[k].x - Mu) : 0.f;
+                L = fmaf(w, ml[k].y, L);
+                A.x = fmaf(w, x[k].x, A.x); A.y = fmaf(w, x[k].y, A.y);
+                A.z = fmaf(w, x[k].z, A.z); A.w = fmaf(w, x[k].w, A.w);
+            }
+            merge_store<HD>(dst_rec, mo, h, d, M, L, A);
+        }
+        __syncthreads();
+        return;
+    }
     for (uint32_t i = threadIdx.x; i < count * HEADS; i += DEC_THREADS) {
         const float2 *r = reinterpret_cast<const float2 *>(recs + (size_t)i * REC + HD);
         const float2 ml = global ? __ldcg(r) : *r;   /* one round trip for every m and l */
@@ -295,29 +359,7 @@ __device__ __noinline__ void merge_records(const float *recs, uint32_t count, bo
                 A.z = fmaf(w, x[k].z, A.z); A.w = fmaf(w, x[k].w, A.w);
             }
         }
-        const float M = s_M[h], L = s_L[h];
-        if (dst_rec) {
-            float *o = dst_rec + (size_t)h * REC;
-            *reinterpret_cast<float4 *>(o + d) = A;
-            if (d == 0) { o[HD] = M; o[HD + 1] = L; }
-        } else if (mo.part_out) {
-            float *pr = mo.part_out + (mo.row0 + h) * (HD + 2);
-            if (d == 0) {
-                pr[0] = L > 0.f ? M * 0.6931471805599453f : 0.f;
-                pr[1] = L;
-            }
-            pr[2 + d] = A.x; pr[3 + d] = A.y; pr[4 + d] = A.z; pr[5 + d] = A.w;
-        } else {
-            const float inv = L > 0.f ? 1.f / L : 0.f;
-            float4 o = make_float4(A.x * inv, A.y * inv, A.z * inv, A.w * inv);
-            const size_t off = (mo.row0 + h) * HD + d;
-            if (mo.gate) {
-                const float4 gt = *reinterpret_cast<const float4 *>(mo.gate + off);
-                o.x *= 1.f / (1.f + __expf(-gt.x)); o.y *= 1.f / (1.f + __expf(-gt.y));
-                o.z *= 1.f / (1.f + __expf(-gt.z)); o.w *= 1.f / (1.f + __expf(-gt.w));
-            }
-            *reinterpret_cast<float4 *>(mo.out + off) = o;
-        }
+        merge_store<HD>(dst_rec, mo, h, d, s_M[h], s_L[h], A);
     }
     __syncthreads();   /* s_w is reused by the next level */
 }

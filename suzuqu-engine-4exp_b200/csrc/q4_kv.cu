@@ -396,6 +396,26 @@ extern "C" uint64_t q4_gpu_kv_snapshot_bytes(const q4_gpu_kv *kv, uint32_t n_kv)
     const uint64_t rows = (uint64_t)kv->n_layers * kv->n_kvh * n_kv;
     return rows * (kv->kind == Q4K_Q8 ? (uint64_t)kv->rec_bytes : 2ull * row_bytes(kv->hd, kv->kind));
 }
+/* Device-to-device prefix copy: `height` rows of `width16` 16-byte words, source and destination
+ * pitches in bytes.  A block moves 32 KB of one row, eight independent 16-byte loads per thread in
+ * flight before the first store, streaming cache hints both ways (nothing is re-read).  Measured at
+ * 431 MB: 2-D copy engine path 3.5 TB/s (read + write), this kernel below. */
+constexpr uint32_t SNAP_TILE_WORDS = 2048;
+static __global__ void __launch_bounds__(256) q4_snap_copy_k(uint8_t *dst, size_t dpitch, const uint8_t *src, size_t spitch,
+                                                      size_t width16, uint32_t tiles_per_row) {
+    const uint32_t row = blockIdx.x / tiles_per_row, tile = blockIdx.x % tiles_per_row;
+    const uint4 *s = reinterpret_cast<const uint4 *>(src + (size_t)row * spitch);
+    uint4 *d = reinterpret_cast<uint4 *>(dst + (size_t)row * dpitch);
+    const size_t base = (size_t)tile * SNAP_TILE_WORDS + threadIdx.x;
+    uint4 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+        if (base + i * 256 < width16) v[i] = __ldcs(s + base + i * 256);
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+        if (base + i * 256 < width16) __stcs(d + base + i * 256, v[i]);
+}
+
 static bool snapshot(const q4_gpu_kv *kv, uint32_t n_kv, void *buf, int host, bool save) {
     if (!g_q4.ok) return q4i_fail(Q4E_INIT, "kv snapshot: library not initialised");
     Q4_REQUIRE(kv && buf && n_kv && n_kv <= kv->max_kv, "kv snapshot: bad argument");
@@ -406,9 +426,18 @@ static bool snapshot(const q4_gpu_kv *kv, uint32_t n_kv, void *buf, int host, bo
     struct { uint8_t *plane; uint32_t row; } pl[2] = {{kv->k, rb}, {kv->v, rb}};
     for (int i = 0; i < (kv->kind == Q4K_Q8 ? 1 : 2); i++) {
         const size_t width = (size_t)n_kv * pl[i].row, pitch = (size_t)kv->max_kv * pl[i].row;
-        cudaError_t e = save ? cudaMemcpy2DAsync(b, width, pl[i].plane, pitch, width, height, kind, g_q4.stream)
-                             : cudaMemcpy2DAsync(pl[i].plane, pitch, b, width, width, height, kind, g_q4.stream);
-        if (!q4i_check(e, "kv snapshot copy")) return false;
+        if (!host && width % 16 == 0 && pitch % 16 == 0 && ((uintptr_t)b & 15u) == 0) {
+            const size_t width16 = width / 16;
+            const uint32_t tiles = (uint32_t)((width16 + SNAP_TILE_WORDS - 1) / SNAP_TILE_WORDS);
+            const uint32_t grid = tiles * (uint32_t)height;
+            if (save) q4_snap_copy_k<<<grid, 256, 0, g_q4.stream>>>(b, width, pl[i].plane, pitch, width16, tiles);
+            else q4_snap_copy_k<<<grid, 256, 0, g_q4.stream>>>(pl[i].plane, pitch, b, width, width16, tiles);
+            if (!q4i_check(cudaGetLastError(), "kv snapshot copy kernel")) return false;
+        } else {
+            cudaError_t e = save ? cudaMemcpy2DAsync(b, width, pl[i].plane, pitch, width, height, kind, g_q4.stream)
+                                 : cudaMemcpy2DAsync(pl[i].plane, pitch, b, width, width, height, kind, g_q4.stream);
+            if (!q4i_check(e, "kv snapshot copy")) return false;
+        }
         b += width * height;
     }
     return true;
@@ -462,6 +491,39 @@ extern "C" bool q4_gpu_kv_decode_partial(const q4_gpu_kv *kv, uint32_t layer, co
                                          uint32_t n_head, const int32_t *idx, uint32_t width,
                                          uint32_t idx_kvh_stride, uint32_t n_kv, float scale) {
     return store_decode(kv, layer, q, q_bf16, nullptr, nullptr, part, n_head, idx, width, idx_kvh_stride, n_kv, scale);
+}
+/* Sparse prefill on the store: the n_tok > 1 form of q4_hip_qsa_decode_idx (gqa_prefill_k<KIND, true>,
+ * src/q4_rocm.cu:7319,7342-7357).  Query t attends the rows its own list names; the work is a gather,
+ * not a contraction, so it runs as one launch of the decode kernel with a unit per (token, kv head). */
+extern "C" bool q4_gpu_kv_decode_idx_n(const q4_gpu_kv *kv, uint32_t layer, const void *q, int q_bf16,
+                                       const float *gate, float *out, uint32_t n_head, const int32_t *idx,
+                                       uint32_t width, uint32_t idx_kvh_stride, uint32_t idx_tok_stride,
+                                       uint32_t n_tok, float scale) {
+    if (!g_q4.ok) return q4i_fail(Q4E_INIT, "kv_decode_idx_n: library not initialised");
+    Q4_REQUIRE(kv && q && out && idx && width && n_tok && layer < kv->n_layers && n_head,
+               "kv_decode_idx_n: bad argument");
+    Q4_REQUIRE(idx_tok_stride >= width, "kv_decode_idx_n: lists of consecutive tokens overlap");
+    Q4DecodeArgs a;
+    memset(&a, 0, sizeof(a));
+    a.one = kv->view;
+    a.layout = store_layout(kv->kind);
+    a.layer = layer;
+    a.n_units = n_tok;
+    a.n_head = n_head;
+    a.n_kvh = kv->n_kvh;
+    a.hd = kv->hd;
+    a.q = q;
+    a.q_bf16 = q_bf16;
+    a.gate = gate;
+    a.out = out;
+    a.idx = idx;
+    a.width = width;
+    a.idx_kvh_stride = idx_kvh_stride;
+    a.idx_unit_stride = idx_tok_stride;
+    /* the lists alone bound the rows: entries >= max_kv are skipped and raise the range status bit */
+    a.hint_rows = width;
+    a.scale = scale;
+    return q4i_decode(a);
 }
 
 /* ======================================================================= batch ============= */

@@ -60,6 +60,7 @@ SIGNATURES = {
     "q4_gpu_kv_write_fd": (_b, [_v, _u32, _i]), "q4_gpu_kv_read_fd": (_b, [_v, _u32, _i]),
     "q4_gpu_kv_decode": (_b, [_v, _u32, _v, _i, _v, _v, _u32, _v, _u32, _u32, _u32, _f]),
     "q4_gpu_kv_decode_noalloc": (_b, [_v, _u32, _v, _i, _v, _v, _u32, _v, _u32, _u32, _u32, _f]),
+    "q4_gpu_kv_decode_idx_n": (_b, [_v, _u32, _v, _i, _v, _v, _u32, _v, _u32, _u32, _u32, _u32, _f]),
     "q4_gpu_kv_decode_partial": (_b, [_v, _u32, _v, _i, _v, _u32, _v, _u32, _u32, _u32, _f]),
     "q4_gpu_lse_merge": (_b, [_v, _u32, _u32, _u32, _v, _v]),
     "q4_hip_qsa_pool": (_b, [_v, _v, _v, _u32, _u32, _u32, _u32, _u32, _f, _f]),
@@ -207,6 +208,13 @@ class KVStore:
         check(self.L.q4_gpu_kv_append_decode_d(self.h, layer, _ptr(k), _ptr(v), _ptr(q), int(q_bf16), _ptr(gate),
                                                _ptr(out), n_head, _ptr(idx), width, idx_kvh_stride, scale),
               "q4_gpu_kv_append_decode_d")
+
+    def decode_idx_n(self, layer, q, out, n_head, scale, idx, width, n_tok, idx_tok_stride, idx_kvh_stride=0,
+                     gate=None, q_bf16=False):
+        """sparse prefill: n_tok queries, each over the rows of its own list (one launch)"""
+        check(self.L.q4_gpu_kv_decode_idx_n(self.h, layer, _ptr(q), int(q_bf16), _ptr(gate), _ptr(out), n_head,
+                                            _ptr(idx), width, idx_kvh_stride, idx_tok_stride, n_tok, scale),
+              "q4_gpu_kv_decode_idx_n")
 
     def decode_partial(self, layer, q, part, n_head, scale, idx=None, width=0, idx_kvh_stride=0, n_kv=0,
                        q_bf16=False):

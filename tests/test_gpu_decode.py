@@ -248,6 +248,45 @@ def test_causal_batch_through_reference_abi(oracle):
 
 
 @pytest.mark.parametrize("kind", [2, 1, 0])
+@pytest.mark.parametrize("per_kvh", [True, False])
+def test_sparse_prefill_on_the_store(oracle, kind, per_kvh):
+    """n_tok queries, each over its own list (one per kv head, or one shared by the kv heads as in the
+    reference), padding inside the lists, one launch on the library-owned store"""
+    lib()
+    n_head, n_kvh, hd, ctx, n_tok, width = 16, 2, 128, 3000, 37, 301
+    k, v, _ = make_case(oracle, 4100 + kind, ctx, n_head, n_kvh, hd, rope=False)
+    q = oracle.normal(4100, 7, n_tok * n_head * hd)
+    gate = oracle.normal(4100, 8, n_tok * n_head * hd)
+    rng = np.random.default_rng(41 + kind)
+    lists = n_kvh if per_kvh else 1
+    idx = np.full((n_tok, lists, width), -1, np.int32)
+    for t in range(n_tok):
+        for l in range(lists):
+            m = int(rng.integers(1, width + 1))
+            idx[t, l, np.sort(rng.choice(width, m, replace=False))] = np.sort(rng.choice(ctx, m, replace=False))
+    idx[5] = -1                                  # a token that selects nothing -> zeros
+    kc, vc = oracle.kv_write(k, kind), oracle.kv_write(v, kind)
+    ref = oracle.attn(q, kc, vc, gate, n_head, n_kvh, hd, n_tok, 0, ctx, 0.0884, kind, idx=idx, width=width,
+                      idx_kvh_stride=width if per_kvh else 0)
+    st = q4gpu.KVStore(1, n_kvh, hd, ctx, kind)
+    st.append(0, dev(k), dev(v), 0, ctx)
+    dout = torch.full((n_tok * n_head * hd,), 3.0, device="cuda")
+    st.decode_idx_n(0, dev(q), dout, n_head, 0.0884, dev(idx), width, n_tok, idx_tok_stride=lists * width,
+                    idx_kvh_stride=width if per_kvh else 0, gate=dev(gate))
+    got = host(dout).reshape(n_tok, n_head, hd)
+    assert_close(got, ref, "sparse prefill kind %d" % kind)
+    assert not got[5].any()
+    # bf16 queries: same call, the oracle sees the rounded values
+    qb = dev(q).to(torch.bfloat16)
+    ref_b = oracle.attn(host(qb.float()), kc, vc, None, n_head, n_kvh, hd, n_tok, 0, ctx, 0.0884, kind, idx=idx,
+                        width=width, idx_kvh_stride=width if per_kvh else 0)
+    st.decode_idx_n(0, qb, dout, n_head, 0.0884, dev(idx), width, n_tok, idx_tok_stride=lists * width,
+                    idx_kvh_stride=width if per_kvh else 0, q_bf16=True)
+    assert_close(host(dout).reshape(n_tok, n_head, hd), ref_b, "sparse prefill bf16 q kind %d" % kind)
+    st.close()
+
+
+@pytest.mark.parametrize("kind", [2, 1, 0])
 def test_sequence_shards_partial_and_merge(oracle, kind):
     """One sequence split by position over G stores: each computes (m, l, acc), the records are merged
     (the exchange payload of the sequence-sharded decode) == attention over the whole sequence; records

@@ -170,11 +170,14 @@ def test_store_append_d_and_graph_replay(oracle):
     q4gpu.use_torch_stream()
 
 
+@pytest.mark.parametrize("n", [77, 199])
 @pytest.mark.parametrize("kind", [2, 1, 0])
-def test_prefix_save_restore_round_trip(oracle, kind):
-    """save rows [0,n) -> wipe -> restore == original, to device memory and to pinned host memory"""
+def test_prefix_save_restore_round_trip(oracle, kind, n):
+    """save rows [0,n) -> wipe -> restore == original, to device memory (the library's own copy kernel:
+    one partial 32 KB tile per row at 77 rows, several at 199; a buffer that is not 16-byte aligned takes
+    the driver's 2-D copy) and to pinned host memory"""
     L = lib()
-    n_layers, n_kvh, hd, max_kv, n = 3, 2, 128, 200, 77
+    n_layers, n_kvh, hd, max_kv = 3, 2, 128, 200
     st = q4gpu.KVStore(n_layers, n_kvh, hd, max_kv, kind)
     kvw = n_kvh * hd
     ref = {}
@@ -185,9 +188,9 @@ def test_prefix_save_restore_round_trip(oracle, kind):
         ref[layer] = (oracle.kv_write(k, kind), oracle.kv_write(v, kind))
     nbytes = st.snapshot_bytes(n)
     assert nbytes == n * n_layers * 2 * st.token_bytes       # same byte count as the reference snapshot
-    for host_side in (False, True):
+    for host_side, skew in ((False, 0), (False, 8), (True, 0)):
         snap = torch.empty(nbytes, dtype=torch.uint8, device="cpu", pin_memory=True) if host_side else \
-            torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+            torch.empty(nbytes + 16, dtype=torch.uint8, device="cuda")[skew:skew + nbytes]
         st.save(n, snap, host=host_side)
         torch.cuda.synchronize()
         other = q4gpu.KVStore(n_layers, n_kvh, hd, max_kv, kind)
