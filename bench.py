@@ -47,7 +47,7 @@ PAD = 64                              # token slots appended during the run
 L2_BYTES = 126e6
 # dram bytes per algorithmic byte of the batched decode kernel, from the ncu capture summarised in
 # profiles/ (None until a capture exists)
-DECODE_TRAFFIC_RATIO = 1.136   # profiles/decode_q8_batched_sparse.md: (78.9 + 1.8) MB dram per 71.1 MB algorithmic
+DECODE_TRAFFIC_RATIO = 1.14    # profiles/decode_q8_batched_sparse.md: (79.0 + 2.1) MB dram per 71.1 MB algorithmic
 
 
 def draw_contexts(n, lo=1024, hi=131072, seed=SEED + 4):
