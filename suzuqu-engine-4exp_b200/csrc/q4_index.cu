@@ -128,10 +128,17 @@ __global__ void __launch_bounds__(SC_WARPS * 32) q4_ix_score_k(const float *q, c
         if (b < lim) {
             const uint32_t row = buf0 + which * SC_TILE_BYTES + lane * SC_ROW_FLOATS * 4u;
             float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
-#pragma unroll 8
+            /* the row is read two steps ahead of the multiply-adds that use it */
+            float4 kq[3];
+            asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(kq[0].x), "=f"(kq[0].y), "=f"(kq[0].z), "=f"(kq[0].w) : "r"(row));
+            asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(kq[1].x), "=f"(kq[1].y), "=f"(kq[1].z), "=f"(kq[1].w) : "r"(row + 16u));
+#pragma unroll
             for (uint32_t i = 0; i < IX_HD / 4; i++) {
-                float4 k;
-                asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(k.x), "=f"(k.y), "=f"(k.z), "=f"(k.w) : "r"(row + 16u * i));
+                if (i + 2 < IX_HD / 4)
+                    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+                                 : "=f"(kq[(i + 2) % 3].x), "=f"(kq[(i + 2) % 3].y), "=f"(kq[(i + 2) % 3].z), "=f"(kq[(i + 2) % 3].w)
+                                 : "r"(row + 16u * (i + 2)));
+                const float4 k = kq[i % 3];
                 const float4 q0 = qs[4 * i], q1 = qs[4 * i + 1], q2 = qs[4 * i + 2], q3 = qs[4 * i + 3];
                 d0 = __fmaf_rn(q0.x, k.x, d0); d1 = __fmaf_rn(q0.y, k.x, d1); d2 = __fmaf_rn(q0.z, k.x, d2); d3 = __fmaf_rn(q0.w, k.x, d3);
                 d0 = __fmaf_rn(q1.x, k.y, d0); d1 = __fmaf_rn(q1.y, k.y, d1); d2 = __fmaf_rn(q1.z, k.y, d2); d3 = __fmaf_rn(q1.w, k.y, d3);
