@@ -97,12 +97,6 @@ __global__ void __launch_bounds__(SC_WARPS * 32) q4_ix_score_k(const float *q, c
     const uint32_t pos = (pp ? (uint32_t)*pp : pos0) + t;
     const uint32_t n_vis = ratio ? (pos + 1u) / ratio : 0u;
     if (pp) n_blocks = n_vis;      /* device position: the bound is derived here */
-    for (uint32_t d = threadIdx.x; d < IX_HD; d += SC_WARPS * 32u) {
-        const float *qt = q + (size_t)t * n_head * IX_HD + d;
-        qs[d] = make_float4(qt[0], n_head > 1 ? qt[IX_HD] : 0.f, n_head > 2 ? qt[2 * IX_HD] : 0.f,
-                            n_head > 3 ? qt[3 * IX_HD] : 0.f);
-    }
-    __syncthreads();
     const uint32_t buf0 = (uint32_t)__cvta_generic_to_shared(sc_smem + IX_HD * sizeof(float4)) + warp * 2u * SC_TILE_BYTES;
     const uint32_t lim = min(n_blocks, n_vis);                       /* rows to score */
     const uint32_t n_tiles = (lim + 31u) / 32u;
@@ -119,6 +113,13 @@ __global__ void __launch_bounds__(SC_WARPS * 32) q4_ix_score_k(const float *q, c
         asm volatile("cp.async.commit_group;" ::: "memory");   /* one group per call keeps the wait count uniform */
     };
     fetch(first, 0);
+    /* the query is staged while the first tile is in flight */
+    for (uint32_t d = threadIdx.x; d < IX_HD; d += SC_WARPS * 32u) {
+        const float *qt = q + (size_t)t * n_head * IX_HD + d;
+        qs[d] = make_float4(qt[0], n_head > 1 ? qt[IX_HD] : 0.f, n_head > 2 ? qt[2 * IX_HD] : 0.f,
+                            n_head > 3 ? qt[3 * IX_HD] : 0.f);
+    }
+    __syncthreads();
     uint32_t which = 0;
     for (uint32_t tile = first; tile < n_tiles; tile += step, which ^= 1u) {
         fetch(tile + step, which ^ 1u);
