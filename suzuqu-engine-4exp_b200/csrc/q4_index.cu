@@ -85,6 +85,19 @@ __global__ void __launch_bounds__(128) q4_ix_pool_k(const __half *raw, float *po
  * fully coalesced, 16 KB in flight per warp while the previous tile is being scored -- and every lane
  * walks its own row there.  Rows are 132 floats apart: 16-byte reads of eight consecutive rows fall
  * into eight different bank groups, so the walk is conflict free; the query is read as a broadcast. */
+/* Programmatic dependent launch: the blocks of a launch may become resident while the previous kernel of
+ * the stream drains; nothing the previous kernels write (position word, pool, scores, queries) is read
+ * before this point.  A no-op for a launch without the attribute. */
+__device__ __forceinline__ void ix_pdl_sync() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+/* Q4_IX_PDL=0 switches it off for the score and selection launches */
+bool ix_pdl() {
+    static int on = -1;
+    if (on < 0) { const char *e = getenv("Q4_IX_PDL"); on = e ? atoi(e) : 1; }
+    return on != 0;
+}
 constexpr uint32_t SC_ROW_FLOATS = IX_HD + 4, SC_WARPS = 2;
 constexpr uint32_t SC_TILE_BYTES = 32u * SC_ROW_FLOATS * sizeof(float);
 constexpr uint32_t SC_SMEM = SC_WARPS * 2u * SC_TILE_BYTES + IX_HD * sizeof(float4);
@@ -94,6 +107,7 @@ __global__ void __launch_bounds__(SC_WARPS * 32) q4_ix_score_k(const float *q, c
     extern __shared__ __align__(16) uint8_t sc_smem[];
     float4 *qs = reinterpret_cast<float4 *>(sc_smem);   /* [dim] = the 4 heads' values (0 for heads that do not exist) */
     const uint32_t t = blockIdx.y, lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    ix_pdl_sync();
     const uint32_t pos = (pp ? (uint32_t)*pp : pos0) + t;
     const uint32_t n_vis = ratio ? (pos + 1u) / ratio : 0u;
     if (pp) n_blocks = n_vis;      /* device position: the bound is derived here */
@@ -175,9 +189,19 @@ bool score_launch(const float *q, const float *pool, float *score, uint32_t n_to
     if (n_tok > 1) gx = (gx + n_tok - 1u) / n_tok;
     if (gx > need) gx = need;
     if (gx < 1) gx = 1;
-    q4_ix_score_k<<<dim3(gx, n_tok), SC_WARPS * 32, SC_SMEM, g_q4.stream>>>(q, pool, score, n_blocks, stride, n_head, pos0,
-                                                                            ratio, pp);
-    return q4i_check(cudaGetLastError(), "qsa_score launch");
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(gx, n_tok);
+    cfg.blockDim = dim3(SC_WARPS * 32);
+    cfg.dynamicSmemBytes = SC_SMEM;
+    cfg.stream = g_q4.stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = ix_pdl() ? 1 : 0;
+    return q4i_check(cudaLaunchKernelEx(&cfg, q4_ix_score_k, q, pool, score, n_blocks, stride, n_head, pos0, ratio, pp),
+                     "qsa_score launch");
 }
 
 /* ---- selection: one block per token */
@@ -388,6 +412,7 @@ __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topkc_k(const float *scor
     __shared__ int32_t chosen[IX_MAX_KBLK];       /* block 0's copy is the list */
     __shared__ uint32_t warp_tot[33], st_prefix, st_hi;
     const uint32_t t = blockIdx.y, tx = threadIdx.x, lane = tx & 31u, warp = tx >> 5, rank = tkc_rank();
+    ix_pdl_sync();
     const uint32_t pos = (pp ? (uint32_t)*pp : pos0) + t;
     const uint32_t n_vis = ratio ? (pos + 1u) / ratio : 0u;
     const uint32_t need = n_vis < k_blk ? n_vis : k_blk;
@@ -529,13 +554,15 @@ bool launch_topk(const float *score, int32_t *sel, uint32_t n_tok, uint32_t stri
         cfg.gridDim = dim3(TKC_BLOCKS, n_tok);
         cfg.blockDim = dim3(IX_TK_THREADS);
         cfg.stream = g_q4.stream;
-        cudaLaunchAttribute at[1];
+        cudaLaunchAttribute at[2];
+        at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[1].val.programmaticStreamSerializationAllowed = 1;
         at[0].id = cudaLaunchAttributeClusterDimension;
         at[0].val.clusterDim.x = TKC_BLOCKS;
         at[0].val.clusterDim.y = 1;
         at[0].val.clusterDim.z = 1;
         cfg.attrs = at;
-        cfg.numAttrs = 1;
+        cfg.numAttrs = ix_pdl() ? 2 : 1;
         return q4i_check(cudaLaunchKernelEx(&cfg, q4_ix_topkc_k, score, sel, stride, k_blk, ratio, pos0, width, pp),
                          "qsa_topk launch");
     }
