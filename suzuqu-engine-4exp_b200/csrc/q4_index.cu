@@ -374,9 +374,11 @@ __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topk1_k(const float *scor
 /* ---- selection by a cluster of 8 blocks (rows of up to 65 536 pooled blocks = ctx 262 144): every
  * thread keeps its 8 keys in registers (block r, warp w, step i, lane l holds index 8192 r + 256 w +
  * 32 i + l, so (r, w, i, l) is ascending index order), the per-pass histograms are summed into block
- * 0 through distributed shared memory, every block picks the digit from that sum, and the ordered
- * emit ranks by ballots, a scan over the warps and a scan over the blocks.  One cluster barrier per
- * pass; 8 SMs instead of one. */
+ * 0 through distributed shared memory, every block picks the digit from that sum (copied back with one
+ * load per thread: one warp reading its bins from block 0 itself was 3 us slower), and the ordered emit ranks by ballots, one scan over the warps and the other
+ * blocks' counts, and writes the positions straight into the list.  One cluster barrier and three block
+ * barriers per pass, one cluster barrier for the counts, none after the last remote access; 8 SMs
+ * instead of one. */
 constexpr uint32_t TKC_BLOCKS = 8, TKC_KPT = 8, TKC_MAX_ROW = TKC_BLOCKS * IX_TK_THREADS * TKC_KPT;
 __device__ __forceinline__ uint32_t tkc_rank() {
     uint32_t r;
@@ -406,10 +408,9 @@ __device__ __forceinline__ void tkc_red_add(uint32_t ra, uint32_t v) {
 __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topkc_k(const float *score, int32_t *sel, uint32_t stride,
                                                                uint32_t k_blk, uint32_t ratio, uint32_t pos0,
                                                                uint32_t width, const int32_t *pp) {
-    __shared__ uint32_t hist[256];
+    __shared__ uint32_t lhist[4][256];            /* this block's histogram of every pass, zeroed once */
     __shared__ uint32_t ghist[4][256];            /* block 0's copy is the cluster-wide sum, one per pass */
-    __shared__ uint32_t cta_cnt[TKC_BLOCKS][2];   /* block 0's copy: (above, ties) of every block */
-    __shared__ int32_t chosen[IX_MAX_KBLK];       /* block 0's copy is the list */
+    __shared__ uint32_t cta_cnt[TKC_BLOCKS];      /* (ties << 16 | above) of every block, pushed by its owner */
     __shared__ uint32_t warp_tot[33], st_prefix, st_hi;
     const uint32_t t = blockIdx.y, tx = threadIdx.x, lane = tx & 31u, warp = tx >> 5, rank = tkc_rank();
     ix_pdl_sync();
@@ -431,15 +432,19 @@ __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topkc_k(const float *scor
         const uint32_t b = base + 32u * i;
         key[i] = b < n_vis ? ix_key(__ldcg(row + b)) : 0u;
     }
-    if (rank == 0) {
-        for (uint32_t i = tx; i < 4u * 256u; i += IX_TK_THREADS) (&ghist[0][0])[i] = 0u;
-    }
+    (&lhist[0][0])[tx] = 0u;                      /* 4 x 256 words, one per thread */
+    if (rank == 0) (&ghist[0][0])[tx] = 0u;
+    static_assert(IX_TK_THREADS == 4 * 256, "one histogram word per thread");
     if (tx == 0) { st_prefix = 0u; st_hi = 0u; }
+    /* the tail of the list (positions behind the last complete block) does not depend on the selection */
+    const uint32_t ncs = need * ratio;
+    for (uint32_t w = max(w0, ncs) + tx; w < w1; w += IX_TK_THREADS) {
+        const uint32_t tail = n_vis * ratio + (w - ncs);
+        out[w] = tail <= pos ? (int32_t)tail : -1;
+    }
     tkc_sync();   /* block 0's sums are zero before anyone adds to them */
 
     for (int p = 0; p < 4; p++) {
-        if (tx < 256) hist[tx] = 0u;
-        __syncthreads();
         const uint32_t sh = 24u - 8u * p, pre = st_prefix;
 #pragma unroll
         for (uint32_t i = 0; i < TKC_KPT; i++) {
@@ -450,16 +455,16 @@ __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topkc_k(const float *scor
             if (m) {   /* one add per warp where the lanes agree, else one per lane */
                 const uint32_t first = __shfl_sync(0xffffffffu, bin, __ffs(m) - 1);
                 if (__all_sync(0xffffffffu, !in || bin == first)) {
-                    if (lane == (uint32_t)(__ffs(m) - 1)) atomicAdd(&hist[first], (uint32_t)__popc(m));
+                    if (lane == (uint32_t)(__ffs(m) - 1)) atomicAdd(&lhist[p][first], (uint32_t)__popc(m));
                 } else if (in) {
-                    atomicAdd(&hist[bin], 1u);
+                    atomicAdd(&lhist[p][bin], 1u);
                 }
             }
         }
         __syncthreads();
-        if (tx < 256 && hist[tx]) tkc_red_add(tkc_remote(&ghist[p][tx], 0), hist[tx]);
+        if (tx < 256 && lhist[p][tx]) tkc_red_add(tkc_remote(&ghist[p][tx], 0), lhist[p][tx]);
         tkc_sync();
-        if (tx < 256) hist[tx] = tkc_ld(tkc_remote(&ghist[p][tx], 0));   /* the cluster-wide sum, one load per thread */
+        if (tx < 256) lhist[p][tx] = tkc_ld(tkc_remote(&ghist[p][tx], 0));   /* the cluster-wide sum, one load per thread */
         __syncthreads();
         if (tx < 32) {
             /* digit = the highest bin whose count, added to those above it, reaches the target: lane l owns
@@ -467,7 +472,7 @@ __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topkc_k(const float *scor
             const uint32_t target = need - st_hi;
             uint32_t c[8], tot = 0;
 #pragma unroll
-            for (int j = 0; j < 8; j++) { c[j] = hist[255 - 8 * (int)lane - j]; tot += c[j]; }
+            for (int j = 0; j < 8; j++) { c[j] = lhist[p][255 - 8 * (int)lane - j]; tot += c[j]; }
             uint32_t incl = tot;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -490,7 +495,8 @@ __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topkc_k(const float *scor
     }
     const uint32_t thr = st_prefix, n_gt = st_hi;
 
-    /* counts: per warp by ballots, per block by a scan over the warps, per cluster through block 0 */
+    /* counts: per warp by ballots, per block by one scan over the warps (ties in the high half-word: a
+     * block holds at most 8192 keys), per cluster by every block pushing its pair to all the others */
     uint32_t ng = 0, ne = 0;
 #pragma unroll
     for (uint32_t i = 0; i < TKC_KPT; i++) {
@@ -498,51 +504,29 @@ __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topkc_k(const float *scor
         ng += __popc(__ballot_sync(0xffffffffu, live && key[i] > thr));
         ne += __popc(__ballot_sync(0xffffffffu, live && key[i] == thr));
     }
-    uint32_t og, oe;
-    const uint32_t tot_g = block_excl_scan(lane == 0 ? ng : 0u, og, warp_tot);
-    const uint32_t tot_e = block_excl_scan(lane == 0 ? ne : 0u, oe, warp_tot);
-    og = __shfl_sync(0xffffffffu, og, 0);
-    oe = __shfl_sync(0xffffffffu, oe, 0);
-    if (tx == 0) {
-        tkc_st(tkc_remote(&cta_cnt[rank][0], 0), tot_g);
-        tkc_st(tkc_remote(&cta_cnt[rank][1], 0), tot_e);
-    }
-    tkc_sync();
-    for (uint32_t r = 0; r < rank; r++) {
-        og += tkc_ld(tkc_remote(&cta_cnt[r][0], 0));
-        oe += tkc_ld(tkc_remote(&cta_cnt[r][1], 0));
-    }
-    /* ordered emit into block 0's list: above the threshold in index order, then ties until `need` is full */
+    static_assert(IX_TK_THREADS * TKC_KPT < 65536, "two counts share a word");
+    uint32_t off;
+    const uint32_t tot = block_excl_scan(lane == 0 ? (ne << 16 | ng) : 0u, off, warp_tot);
+    off = __shfl_sync(0xffffffffu, off, 0);
+    if (tx < TKC_BLOCKS) tkc_st(tkc_remote(&cta_cnt[rank], tx), tot);
+    tkc_sync();   /* the last access to another block's shared memory is behind this point */
+    for (uint32_t r = 0; r < rank; r++) off += cta_cnt[r];   /* neither half carries: at most 7 x 8192 + 8191 keys precede a thread */
+    uint32_t og = off & 0xffffu, oe = off >> 16;
+    /* ordered emit, straight into the list: above the threshold in index order, then ties until `need` is full */
     const uint32_t lt = (1u << lane) - 1u;
 #pragma unroll
     for (uint32_t i = 0; i < TKC_KPT; i++) {
         const uint32_t b = base + 32u * i;
         const bool live = b < n_vis, gt = live && key[i] > thr, eq = live && key[i] == thr;
         const uint32_t mg = __ballot_sync(0xffffffffu, gt), me = __ballot_sync(0xffffffffu, eq);
-        if (gt) {
-            const uint32_t at = og + __popc(mg & lt);
-            if (at < IX_MAX_KBLK) tkc_st(tkc_remote(&chosen[at], 0), b);
-        } else if (eq) {
-            const uint32_t at = n_gt + oe + __popc(me & lt);
-            if (at < need) tkc_st(tkc_remote(&chosen[at], 0), b);
-        }
+        uint32_t at = need;
+        if (gt) at = og + __popc(mg & lt);
+        else if (eq) at = n_gt + oe + __popc(me & lt);
+        if (at < need)
+            for (uint32_t j = 0; j < ratio && at * ratio + j < width; j++) out[at * ratio + j] = (int32_t)(b * ratio + j);
         og += __popc(mg);
         oe += __popc(me);
     }
-    tkc_sync();
-    const uint32_t ncs = need * ratio;
-    for (uint32_t w = w0 + tx; w < w1; w += IX_TK_THREADS) {
-        int32_t v;
-        if (w < ncs) {
-            const uint32_t i = w / ratio, j = w - i * ratio;
-            v = (int32_t)(tkc_ld(tkc_remote(&chosen[i], 0)) * ratio + j);
-        } else {
-            const uint32_t tail = n_vis * ratio + (w - ncs);
-            v = tail <= pos ? (int32_t)tail : -1;
-        }
-        out[w] = v;
-    }
-    tkc_sync();   /* block 0's shared memory stays until every block has read the list */
 }
 
 /* rows that fit the cluster kernel go there, longer ones to the single block */
