@@ -380,6 +380,7 @@ __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topk1_k(const float *scor
  * barriers per pass, one cluster barrier for the counts, none after the last remote access; 8 SMs
  * instead of one. */
 constexpr uint32_t TKC_BLOCKS = 8, TKC_KPT = 8, TKC_MAX_ROW = TKC_BLOCKS * IX_TK_THREADS * TKC_KPT;
+constexpr uint32_t TKC_CAND = 256;   /* most keys sharing a 16-bit prefix that are ranked directly */
 __device__ __forceinline__ uint32_t tkc_rank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -401,6 +402,11 @@ __device__ __forceinline__ uint32_t tkc_ld(uint32_t ra) {
 __device__ __forceinline__ void tkc_st(uint32_t ra, uint32_t v) {
     asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(ra), "r"(v) : "memory");
 }
+__device__ __forceinline__ uint32_t tkc_atom_add(uint32_t ra, uint32_t v) {
+    uint32_t old;
+    asm volatile("atom.relaxed.cluster.shared::cluster.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(ra), "r"(v) : "memory");
+    return old;
+}
 __device__ __forceinline__ void tkc_red_add(uint32_t ra, uint32_t v) {
     asm volatile("red.relaxed.cluster.shared::cluster.add.u32 [%0], %1;" ::"r"(ra), "r"(v) : "memory");
 }
@@ -411,7 +417,8 @@ __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topkc_k(const float *scor
     __shared__ uint32_t lhist[4][256];            /* this block's histogram of every pass, zeroed once */
     __shared__ uint32_t ghist[4][256];            /* block 0's copy is the cluster-wide sum, one per pass */
     __shared__ uint32_t cta_cnt[TKC_BLOCKS];      /* (ties << 16 | above) of every block, pushed by its owner */
-    __shared__ uint32_t warp_tot[33], st_prefix, st_hi;
+    __shared__ uint32_t warp_tot[33], st_prefix, st_hi, st_cnt;
+    __shared__ uint32_t cand[TKC_CAND], cand_n;   /* block 0's copy collects the keys that share the 16-bit prefix */
     const uint32_t t = blockIdx.y, tx = threadIdx.x, lane = tx & 31u, warp = tx >> 5, rank = tkc_rank();
     ix_pdl_sync();
     const uint32_t pos = (pp ? (uint32_t)*pp : pos0) + t;
@@ -435,7 +442,7 @@ __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topkc_k(const float *scor
     (&lhist[0][0])[tx] = 0u;                      /* 4 x 256 words, one per thread */
     if (rank == 0) (&ghist[0][0])[tx] = 0u;
     static_assert(IX_TK_THREADS == 4 * 256, "one histogram word per thread");
-    if (tx == 0) { st_prefix = 0u; st_hi = 0u; }
+    if (tx == 0) { st_prefix = 0u; st_hi = 0u; cand_n = 0u; }
     /* the tail of the list (positions behind the last complete block) does not depend on the selection */
     const uint32_t ncs = need * ratio;
     for (uint32_t w = max(w0, ncs) + tx; w < w1; w += IX_TK_THREADS) {
@@ -444,6 +451,7 @@ __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topkc_k(const float *scor
     }
     tkc_sync();   /* block 0's sums are zero before anyone adds to them */
 
+    bool ranked = false;   /* the threshold came from ranking the last candidates, st_cnt holds the count above it */
     for (int p = 0; p < 4; p++) {
         const uint32_t sh = 24u - 8u * p, pre = st_prefix;
 #pragma unroll
@@ -481,19 +489,53 @@ __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topkc_k(const float *scor
             }
             uint32_t above = incl - tot;
             if (above < target && incl >= target) {   /* exactly one lane */
-                uint32_t dg = 0;
+                uint32_t dg = 0, cnt = 0;
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
-                    if (above + c[j] >= target) { dg = 255u - 8u * lane - (uint32_t)j; break; }
+                    if (above + c[j] >= target) { dg = 255u - 8u * lane - (uint32_t)j; cnt = c[j]; break; }
                     above += c[j];
                 }
                 st_hi += above;
                 st_prefix = (pre << 8) | dg;
+                st_cnt = cnt;   /* keys that share the prefix chosen so far */
             }
         }
         __syncthreads();
+        if (p == 1 && st_cnt <= TKC_CAND) {
+            /* After 16 bits only a handful of keys still share the prefix (the same decision in every
+             * block: the counts are cluster-wide).  They are collected in block 0, and every block ranks
+             * them itself: the key with fewer than `target` keys above it and at least `target` at or
+             * above it is the threshold.  One cluster barrier instead of the two remaining passes. */
+            const uint32_t pre16 = st_prefix, target = need - st_hi;
+#pragma unroll
+            for (uint32_t i = 0; i < TKC_KPT; i++)
+                if (base + 32u * i < n_vis && (key[i] >> 16) == pre16) {
+                    const uint32_t slot = tkc_atom_add(tkc_remote(&cand_n, 0), 1u);
+                    if (slot < TKC_CAND) tkc_st(tkc_remote(&cand[slot], 0), key[i]);
+                }
+            tkc_sync();
+            const uint32_t n = st_cnt;   /* exactly the keys just collected */
+            if (rank != 0 && tx < n) cand[tx] = tkc_ld(tkc_remote(&cand[tx], 0));
+            __syncthreads();
+            if (tx < n) {
+                const uint32_t mine = cand[tx];
+                uint32_t gt = 0, ge = 0;
+                for (uint32_t j = 0; j < n; j++) {
+                    const uint32_t o = cand[j];
+                    gt += o > mine;
+                    ge += o >= mine;
+                }
+                if (gt < target && ge >= target) {   /* every copy of the threshold key writes the same values */
+                    st_prefix = mine;
+                    st_cnt = st_hi + gt;
+                }
+            }
+            __syncthreads();
+            ranked = true;
+            break;
+        }
     }
-    const uint32_t thr = st_prefix, n_gt = st_hi;
+    const uint32_t thr = st_prefix, n_gt = ranked ? st_cnt : st_hi;
 
     /* counts: per warp by ballots, per block by one scan over the warps (ties in the high half-word: a
      * block holds at most 8192 keys), per cluster by every block pushing its pair to all the others */
