@@ -548,7 +548,29 @@ def extras_indexer(torch, q4gpu, L, ext, peak_gbs):
     for gr in graphs:
         L.q4_hip_graph_free(gr)
     st.close()
+    # ---- batched form: 8 sessions at ctx 262144, one score launch and one selection launch per layer for all of
+    # them (q4_gpu_qsa_select_batch); 4 rotating pool sets of 8 x 33.5 MB, far beyond L2
+    n_sess, sets = 8, 4
+    del pool, score, sel
+    torch.cuda.empty_cache()
+    bpool = torch.randn(sets, n_sess, nb, HD, device="cuda")
+    ptrs = torch.tensor([[bpool[g, i].data_ptr() for i in range(n_sess)] for g in range(sets)], dtype=torch.int64, device="cuda")
+    bpos = torch.full((n_sess,), pos, dtype=torch.int32, device="cuda")
+    bq = torch.randn(n_sess, n_head, HD, device="cuda")
+    bscore = torch.empty(n_sess, nb, device="cuda")
+    bsel = torch.empty(n_sess, WIDTH, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+
+    def batch_one(i):
+        assert L.q4_gpu_qsa_select_batch(ptrs[i % sets].data_ptr(), bpos.data_ptr(), bq.data_ptr(), bscore.data_ptr(),
+                                         bsel.data_ptr(), n_sess, nb, n_head, HD, k_blk, ratio, WIDTH)
+    timed(torch, ext, batch_one, sets)
+    dtb = timed(torch, ext, batch_one, 6 * sets) / (6 * sets)
     by = nb * HD * 4
+    res["batch8_score_plus_select_us_per_layer"] = dtb * 1e6
+    res["batch8_pool_gbs"] = n_sess * by / dtb / 1e9
+    res["batch8_pool_frac_of_measured_hbm"] = n_sess * by / dtb / 1e9 / peak_gbs
+    del bpool
     res.update({"workload": "QSA indexer, ctx 262144: 65536 pooled blocks x 4 heads scored, exact top-512 + tail -> 2051 positions; "
                             "select_plus_attend = score + select + fused append + sparse decode over the produced list",
                 "pool_bytes_per_layer": by, "score_gbs": by / res["score_us_per_layer"] / 1e3,

@@ -153,6 +153,17 @@ bool q4_hip_qsa_topk(const float *score, int32_t *sel, uint32_t n_tok, uint32_t 
 bool q4_hip_qsa_topk_d(const float *score, int32_t *sel, uint32_t stride, uint32_t k_blk, uint32_t ratio,
                        uint32_t width);
 
+/* Batched indexer for concurrent sessions (additive): row t of q [n_sess][n_head][hd], score
+ * [n_sess][stride] and sel [n_sess][width] belongs to session t, which has its own pool (pools[t]: a
+ * device array of device pointers) and its own position (pos[t]: a device array, e.g. the one the
+ * batch decode reads).  Two launches for all sessions; the same arithmetic and the same lists as one
+ * q4_hip_qsa_score_d + q4_hip_qsa_topk_d pair per session (src/q4_fwd.c:894-920).  Every session must
+ * have at most `stride` visible blocks.  The lists feed q4_gpu_batch_decode / _append_decode with
+ * idx_kvh_stride 0 and idx_sess_stride width. */
+bool q4_gpu_qsa_select_batch(const float *const *pools, const int32_t *pos, const float *q, float *score,
+                             int32_t *sel, uint32_t n_sess, uint32_t stride, uint32_t n_head, uint32_t hd,
+                             uint32_t k_blk, uint32_t ratio, uint32_t width);
+
 /* ======================================================================================= */
 /* 2. B200-native additions                                                                 */
 /* ======================================================================================= */

@@ -103,14 +103,17 @@ constexpr uint32_t SC_TILE_BYTES = 32u * SC_ROW_FLOATS * sizeof(float);
 constexpr uint32_t SC_SMEM = SC_WARPS * 2u * SC_TILE_BYTES + IX_HD * sizeof(float4);
 __global__ void __launch_bounds__(SC_WARPS * 32) q4_ix_score_k(const float *q, const float *pool, float *score,
                                                                uint32_t n_blocks, uint32_t stride, uint32_t n_head,
-                                                               uint32_t pos0, uint32_t ratio, const int32_t *pp) {
+                                                               uint32_t pos0, uint32_t ratio, const int32_t *pp,
+                                                               const float *const *pools, const int32_t *pos_arr) {
     extern __shared__ __align__(16) uint8_t sc_smem[];
     float4 *qs = reinterpret_cast<float4 *>(sc_smem);   /* [dim] = the 4 heads' values (0 for heads that do not exist) */
     const uint32_t t = blockIdx.y, lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     ix_pdl_sync();
-    const uint32_t pos = (pp ? (uint32_t)*pp : pos0) + t;
+    /* batched form: row t is session t, with its own pool and its own position */
+    const uint32_t pos = pos_arr ? (uint32_t)pos_arr[t] : (pp ? (uint32_t)*pp : pos0) + t;
+    if (pos_arr) pool = pools[t];
     const uint32_t n_vis = ratio ? (pos + 1u) / ratio : 0u;
-    if (pp) n_blocks = n_vis;      /* device position: the bound is derived here */
+    if (pp || pos_arr) n_blocks = min(n_vis, stride);      /* device position: the bound is derived here */
     const uint32_t buf0 = (uint32_t)__cvta_generic_to_shared(sc_smem + IX_HD * sizeof(float4)) + warp * 2u * SC_TILE_BYTES;
     const uint32_t lim = min(n_blocks, n_vis);                       /* rows to score */
     const uint32_t n_tiles = (lim + 31u) / 32u;
@@ -174,7 +177,8 @@ __global__ void __launch_bounds__(SC_WARPS * 32) q4_ix_score_k(const float *q, c
         score[(size_t)t * stride + b] = -1.0e30f;
 }
 bool score_launch(const float *q, const float *pool, float *score, uint32_t n_tok, uint32_t n_blocks, uint32_t stride,
-                  uint32_t n_head, uint32_t pos0, uint32_t ratio, const int32_t *pp) {
+                  uint32_t n_head, uint32_t pos0, uint32_t ratio, const int32_t *pp,
+                  const float *const *pools = nullptr, const int32_t *pos_arr = nullptr) {
     static bool done = false;
     if (!done) {
         if (!q4i_check(cudaFuncSetAttribute(q4_ix_score_k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SC_SMEM),
@@ -183,7 +187,7 @@ bool score_launch(const float *q, const float *pool, float *score, uint32_t n_to
         done = true;
     }
     /* persistent grid: 3 blocks of 2 warps per SM share 227 KB; fewer when the row is short */
-    const uint32_t rows = pp ? stride : n_blocks;
+    const uint32_t rows = pp || pos_arr ? stride : n_blocks;
     uint32_t gx = (uint32_t)g_q4.sm_count * 3u;
     const uint32_t need = (rows + SC_WARPS * 32u - 1u) / (SC_WARPS * 32u);
     if (n_tok > 1) gx = (gx + n_tok - 1u) / n_tok;
@@ -200,7 +204,7 @@ bool score_launch(const float *q, const float *pool, float *score, uint32_t n_to
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = ix_pdl() ? 1 : 0;
-    return q4i_check(cudaLaunchKernelEx(&cfg, q4_ix_score_k, q, pool, score, n_blocks, stride, n_head, pos0, ratio, pp),
+    return q4i_check(cudaLaunchKernelEx(&cfg, q4_ix_score_k, q, pool, score, n_blocks, stride, n_head, pos0, ratio, pp, pools, pos_arr),
                      "qsa_score launch");
 }
 
@@ -261,11 +265,11 @@ __device__ __forceinline__ void ix_walk(const float *row, uint32_t n_vis, uint32
 
 __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topk1_k(const float *score, int32_t *sel, uint32_t stride,
                                                               uint32_t k_blk, uint32_t ratio, uint32_t pos0,
-                                                              uint32_t width, const int32_t *pp) {
+                                                              uint32_t width, const int32_t *pp, const int32_t *pos_arr) {
     __shared__ uint32_t hist[256], warp_tot[33], st_prefix, st_hi;
     __shared__ int32_t chosen[IX_MAX_KBLK];
     const uint32_t t = blockIdx.x, tx = threadIdx.x, lane = tx & 31u;
-    const uint32_t pos = (pp ? (uint32_t)*pp : pos0) + t;
+    const uint32_t pos = pos_arr ? (uint32_t)pos_arr[t] : (pp ? (uint32_t)*pp : pos0) + t;
     const uint32_t n_vis = ratio ? (pos + 1u) / ratio : 0u;
     const uint32_t need = n_vis < k_blk ? n_vis : k_blk;
     const float *row = score + (size_t)t * stride;
@@ -413,7 +417,7 @@ __device__ __forceinline__ void tkc_red_add(uint32_t ra, uint32_t v) {
 
 __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topkc_k(const float *score, int32_t *sel, uint32_t stride,
                                                                uint32_t k_blk, uint32_t ratio, uint32_t pos0,
-                                                               uint32_t width, const int32_t *pp) {
+                                                               uint32_t width, const int32_t *pp, const int32_t *pos_arr) {
     __shared__ uint32_t lhist[4][256];            /* this block's histogram of every pass, zeroed once */
     __shared__ uint32_t ghist[4][256];            /* block 0's copy is the cluster-wide sum, one per pass */
     __shared__ uint32_t cta_cnt[TKC_BLOCKS];      /* (ties << 16 | above) of every block, pushed by its owner */
@@ -421,7 +425,7 @@ __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topkc_k(const float *scor
     __shared__ uint32_t cand[TKC_CAND], cand_n;   /* block 0's copy collects the keys that share the 16-bit prefix */
     const uint32_t t = blockIdx.y, tx = threadIdx.x, lane = tx & 31u, warp = tx >> 5, rank = tkc_rank();
     ix_pdl_sync();
-    const uint32_t pos = (pp ? (uint32_t)*pp : pos0) + t;
+    const uint32_t pos = pos_arr ? (uint32_t)pos_arr[t] : (pp ? (uint32_t)*pp : pos0) + t;
     const uint32_t n_vis = ratio ? (pos + 1u) / ratio : 0u;
     const uint32_t need = n_vis < k_blk ? n_vis : k_blk;
     const float *row = score + (size_t)t * stride;
@@ -573,7 +577,7 @@ __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topkc_k(const float *scor
 
 /* rows that fit the cluster kernel go there, longer ones to the single block */
 bool launch_topk(const float *score, int32_t *sel, uint32_t n_tok, uint32_t stride, uint32_t k_blk, uint32_t ratio,
-                 uint32_t pos0, uint32_t width, const int32_t *pp) {
+                 uint32_t pos0, uint32_t width, const int32_t *pp, const int32_t *pos_arr = nullptr) {
     if (stride <= TKC_MAX_ROW) {
         cudaLaunchConfig_t cfg;
         memset(&cfg, 0, sizeof(cfg));
@@ -589,10 +593,10 @@ bool launch_topk(const float *score, int32_t *sel, uint32_t n_tok, uint32_t stri
         at[0].val.clusterDim.z = 1;
         cfg.attrs = at;
         cfg.numAttrs = ix_pdl() ? 2 : 1;
-        return q4i_check(cudaLaunchKernelEx(&cfg, q4_ix_topkc_k, score, sel, stride, k_blk, ratio, pos0, width, pp),
+        return q4i_check(cudaLaunchKernelEx(&cfg, q4_ix_topkc_k, score, sel, stride, k_blk, ratio, pos0, width, pp, pos_arr),
                          "qsa_topk launch");
     }
-    q4_ix_topk1_k<<<n_tok, IX_TK_THREADS, 0, g_q4.stream>>>(score, sel, stride, k_blk, ratio, pos0, width, pp);
+    q4_ix_topk1_k<<<n_tok, IX_TK_THREADS, 0, g_q4.stream>>>(score, sel, stride, k_blk, ratio, pos0, width, pp, pos_arr);
     return q4i_check(cudaGetLastError(), "qsa_topk launch");
 }
 
@@ -636,4 +640,20 @@ extern "C" bool q4_hip_qsa_topk_d(const float *score, int32_t *sel, uint32_t str
                                   uint32_t width) {
     if (!g_q4.ok || !g_q4.pos_d || !score || !sel || k_blk == 0 || k_blk > IX_MAX_KBLK || width == 0) return false;
     return launch_topk(score, sel, 1, stride, k_blk, ratio, 0, width, g_q4.pos_d);
+}
+
+/* Batched form for concurrent sessions (additive): row t of q / score / sel belongs to session t, which
+ * has its own pool (pools[t], device array of device pointers) and its own position (pos[t], device
+ * array); scoring and selection of all sessions in two launches.  Every session must have at most
+ * `stride` visible blocks.  Same arithmetic and the same lists as one q4_hip_qsa_score_d +
+ * q4_hip_qsa_topk_d pair per session. */
+extern "C" bool q4_gpu_qsa_select_batch(const float *const *pools, const int32_t *pos, const float *q, float *score,
+                                        int32_t *sel, uint32_t n_sess, uint32_t stride, uint32_t n_head, uint32_t hd,
+                                        uint32_t k_blk, uint32_t ratio, uint32_t width) {
+    if (!g_q4.ok) return q4i_fail(Q4E_INIT, "qsa_select_batch: library not initialised");
+    Q4_REQUIRE(pools && pos && q && score && sel && n_sess && stride && ratio && width, "qsa_select_batch: bad argument");
+    Q4_REQUIRE(hd == IX_HD && n_head >= 1 && n_head <= 4 && k_blk >= 1 && k_blk <= IX_MAX_KBLK,
+               "qsa_select_batch: unsupported shape");
+    return score_launch(q, nullptr, score, n_sess, 0, stride, n_head, 0, ratio, nullptr, pools, pos) &&
+           launch_topk(score, sel, n_sess, stride, k_blk, ratio, 0, width, nullptr, pos);
 }

@@ -69,6 +69,7 @@ SIGNATURES = {
     "q4_hip_qsa_score_d": (_b, [_v, _v, _v, _u32, _u32, _u32, _u32]),
     "q4_hip_qsa_topk": (_b, [_v, _v, _u32, _u32, _u32, _u32, _u32, _u32, _u32]),
     "q4_hip_qsa_topk_d": (_b, [_v, _v, _u32, _u32, _u32, _u32]),
+    "q4_gpu_qsa_select_batch": (_b, [_v, _v, _v, _v, _v, _u32, _u32, _u32, _u32, _u32, _u32, _u32]),
     "q4_gpu_xchg_create": (_v, [_u32, _u32, _u32, _u32, _u32]), "q4_gpu_xchg_destroy": (None, [_v]),
     "q4_gpu_xchg_handle": (_b, [_v, _v]), "q4_gpu_xchg_window": (_v, [_v]),
     "q4_gpu_xchg_attach": (_b, [_v, _u32, _v]), "q4_gpu_xchg_attach_ptr": (_b, [_v, _u32, _v]),

@@ -128,6 +128,39 @@ def test_device_position_forms_feed_the_sparse_decode(oracle):
     assert L.q4_gpu_last_error() == 0
 
 
+def test_batched_sessions_select_like_single_sessions(oracle):
+    """q4_gpu_qsa_select_batch: every session has its own pool and position; scores bit-equal and lists
+    equal to the oracle's per-session result (short rows, the dense-prefix case and a long row together)"""
+    L = lib()
+    n_head, width, k_blk = 4, 2051, 512
+    positions = [4098, 99, 70001, 2050, 20000]          # 99 and 2050: every block fits (dense prefix)
+    stride = max(p + 1 for p in positions) // RATIO + 3
+    rng = np.random.default_rng(77)
+    pools, d_pools, want_sc, want_sel = [], [], [], []
+    q = rng.standard_normal((len(positions), n_head, 128)).astype(np.float32)
+    for s_i, pos in enumerate(positions):
+        nb = (pos + 1) // RATIO
+        pool = rng.standard_normal((max(nb, 1), 128)).astype(np.float32)
+        d_pools.append(dev(pool))
+        sc = oracle.ix_score(q[s_i:s_i + 1], pool, 1, nb, stride, n_head, pos, RATIO)
+        want_sc.append(sc)
+        want_sel.append(oracle.ix_topk(sc, 1, stride, k_blk, RATIO, pos, width))
+    ptrs = torch.tensor([t.data_ptr() for t in d_pools], dtype=torch.int64, device="cuda")
+    d_pos = torch.tensor(positions, dtype=torch.int32, device="cuda")
+    d_score = torch.zeros(len(positions), stride, device="cuda")
+    d_sel = torch.zeros(len(positions), width, dtype=torch.int32, device="cuda")
+    assert L.q4_gpu_qsa_select_batch(ptrs.data_ptr(), d_pos.data_ptr(), dev(q).data_ptr(), d_score.data_ptr(),
+                                     d_sel.data_ptr(), len(positions), stride, n_head, 128, k_blk, RATIO, width)
+    got_sc, got_sel = host(d_score), host(d_sel)
+    for s_i, pos in enumerate(positions):
+        nb = (pos + 1) // RATIO
+        assert np.array_equal(got_sc[s_i, :nb].view(np.uint32), want_sc[s_i][0, :nb].view(np.uint32)), s_i
+        assert np.array_equal(got_sel[s_i], want_sel[s_i][0]), s_i
+    assert not L.q4_gpu_qsa_select_batch(None, d_pos.data_ptr(), dev(q).data_ptr(), d_score.data_ptr(), d_sel.data_ptr(),
+                                         len(positions), stride, n_head, 128, k_blk, RATIO, width)
+    L.q4_gpu_last_error()
+
+
 def test_argument_checks():
     L = lib()
     z = torch.zeros(256, device="cuda")
