@@ -424,6 +424,13 @@ __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topkc_k(const float *scor
     __shared__ uint32_t warp_tot[33], st_prefix, st_hi, st_cnt;
     __shared__ uint32_t cand[TKC_CAND], cand_n;   /* block 0's copy collects the keys that share the 16-bit prefix */
     const uint32_t t = blockIdx.y, tx = threadIdx.x, lane = tx & 31u, warp = tx >> 5, rank = tkc_rank();
+    /* The block's own shared memory is prepared, and the cluster has met once, before the launch waits for
+     * the previous kernel: with programmatic dependent launch this part runs under that kernel's tail. */
+    (&lhist[0][0])[tx] = 0u;                      /* 4 x 256 words, one per thread */
+    if (rank == 0) (&ghist[0][0])[tx] = 0u;
+    static_assert(IX_TK_THREADS == 4 * 256, "one histogram word per thread");
+    if (tx == 0) { st_prefix = 0u; st_hi = 0u; cand_n = 0u; }
+    tkc_sync();   /* block 0's sums are zero before anyone adds to them */
     ix_pdl_sync();
     const uint32_t pos = pos_arr ? (uint32_t)pos_arr[t] : (pp ? (uint32_t)*pp : pos0) + t;
     const uint32_t n_vis = ratio ? (pos + 1u) / ratio : 0u;
@@ -443,17 +450,12 @@ __global__ void __launch_bounds__(IX_TK_THREADS) q4_ix_topkc_k(const float *scor
         const uint32_t b = base + 32u * i;
         key[i] = b < n_vis ? ix_key(__ldcg(row + b)) : 0u;
     }
-    (&lhist[0][0])[tx] = 0u;                      /* 4 x 256 words, one per thread */
-    if (rank == 0) (&ghist[0][0])[tx] = 0u;
-    static_assert(IX_TK_THREADS == 4 * 256, "one histogram word per thread");
-    if (tx == 0) { st_prefix = 0u; st_hi = 0u; cand_n = 0u; }
     /* the tail of the list (positions behind the last complete block) does not depend on the selection */
     const uint32_t ncs = need * ratio;
     for (uint32_t w = max(w0, ncs) + tx; w < w1; w += IX_TK_THREADS) {
         const uint32_t tail = n_vis * ratio + (w - ncs);
         out[w] = tail <= pos ? (int32_t)tail : -1;
     }
-    tkc_sync();   /* block 0's sums are zero before anyone adds to them */
 
     bool ranked = false;   /* the threshold came from ranking the last candidates, st_cnt holds the count above it */
     for (int p = 0; p < 4; p++) {
