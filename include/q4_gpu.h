@@ -192,6 +192,9 @@ const int32_t *q4_gpu_pos_word(void);
  * so a gathered position is one contiguous, 16-byte aligned read.  fp16 / fp32 kinds: K and V planes
  * of [layer][kv head][max_kv][hd] rows. */
 typedef struct q4_gpu_kv q4_gpu_kv;
+/* Device bytes q4_gpu_kv_create allocates for the K and V planes of such a store (what a placement
+ * planner must reserve): equal to q4_qsa_kv_bytes at hd 128 / 256; q8_0 records at hd 32 / 64 are
+ * padded to 16 bytes (80 instead of 68, 144 instead of 136 per kv head and position). */
 uint64_t q4_gpu_kv_bytes(uint32_t n_layers, uint32_t n_kvh, uint32_t hd, uint32_t max_kv, int kind);
 q4_gpu_kv *q4_gpu_kv_create(uint32_t n_layers, uint32_t n_kvh, uint32_t hd, uint32_t max_kv,
                             int kind);
@@ -222,7 +225,10 @@ bool q4_gpu_kv_import(q4_gpu_kv *kv, uint32_t layer, int which, uint32_t tok0, u
                       const void *src);
 /* Prefix snapshot (the KV part of q4_sess_save / q4_sess_restore, src/q4_fwd.c:2314-2477) as bulk
  * strided copies of rows [0, n_kv) of every plane.  buf is device memory (host = 0) or pinned /
- * pageable host memory (host = 1); snapshot_bytes = n_kv * n_layers * 2 * kv_token_bytes. */
+ * pageable host memory (host = 1).  snapshot_bytes = n_kv * n_layers * n_kvh * bytes per (kv head,
+ * position): 2*hd + hd/8 rounded up to 16 for q8_0 (at hd 128 / 256 that equals the reference's
+ * n_kv * n_layers * 2 * kv_token_bytes; hd 32 / 64 records carry 12 / 8 bytes of padding), else the K and
+ * V rows of hd fp16 / fp32 values. */
 uint64_t q4_gpu_kv_snapshot_bytes(const q4_gpu_kv *kv, uint32_t n_kv);
 bool q4_gpu_kv_save(const q4_gpu_kv *kv, uint32_t n_kv, void *buf, int host);
 bool q4_gpu_kv_restore(q4_gpu_kv *kv, uint32_t n_kv, const void *buf, int host);
@@ -242,8 +248,10 @@ bool q4_gpu_kv_read_fd(q4_gpu_kv *kv, uint32_t n_kv, int fd);
  *  idx      : NULL = dense over [0, n_kv); else `width` int32 positions per list, -1 = skip;
  *             idx_kvh_stride = 0: one list shared by all kv heads (the reference), else the list
  *             of kv head kh starts at idx + kh*idx_kvh_stride (one list per kv head)
- *  n_kv     : rows attended in dense mode, upper bound for positions in indexed mode; 0 = take
- *             (device position word + 1), as the graph-captured reference path does
+ *  n_kv     : rows attended in dense mode; in indexed mode the number of rows written so far: list
+ *             entries >= n_kv are skipped and raise status bit 4 (the store is not cleared when it
+ *             is created, so rows beyond n_kv hold nothing meaningful); 0 = take (device position
+ *             word + 1), as the graph-captured reference path does
  *  out      : [n_head][hd] fp32
  * Replaces q4_hip_qsa_decode_idx / q4_hip_qsa_decode_n for n_tok = 1 (src/q4_fwd.c:738-741,922). */
 bool q4_gpu_kv_decode(const q4_gpu_kv *kv, uint32_t layer, const void *q, int q_bf16,
@@ -322,8 +330,10 @@ q4_gpu_batch *q4_gpu_batch_create(uint32_t max_sessions);
 void q4_gpu_batch_destroy(q4_gpu_batch *b);
 /* Bind session slot s to a store (all stores of a batch share n_layers, n_kvh, hd and kind). */
 bool q4_gpu_batch_bind(q4_gpu_batch *b, uint32_t slot, q4_gpu_kv *kv);
-/* Publish every session's decode position (host array of n_sessions int32), stream-ordered like
- * q4_hip_pos_push. */
+/* Publish the decode positions of sessions [0, n_sessions) (host array of n_sessions int32),
+ * stream-ordered like q4_hip_pos_push.  n_sessions may be smaller than the number of bound slots: every
+ * later q4_gpu_batch_append / _decode / _append_decode covers exactly these n_sessions sessions (their k,
+ * v, q, gate, out and idx arrays have n_sessions rows) until the next call. */
 bool q4_gpu_batch_set_pos(q4_gpu_batch *b, const int32_t *pos, uint32_t n_sessions);
 /* k, v: [n_sessions][n_kvh*hd] fp32; row s goes to slot pos[s] of session s. */
 bool q4_gpu_batch_append(q4_gpu_batch *b, uint32_t layer, const float *k, const float *v);

@@ -63,10 +63,10 @@ struct DecParams {
     uint32_t width, idx_kvh_stride, idx_unit_stride;
     const int32_t *pos;
     uint32_t kv_base;
+    uint32_t idx_bound_nkv;   /* 1: list entries must be below the rows written so far (newest + 1), else below max_kv */
     float scale_log2e;
     uint32_t S;
     uint32_t cluster; /* blocks per cluster (0 = none): the S splits of a unit form one cluster and merge through DSMEM */
-    uint32_t debug;   /* experiment builds (Q4_DEC_TIMING) only: 1 = copy the tiles but skip the arithmetic */
     float *scratch;
     uint32_t *counters;
     uint32_t *err;
@@ -108,7 +108,28 @@ __device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void *gsrc, 
     else
         asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(smem_dst), "r"(0u) : "memory");
 }
+/* The K and the V chunk of one record (V codes follow the K codes at +HD in the native q8_0 record) into
+ * the K tile and, 2048 bytes further, the V tile of a ring stage; nothing is copied for a padding position. */
+template <int HD>
+__device__ __forceinline__ void cp_async16_kv(uint32_t smem_dst, const void *gsrc, int32_t pos) {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\tsetp.ge.s32 q, %2, 0;\n\t"
+        "@q cp.async.cg.shared.global [%0], [%1], 16;\n\t"
+        "@q cp.async.cg.shared.global [%0+2048], [%1+%3], 16;\n\t}"
+        ::"r"(smem_dst), "l"(gsrc), "r"(pos), "n"(HD) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+/* four 8x8 matrices of 16-bit elements (eight 16-byte rows each; lanes 8i..8i+7 give the row addresses of
+ * matrix i); thread (g, t) receives elements 2t, 2t+1 of row g of every matrix -- of the transposed
+ * matrix with .trans, i.e. element g of rows 2t and 2t+1 */
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t saddr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t saddr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr) : "memory");
+}
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ uint32_t lds32(uint32_t a) {
@@ -127,6 +148,14 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
         "{%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+/* same product with the initial accumulator in registers of its own: rows g and g+8 start from (c0, c1) */
+__device__ __forceinline__ void mma16816_from(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1, float c0, float c1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%11,%10,%11};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1));
 }
 __device__ __forceinline__ uint32_t movmatrix_t(uint32_t x) {
     uint32_t y;
@@ -171,10 +200,11 @@ __device__ __forceinline__ float warp_sum_over_g(float v) {
 }
 
 /* Which head dimension the accumulator pair (c0,c1) / (c2,c3) of output tile mt holds for lane
- * group g.  q8 layouts interleave so that each tile stays inside one 32-wide scale block. */
-template <int LAY>
+ * group g.  The register-direct q8 paths interleave so that each tile stays inside one 32-wide scale
+ * block; the staged path (fragments through ldmatrix) and the fp16 / fp32 rows use plain 16-dim tiles. */
+template <int LAY, bool STAGED>
 __device__ __forceinline__ int out_dim(int mt, int g, int hi) {
-    if (LAY == LAY_Q8P || LAY == LAY_Q8R) return 32 * (mt >> 1) + 4 * g + 2 * (mt & 1) + hi;
+    if ((LAY == LAY_Q8P || LAY == LAY_Q8R) && !STAGED) return 32 * (mt >> 1) + 4 * g + 2 * (mt & 1) + hi;
     return 16 * mt + 2 * g + hi;
 }
 /* Which 4 head dimensions lane t feeds to k-step ks of the QK product (same map for Q and K). */
@@ -641,31 +671,6 @@ __global__ void __launch_bounds__(DEC_THREADS) q4_xchg_merge_k(const Q4XchgDev *
     xchg_wait_merge<HD, HEADS>(xd, unit, __ldcg(&xd->win[xd->rank]->epoch[unit]), mo, err);
 }
 
-#ifdef Q4_DEC_TIMING
-/* experiment builds only: per-block time stamps {globaltimer at start, then SM cycles since start at
- * first data, end of the position loop, block record merged, exit} */
-__device__ unsigned long long q4_dbg_stamps[8192 * 16];
-#define Q4_STAMP(i)                                                                                   \
-    do {                                                                                              \
-        if (threadIdx.x == 0) {                                                                       \
-            const uint32_t bid_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);     \
-            if (bid_ < 8192) q4_dbg_stamps[bid_ * 16 + (i)] = (i) == 0 ? global_ns() : (unsigned long long)(clock64() - dbg_c0_); \
-        }                                                                                             \
-    } while (0)
-/* same, but not before the value `dep` is in a register */
-#define Q4_STAMP_DEP(i, dep)                                                                          \
-    do {                                                                                              \
-        long long c_;                                                                                 \
-        asm volatile("mov.u64 %0, %%clock64;" : "=l"(c_) : "r"((uint32_t)(dep)) : "memory");          \
-        if (threadIdx.x == 0) {                                                                       \
-            const uint32_t bid_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);     \
-            if (bid_ < 8192) q4_dbg_stamps[bid_ * 16 + (i)] = (unsigned long long)(c_ - dbg_c0_);     \
-        }                                                                                             \
-    } while (0)
-#else
-#define Q4_STAMP(i) do { } while (0)
-#define Q4_STAMP_DEP(i, dep) do { } while (0)
-#endif
 
 /* ---- the kernel ---------------------------------------------------------------------------- */
 constexpr int RING_STAGES = 4;
@@ -697,21 +702,16 @@ q4_decode_k(const DecParams P) {
     constexpr int NBQ = Q8 ? NB : 1;
 
     extern __shared__ __align__(16) uint8_t smem_raw[];
-#ifdef Q4_DEC_TIMING
-    const long long dbg_c0_ = clock64();
-    if (threadIdx.x == 0) {
-        const uint32_t bid_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
-        uint32_t smid_;
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid_));
-        if (bid_ < 8192) q4_dbg_stamps[bid_ * 16 + 7] = smid_;
-    }
-#endif
-    Q4_STAMP(0);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const uint32_t split = blockIdx.x, kh = blockIdx.y, u = blockIdx.z;
     const uint32_t S = P.S;
 
     const Q4Cache C = P.many ? P.many[u] : P.one;
+    /* The blocks of a cluster write into one another's shared memory at the end (push merge).  A block's
+     * shared memory may be accessed remotely only once that block runs, so every block announces itself here
+     * and waits for its peers' announcements just before its first remote access: by then they have all
+     * arrived long ago and the wait costs nothing. */
+    if (P.cluster) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
     /* Programmatic dependent launch: the blocks of this launch may already be resident while the previous
      * kernel of the stream drains.  Only the cache view above (written when the store was created or bound)
      * is read before this point; positions, lists, queries and rows are read after it. */
@@ -739,6 +739,9 @@ q4_decode_k(const DecParams P) {
         sbase = C.s + (uint64_t)P.layer * C.s_layer_stride + (uint64_t)kh * C.s_kvh_stride;
     const uint32_t tok_stride = C.tok_stride, s_tok_stride = C.s_tok_stride;
     const uint32_t max_kv = C.max_kv;
+    /* list entries at or beyond this are skipped and raise the range status: the rows written so far for a
+     * store (rows behind them hold nothing), the capacity for a caller-owned cache of the reference ABI */
+    const uint32_t bound = P.idx_bound_nkv ? n_kv : max_kv;
 
     /* ---- fused append, first half: the load of the unit's new K/V row is issued here, next to the
      * loads of the list entries below, so that the two round trips overlap; the row is quantised and
@@ -767,7 +770,7 @@ q4_decode_k(const DecParams P) {
         if (j >= n_pos) return -1;
         if (!list) return (int32_t)j;
         int32_t p = list[j];
-        if (p >= (int32_t)max_kv) {
+        if (p >= (int32_t)bound) {
             atomicOr(P.err, (uint32_t)Q4E_RANGE);
             p = -1;
         }
@@ -963,97 +966,87 @@ q4_decode_k(const DecParams P) {
     };
 
     if constexpr (Cfg::STAGED) {
-        /* ---- native q8_0 store, hd 128: per-warp cp.async ring of 16-position stages; an iteration consumes
-         * two stages (32 positions, two independent MMA chains) while the next two are in flight.
-         * Lanes 0-15 hold a stage's positions and copy its 16-byte scale rows; the K and V rows are
-         * copied 4 rows per instruction (8 lanes x 16 bytes = one 128-byte line per row).  16-byte chunk
-         * c of row r lands at chunk c ^ ((r & 3) << 1) in the K tile and c ^ (((r >> 1) & 3) << 1) in the
-         * V tile, which makes the 8-byte K reads (rows g) and the 4-byte V reads (rows 2t..) below hit
-         * 32 distinct banks.  Padding positions are zero-filled (cp.async with 0 source bytes): their
-         * scales are 0, so they add nothing to P.V, and their scores are masked to -inf. */
+        /* ---- native q8_0 store, hd 128: every warp owns a ring of RING_STAGES 16-position stages that it
+         * fills with 16-byte cp.async copies gathered by position.  Per tile the warp waits for the oldest
+         * stage, moves the whole tile into registers as MMA fragments (ldmatrix for the K rows, transposing
+         * ldmatrix for the V rows, the scale rows and the mask of live positions), refills the stage at once
+         * with the tile RING_STAGES ahead, and only then does the arithmetic: all stages but the one being
+         * unloaded are in flight all the time.  There is no block barrier in the loop.
+         * Stage = K tile (16 rows x 128 B) | V tile | 16 scale rows of 16 B | mask word.  16-byte chunk c of
+         * row r lies at chunk c ^ (r & 7) of its row in both tiles, so the eight row addresses of one 8x8
+         * ldmatrix block hit eight different bank groups.  Padding positions copy nothing: their scale row is
+         * zeroed (so they add nothing to P.V whatever the stale code bytes are) and their scores are masked. */
         const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem_raw) +
                               (uint32_t)warp * RING_STAGES * RING_STAGE_BYTES;
         const uint32_t n_my = s_begin + warp < s_end ? (s_end - s_begin - warp + DEC_WARPS - 1u) / DEC_WARPS : 0u;
-        const uint32_t n_even = (n_my + 1u) & ~1u;
         const uint32_t r16 = lane & 15, c8 = lane & 7;
-        uint32_t koff[4], voff[4];
+        uint32_t coff[4];   /* copy destination of row 4j + lane / 8, chunk lane % 8 */
 #pragma unroll
         for (uint32_t j = 0; j < 4; j++) {
             const uint32_t row = 4 * j + (lane >> 3);
-            koff[j] = row * 128 + ((c8 ^ ((row & 3) << 1)) << 4);
-            voff[j] = 2048 + row * 128 + ((c8 ^ (((row >> 1) & 3) << 1)) << 4);
+            coff[j] = row * 128 + ((c8 ^ (row & 7)) << 4);
         }
-        /* The list entry is only loaded here; its range check waits until issue() needs the value one
-         * or two iterations later, so the load latency stays off the critical path. */
+        /* ldmatrix row address of this lane for block b: matrix lane / 8 = rows 8 * (that & 1) .., chunk 2b + lane / 16 */
+        uint32_t moff[NB];
+#pragma unroll
+        for (int b = 0; b < NB; b++)
+            moff[b] = (uint32_t)((lane & 7) + ((lane >> 3) & 1) * 8) * 128 + (((uint32_t)(2 * b + (lane >> 4)) ^ (uint32_t)(lane & 7)) << 4);
+
+        /* The list entry is only loaded here; its range check waits until issue() needs the value, several
+         * tiles later, so the load latency stays off the critical path. */
         auto my_pos = [&](uint32_t it) -> int32_t {
             const uint32_t j = ((s_begin + warp + it * DEC_WARPS) << 4) + r16;
             if (it >= n_my || j >= n_pos) return -1;
             return list ? list[j] : (int32_t)j;
         };
         auto issue = [&](uint32_t it, int32_t p) {
-            if (it < n_even) {
-                if (p >= (int32_t)max_kv) {
+            if (it < n_my) {
+                if (p >= (int32_t)bound) {
                     atomicOr(P.err, (uint32_t)Q4E_RANGE);
                     p = -1;
                 }
                 const uint32_t st = ring + (it % RING_STAGES) * RING_STAGE_BYTES;
+                const uint32_t livemask = __ballot_sync(0xffffffffu, p >= 0);
 #pragma unroll
                 for (uint32_t j = 0; j < 4; j++) {
                     const int32_t pr = __shfl_sync(0xffffffffu, p, 4 * j + (lane >> 3));
-                    const uint64_t off = (uint64_t)(uint32_t)max(pr, 0) * tok_stride + c8 * 16;
-                    cp_async16(st + koff[j], kbase + off, pr >= 0);
-                    cp_async16(st + voff[j], vbase + off, pr >= 0);
+                    cp_async16_kv<HD>(st + coff[j], kbase + (uint64_t)(uint32_t)max(pr, 0) * tok_stride + c8 * 16, pr);
                 }
-                if (lane < 16) {
-                    cp_async16(st + 4096 + r16 * 16, sbase + (uint64_t)(uint32_t)max(p, 0) * s_tok_stride, p >= 0);
-                    asm volatile("st.shared.s32 [%0], %1;" ::"r"(st + 4352 + r16 * 4), "r"(p) : "memory");
-                }
+                if (lane < 16)
+                    cp_async16(st + 4096 + r16 * 16, kbase + (uint64_t)(uint32_t)max(p, 0) * tok_stride + 2 * HD, p >= 0);
+                if (lane == 0) asm volatile("st.shared.u32 [%0], %1;" ::"r"(st + 4352), "r"(livemask) : "memory");
             }
-            cp_async_commit();   /* one group per stage, empty or not, keeps the wait count uniform */
+            cp_async_commit();   /* one group per tile, empty or not, keeps the wait count uniform */
         };
-        int32_t pa = my_pos(0), pb = my_pos(1), pc = my_pos(2), pd = my_pos(3), pe = my_pos(4), pf = my_pos(5);
-        /* ---- fused append, second half: every split of the unit quantises and stores the unit's newest
-         * row (identical bytes), before any row is read: a block's own stores are ordered before its later
-         * reads by the barrier, so no split depends on another block having written. */
+        int32_t pa = my_pos(0), pb = my_pos(1), pc = my_pos(2), pd = my_pos(3);
+        int32_t pn0 = my_pos(4), pn1 = my_pos(5), pn2 = my_pos(6);
+        /* ---- fused append, second half.  Every split of the unit quantises and stores the unit's newest row
+         * (identical bytes from every split, so no block depends on another having written); a block's own
+         * store is ordered before its later reads by the barrier.  A warp whose first tiles do not name the
+         * newest row fills its ring before that, so the append runs under the first copies. */
+        bool hold = false;
+        if (P.new_k) {
+            const int32_t nw = (int32_t)newest;
+            hold = __any_sync(0xffffffffu, pa == nw || pb == nw || pc == nw || pd == nw);
+        }
+        if (!hold) { issue(0, pa); issue(1, pb); issue(2, pc); issue(3, pd); }
         if (P.new_k) {
             float d, id;
             q4d_block_scale(ap_x, d, id);
             if (ap_live) {
-                uint8_t *row = const_cast<uint8_t *>(ap_which ? vbase : kbase) + (uint64_t)newest * tok_stride;
-                *reinterpret_cast<uint32_t *>(row + ap_b * 32 + ap_sub * 4) = q4d_quant4(ap_x, id);
-                if (ap_sub == 0)
-                    reinterpret_cast<__half *>(const_cast<uint8_t *>(sbase) + (uint64_t)newest * s_tok_stride)[(ap_which ? NB : 0) + ap_b] =
-                        __float2half_rn(d);
+                uint8_t *row = const_cast<uint8_t *>(kbase) + (uint64_t)newest * tok_stride;
+                *reinterpret_cast<uint32_t *>(row + (ap_which ? HD : 0) + ap_b * 32 + ap_sub * 4) = q4d_quant4(ap_x, id);
+                if (ap_sub == 0) reinterpret_cast<__half *>(row + 2 * HD)[(ap_which ? NB : 0) + ap_b] = __float2half_rn(d);
             }
             if (newest >= max_kv && threadIdx.x == 0) atomicOr(P.err, (uint32_t)Q4E_RANGE);
             __syncthreads();
         }
-        Q4_STAMP_DEP(8, max_kv);
-        Q4_STAMP_DEP(9, pa | pb);
-        Q4_STAMP(12);
-        issue(0, pa);
-        Q4_STAMP(13);
-        issue(1, pb);
-        Q4_STAMP(10);
-        /* A warp with at most four tiles (the single-session decode, small batches) fills the whole ring
-         * before the queries are prepared: its list is then entirely in flight after one round of list
-         * loads.  With more tiles per warp that doubles the burst at the start of the kernel and costs
-         * more than it saves (measured at 64 sessions), so there the second pair waits for the loop. */
-        uint32_t next = 2;                   /* next tile to issue */
-        if (n_even <= 4) {
-            issue(2, pc);
-            issue(3, pd);
-            next = 4;
-            pa = pe; pb = pf;
-            pc = my_pos(6); pd = my_pos(7);
-        } else {
-            pa = pc; pb = pd;                /* the stages the first iteration issues */
-            pc = pe; pd = pf;                /* the ones after: list entries are fetched two iterations ahead */
-        }
+        if (hold) { issue(0, pa); issue(1, pb); issue(2, pc); issue(3, pd); }
 
-        /* Q fragments with scale * log2(e) folded in, rounded to fp16 once; and, per 32-wide block,
-         * -1152 * sum(q): K codes enter the MMA as the fp16 numbers 1152 + code (one byte permute per
-         * pair, no subtract), so each block's partial product starts from that correction. */
+        /* Q fragments with scale * log2(e) folded in, rounded to fp16 once: lane (g, t) holds dims 16ks + 4t ..
+         * + 3 of head nt*8 + g, the columns the K fragments below carry in k-slots 2t, 2t+1, 2t+8, 2t+9.  And,
+         * per 32-wide block, -1152 * sum(q): K codes enter the MMA as the fp16 numbers 1152 + code (one byte
+         * permute per pair, no subtract), so each block's partial product starts from that correction. */
         uint32_t qs[NHT][KS][2];
         float qcorr[NHT][NB][2];
 #pragma unroll
@@ -1066,7 +1059,7 @@ q4_decode_k(const DecParams P) {
             for (int ks = 0; ks < KS; ks++) {
                 float x0 = 0.f, x1 = 0.f, x2 = 0.f, x3 = 0.f;
                 if (live) {
-                    const int d = qk_dim<LAY>(ks, t);
+                    const int d = 16 * ks + 4 * t;
                     if (P.q_bf16) {
                         const uint2 w = *reinterpret_cast<const uint2 *>(
                             reinterpret_cast<const __nv_bfloat16 *>(P.q) + qoff + d);
@@ -1097,108 +1090,93 @@ q4_decode_k(const DecParams P) {
             }
         }
 
-        Q4_STAMP_DEP(11, qs[0][0][0]);
-        for (uint32_t it = 0; it < n_even; it += 2) {
-            if (next == it + 2) {                    /* refill the two stages the previous iteration consumed */
-                issue(next, pa);
-                issue(next + 1, pb);
-                next += 2;
-                pa = pc; pb = pd;
-                pc = my_pos(next + 2);               /* consumed by the issue two iterations from now */
-                pd = my_pos(next + 3);
-            }
-            cp_async_wait<2>();                  /* all but the two newest stages have landed */
+        for (uint32_t it = 0; it < n_my; it++) {
+            cp_async_wait<RING_STAGES - 1>();    /* all but the newest RING_STAGES - 1 tiles have landed: tile `it` is in */
             __syncwarp();
-#ifdef Q4_DEC_TIMING
-            if (it == 0) Q4_STAMP(1);
-#endif
-            uint32_t st[2];
-            st[0] = ring + (it % RING_STAGES) * RING_STAGE_BYTES;
-            st[1] = ring + ((it + 1) % RING_STAGES) * RING_STAGE_BYTES;
-#ifdef Q4_DEC_TIMING
-            if (P.debug) {   /* experiment builds only: copy the tiles but skip the arithmetic */
-                acc[0][0][0] += __uint_as_float(lds32(st[0] + 4 * lane) ^ lds32(st[1] + 2048 + 4 * lane));
-                __syncwarp();
-                continue;
-            }
-#endif
+            const uint32_t st = ring + (it % RING_STAGES) * RING_STAGE_BYTES;
+            /* ---- the tile into registers.  K: matrix i of block b = rows 8 (i & 1).., 16 dims from 32b + 16 (i >> 1):
+             * kf[b][i] = position g (+8 for odd i), 4 codes of dims 32b + 16 (i >> 1) + 4t.  V, transposed:
+             * vf[b][i] = positions 2t, 2t+1 (+8 for odd i), 2 codes each of dims 32b + 16 (i >> 1) + 2g, + 1. */
+            uint32_t kf[NB][4], vf[NB][4];
+#pragma unroll
+            for (int b = 0; b < NB; b++) ldmatrix_x4(kf[b], st + moff[b]);
+#pragma unroll
+            for (int b = 0; b < NB; b++) ldmatrix_x4_trans(vf[b], st + 2048 + moff[b]);
+            const uint2 ks0 = lds64(st + 4096 + g * 16), ks1 = lds64(st + 4096 + (g + 8) * 16);
+            uint2 vs[4];
+#pragma unroll
+            for (int r = 0; r < 4; r++) vs[r] = lds64(st + 4096 + (2 * t + (r & 1) + 8 * (r >> 1)) * 16 + 8);
+            const uint32_t livemask = lds32(st + 4352);
+            /* codes to offset binary: (code ^ 0x80) under the exponent byte 0x64 is the fp16 number 1152 + code */
+#pragma unroll
+            for (int b = 0; b < NB; b++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    kf[b][i] ^= 0x80808080u;
+                    vf[b][i] ^= 0x80808080u;
+                }
+            __syncwarp();                        /* every lane has unloaded the stage */
+            issue(it + RING_STAGES, pn0);        /* refill it with the tile RING_STAGES ahead */
+            pn0 = pn1; pn1 = pn2;
+            pn2 = my_pos(it + RING_STAGES + 3);
 
-            /* ---- S^T = K . Q^T for both tiles */
-            float sc[2][NHT][4];
-            bool kok[2][2];
+            /* ---- S^T = K . Q^T */
+            const bool kok0 = (livemask >> g) & 1u, kok1 = (livemask >> (g + 8)) & 1u;
+            float ksc[2][NB];
+            {
+                const float2 a01 = __half22float2(u2h(ks0.x)), a23 = __half22float2(u2h(ks0.y));
+                const float2 b01 = __half22float2(u2h(ks1.x)), b23 = __half22float2(u2h(ks1.y));
+                ksc[0][0] = a01.x; ksc[0][1] = a01.y; ksc[0][2] = a23.x; ksc[0][3] = a23.y;
+                ksc[1][0] = b01.x; ksc[1][1] = b01.y; ksc[1][2] = b23.x; ksc[1][3] = b23.y;
+            }
+            float sc[NHT][4];
 #pragma unroll
-            for (int ti = 0; ti < 2; ti++) {
-                kok[ti][0] = (int32_t)lds32(st[ti] + 4352 + 4 * g) >= 0;
-                kok[ti][1] = (int32_t)lds32(st[ti] + 4352 + 4 * (g + 8)) >= 0;
-                float ksc[2][NB];
+            for (int nt = 0; nt < NHT; nt++) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
 #pragma unroll
-                for (int r = 0; r < 2; r++) {
-                    const uint2 w = lds64(st[ti] + 4096 + (g + 8 * r) * 16);
-                    const float2 f01 = __half22float2(u2h(w.x)), f23 = __half22float2(u2h(w.y));
-                    ksc[r][0] = f01.x; ksc[r][1] = f01.y; ksc[r][2] = f23.x; ksc[r][3] = f23.y;
+            for (int b = 0; b < NB; b++) {
+                float cb[NHT][4];
+                {
+                    const uint32_t a0 = __byte_perm(kf[b][0], 0x64646464u, 0x4140), a2 = __byte_perm(kf[b][0], 0x64646464u, 0x4342);
+                    const uint32_t a1 = __byte_perm(kf[b][1], 0x64646464u, 0x4140), a3 = __byte_perm(kf[b][1], 0x64646464u, 0x4342);
+#pragma unroll
+                    for (int nt = 0; nt < NHT; nt++)
+                        mma16816_from(cb[nt], a0, a1, a2, a3, qs[nt][2 * b][0], qs[nt][2 * b][1], qcorr[nt][b][0], qcorr[nt][b][1]);
+                }
+                {
+                    const uint32_t a0 = __byte_perm(kf[b][2], 0x64646464u, 0x4140), a2 = __byte_perm(kf[b][2], 0x64646464u, 0x4342);
+                    const uint32_t a1 = __byte_perm(kf[b][3], 0x64646464u, 0x4140), a3 = __byte_perm(kf[b][3], 0x64646464u, 0x4342);
+#pragma unroll
+                    for (int nt = 0; nt < NHT; nt++)
+                        mma16816(cb[nt], a0, a1, a2, a3, qs[nt][2 * b + 1][0], qs[nt][2 * b + 1][1]);
                 }
 #pragma unroll
-                for (int nt = 0; nt < NHT; nt++) sc[ti][nt][0] = sc[ti][nt][1] = sc[ti][nt][2] = sc[ti][nt][3] = 0.f;
-#pragma unroll
-                for (int b = 0; b < NB; b++) {
-                    const uint32_t ko = (((2 * b + (t >> 1)) ^ ((g & 3) << 1)) << 4) + 8 * (t & 1);
-                    const uint2 w0 = lds64(st[ti] + g * 128 + ko);
-                    const uint2 w1 = lds64(st[ti] + (g + 8) * 128 + ko);
-                    float cb[NHT][4];
-#pragma unroll
-                    for (int nt = 0; nt < NHT; nt++) {
-                        cb[nt][0] = cb[nt][2] = qcorr[nt][b][0];
-                        cb[nt][1] = cb[nt][3] = qcorr[nt][b][1];
-                    }
-#pragma unroll
-                    for (int jj = 0; jj < 2; jj++) {
-                        const uint32_t x0 = (jj ? w0.y : w0.x) ^ 0x80808080u, x1 = (jj ? w1.y : w1.x) ^ 0x80808080u;
-                        const uint32_t a0 = __byte_perm(x0, 0x64646464u, 0x4140), a2 = __byte_perm(x0, 0x64646464u, 0x4342);
-                        const uint32_t a1 = __byte_perm(x1, 0x64646464u, 0x4140), a3 = __byte_perm(x1, 0x64646464u, 0x4342);
-#pragma unroll
-                        for (int nt = 0; nt < NHT; nt++)
-                            mma16816(cb[nt], a0, a1, a2, a3, qs[nt][2 * b + jj][0], qs[nt][2 * b + jj][1]);
-                    }
-#pragma unroll
-                    for (int nt = 0; nt < NHT; nt++) {
-                        sc[ti][nt][0] = fmaf(ksc[0][b], cb[nt][0], sc[ti][nt][0]);
-                        sc[ti][nt][1] = fmaf(ksc[0][b], cb[nt][1], sc[ti][nt][1]);
-                        sc[ti][nt][2] = fmaf(ksc[1][b], cb[nt][2], sc[ti][nt][2]);
-                        sc[ti][nt][3] = fmaf(ksc[1][b], cb[nt][3], sc[ti][nt][3]);
-                    }
+                for (int nt = 0; nt < NHT; nt++) {
+                    sc[nt][0] = fmaf(ksc[0][b], cb[nt][0], sc[nt][0]);
+                    sc[nt][1] = fmaf(ksc[0][b], cb[nt][1], sc[nt][1]);
+                    sc[nt][2] = fmaf(ksc[1][b], cb[nt][2], sc[nt][2]);
+                    sc[nt][3] = fmaf(ksc[1][b], cb[nt][3], sc[nt][3]);
                 }
             }
 
-            /* ---- online softmax over the 32 positions; lanes (g, t): positions g / g+8, heads 2t, 2t+1 */
-            uint32_t pb0[2][NHT], pb1[2][NHT];
+            /* ---- online softmax; lanes (g, t) hold positions g / g+8 for heads 2t, 2t+1 */
+            uint32_t pb0[NHT], pb1[NHT];
 #pragma unroll
             for (int nt = 0; nt < NHT; nt++) {
-#pragma unroll
-                for (int ti = 0; ti < 2; ti++) {
-                    if (!kok[ti][0]) sc[ti][nt][0] = sc[ti][nt][1] = -CUDART_INF_F;
-                    if (!kok[ti][1]) sc[ti][nt][2] = sc[ti][nt][3] = -CUDART_INF_F;
-                }
-                const float mx0 = warp_max_over_g(fmaxf(fmaxf(sc[0][nt][0], sc[0][nt][2]), fmaxf(sc[1][nt][0], sc[1][nt][2])));
-                const float mx1 = warp_max_over_g(fmaxf(fmaxf(sc[0][nt][1], sc[0][nt][3]), fmaxf(sc[1][nt][1], sc[1][nt][3])));
+                if (!kok0) sc[nt][0] = sc[nt][1] = -CUDART_INF_F;
+                if (!kok1) sc[nt][2] = sc[nt][3] = -CUDART_INF_F;
+                const float mx0 = warp_max_over_g(fmaxf(sc[nt][0], sc[nt][2]));
+                const float mx1 = warp_max_over_g(fmaxf(sc[nt][1], sc[nt][3]));
                 const float mn0 = fmaxf(m_run[nt][0], mx0), mn1 = fmaxf(m_run[nt][1], mx1);
                 const float mu0 = mn0 == -CUDART_INF_F ? 0.f : mn0;
                 const float mu1 = mn1 == -CUDART_INF_F ? 0.f : mn1;
                 const float al0 = ex2(m_run[nt][0] - mu0), al1 = ex2(m_run[nt][1] - mu1);
                 m_run[nt][0] = mn0;
                 m_run[nt][1] = mn1;
-                float ls0 = 0.f, ls1 = 0.f;
-#pragma unroll
-                for (int ti = 0; ti < 2; ti++) {
-                    const __half2 h0 = __floats2half2_rn(ex2(sc[ti][nt][0] - mu0), ex2(sc[ti][nt][1] - mu1));
-                    const __half2 h1 = __floats2half2_rn(ex2(sc[ti][nt][2] - mu0), ex2(sc[ti][nt][3] - mu1));
-                    const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
-                    ls0 += f0.x + f1.x;
-                    ls1 += f0.y + f1.y;
-                    pb0[ti][nt] = movmatrix_t(h2u(h0));   /* {P[pos 2t][head g], P[pos 2t+1][head g]} */
-                    pb1[ti][nt] = movmatrix_t(h2u(h1));   /* positions 2t+8, 2t+9 */
-                }
-                l_run[nt][0] = fmaf(l_run[nt][0], al0, ls0);
-                l_run[nt][1] = fmaf(l_run[nt][1], al1, ls1);
+                const __half2 h0 = __floats2half2_rn(ex2(sc[nt][0] - mu0), ex2(sc[nt][1] - mu1));
+                const __half2 h1 = __floats2half2_rn(ex2(sc[nt][2] - mu0), ex2(sc[nt][3] - mu1));
+                const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+                l_run[nt][0] = fmaf(l_run[nt][0], al0, f0.x + f1.x);
+                l_run[nt][1] = fmaf(l_run[nt][1], al1, f0.y + f1.y);
                 if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
 #pragma unroll
                     for (int mt = 0; mt < MT; mt++) {
@@ -1206,46 +1184,35 @@ q4_decode_k(const DecParams P) {
                         acc[nt][mt][2] *= al0; acc[nt][mt][3] *= al1;
                     }
                 }
+                pb0[nt] = movmatrix_t(h2u(h0));   /* {P[pos 2t][head g], P[pos 2t+1][head g]} */
+                pb1[nt] = movmatrix_t(h2u(h1));   /* positions 2t+8, 2t+9 */
             }
 
-            /* ---- O^T += V^T . P^T, tile after tile on the same accumulators, 8 independent chains */
+            /* ---- O^T += V^T . P^T: tile mt = 16 dims, row g = dim 16mt + 2g, row g+8 = dim 16mt + 2g + 1 */
 #pragma unroll
-            for (int ti = 0; ti < 2; ti++) {
-                uint2 vs[4];
+            for (int b = 0; b < NB; b++) {
+                /* fp16 scale of block b: halves 0,1 in .x, halves 2,3 in .y */
+                const uint32_t sel = (b & 1) ? 0x7632 : 0x5410;
+                const uint32_t s01 = __byte_perm(b < 2 ? vs[0].x : vs[0].y, b < 2 ? vs[1].x : vs[1].y, sel);
+                const uint32_t s23 = __byte_perm(b < 2 ? vs[2].x : vs[2].y, b < 2 ? vs[3].x : vs[3].y, sel);
+                uint32_t bb0[NHT], bb1[NHT];
 #pragma unroll
-                for (int r = 0; r < 4; r++) vs[r] = lds64(st[ti] + 4096 + (2 * t + (r & 1) + 8 * (r >> 1)) * 16 + 8);
+                for (int nt = 0; nt < NHT; nt++) {
+                    bb0[nt] = h2u(__hmul2(u2h(pb0[nt]), u2h(s01)));
+                    bb1[nt] = h2u(__hmul2(u2h(pb1[nt]), u2h(s23)));
+                }
 #pragma unroll
-                for (int b = 0; b < NB; b++) {
-                    /* fp16 scale of block b: halves 0,1 in .x, halves 2,3 in .y */
-                    const uint32_t sel = (b & 1) ? 0x7632 : 0x5410;
-                    const uint32_t s01 = __byte_perm(b < 2 ? vs[0].x : vs[0].y, b < 2 ? vs[1].x : vs[1].y, sel);
-                    const uint32_t s23 = __byte_perm(b < 2 ? vs[2].x : vs[2].y, b < 2 ? vs[3].x : vs[3].y, sel);
-                    uint32_t bb0[NHT], bb1[NHT];
+                for (int hf = 0; hf < 2; hf++) {
+                    const uint32_t v01 = vf[b][2 * hf], v89 = vf[b][2 * hf + 1];
+                    const uint32_t a0 = magic_sub(__byte_perm(v01, 0x64646464u, 0x4240));
+                    const uint32_t a1 = magic_sub(__byte_perm(v01, 0x64646464u, 0x4341));
+                    const uint32_t a2 = magic_sub(__byte_perm(v89, 0x64646464u, 0x4240));
+                    const uint32_t a3 = magic_sub(__byte_perm(v89, 0x64646464u, 0x4341));
 #pragma unroll
-                    for (int nt = 0; nt < NHT; nt++) {
-                        bb0[nt] = h2u(__hmul2(u2h(pb0[ti][nt]), u2h(s01)));
-                        bb1[nt] = h2u(__hmul2(u2h(pb1[ti][nt]), u2h(s23)));
-                    }
-                    const uint32_t vo = 2048 + (((2 * b + (g >> 2)) ^ (t << 1)) << 4) + 4 * (g & 3);
-                    const uint32_t v0 = lds32(st[ti] + vo + (2 * t) * 128), v1 = lds32(st[ti] + vo + (2 * t + 1) * 128);
-                    const uint32_t v2 = lds32(st[ti] + vo + (2 * t + 8) * 128), v3 = lds32(st[ti] + vo + (2 * t + 9) * 128);
-                    {
-                        const uint32_t a0 = cvt_i8_pair<0>(v0, v1), a1 = cvt_i8_pair<1>(v0, v1);
-                        const uint32_t a2 = cvt_i8_pair<0>(v2, v3), a3 = cvt_i8_pair<1>(v2, v3);
-#pragma unroll
-                        for (int nt = 0; nt < NHT; nt++) mma16816(acc[nt][2 * b], a0, a1, a2, a3, bb0[nt], bb1[nt]);
-                    }
-                    {
-                        const uint32_t a0 = cvt_i8_pair<2>(v0, v1), a1 = cvt_i8_pair<3>(v0, v1);
-                        const uint32_t a2 = cvt_i8_pair<2>(v2, v3), a3 = cvt_i8_pair<3>(v2, v3);
-#pragma unroll
-                        for (int nt = 0; nt < NHT; nt++) mma16816(acc[nt][2 * b + 1], a0, a1, a2, a3, bb0[nt], bb1[nt]);
-                    }
+                    for (int nt = 0; nt < NHT; nt++) mma16816(acc[nt][2 * b + hf], a0, a1, a2, a3, bb0[nt], bb1[nt]);
                 }
             }
-            __syncwarp();   /* every lane is done with both stages before a later issue overwrites them */
         }
-        Q4_STAMP(2);
         cp_async_wait<0>();
         __syncthreads();    /* the epilogue below reuses the ring memory of all warps */
     } else {
@@ -1358,7 +1325,7 @@ q4_decode_k(const DecParams P) {
         }
 #pragma unroll
         for (int mt = 0; mt < MT; mt++) {
-            const int d0 = out_dim<LAY>(mt, g, 0), d1 = out_dim<LAY>(mt, g, 1);
+            const int d0 = out_dim<LAY, Cfg::STAGED>(mt, g, 0), d1 = out_dim<LAY, Cfg::STAGED>(mt, g, 1);
             r0[d0] = acc[nt][mt][0]; r1[d0] = acc[nt][mt][1];
             r0[d1] = acc[nt][mt][2]; r1[d1] = acc[nt][mt][3];
         }
@@ -1381,18 +1348,14 @@ q4_decode_k(const DecParams P) {
     if (P.cluster) {
         float *own = reinterpret_cast<float *>(smem_raw + Cfg::EPI_BYTES);
         merge_records<HD, HEADS>(sm, DEC_WARPS, false, own, mo, mscr);
-        Q4_STAMP(3);
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   /* every peer block has started (arrive at entry) */
         if (P.push_bytes) {
             cluster_push_merge<HD, HEADS>(own, reinterpret_cast<const float *>(smem_raw + Cfg::SMEM), S, cluster_ctarank(), mo);
-            Q4_STAMP(6);
             return;
         }
         cluster_sync_all();
-        Q4_STAMP(4);
         cluster_merge<HD, HEADS>((uint32_t)__cvta_generic_to_shared(own), S, cluster_ctarank(), mo);
-        Q4_STAMP(5);
         cluster_sync_all();
-        Q4_STAMP(6);
         return;
     }
     /* level 1: record per block; groups of DEC_GROUP blocks are merged by their last arrival,
@@ -1413,7 +1376,6 @@ q4_decode_k(const DecParams P) {
     bool last = false;
     for (int level = 0;; level++) {
         merge_records<HD, HEADS>(src, count, global, dst, mo, mscr);
-        Q4_STAMP(3 + level);
         if (last) {                                        /* finalised, or this rank's record is complete */
             if (fin) xchg_finish<HD, HEADS>(P.xchg, P.xchg_phase, (uint32_t)unit, fin, mo, P.err);
             return;
@@ -1653,19 +1615,12 @@ bool q4i_decode(const Q4DecodeArgs &a) {
     p.idx_unit_stride = a.idx_unit_stride;
     p.pos = a.pos;
     p.kv_base = a.kv_base;
+    p.idx_bound_nkv = a.idx_bound_nkv ? 1u : 0u;
     p.scale_log2e = a.scale * 1.4426950408889634f;
     p.S = S;
     p.cluster = cluster;
     /* the push merge needs extra shared memory; the launcher drops it where that would cost a wave */
     p.push_bytes = cluster > 1 ? ((gqa + cluster - 1u) / cluster) * cluster * (a.hd + 4u) * (uint32_t)sizeof(float) : 0u;
-    p.debug = 0;
-#ifdef Q4_DEC_TIMING
-    {
-        static int dbg = -1;
-        if (dbg < 0) { const char *e = getenv("Q4_DEC_DEBUG"); dbg = e ? atoi(e) : 0; }
-        p.debug = (uint32_t)dbg;
-    }
-#endif
     p.scratch = scratch;
     p.counters = counters;
     p.err = g_q4.err_d;
@@ -1710,16 +1665,6 @@ bool q4i_xchg_merge(const q4_gpu_xchg *x, const float *gate, float *out) {
     }
     return q4i_fail(Q4E_ARG, "exchange merge: hd must be 32, 64, 128 or 256");
 }
-
-#ifdef Q4_DEC_TIMING
-extern "C" bool q4_dbg_clear_stamps(void) {
-    void *p = nullptr;
-    return cudaGetSymbolAddress(&p, q4_dbg_stamps) == cudaSuccess && cudaMemset(p, 0, sizeof(q4_dbg_stamps)) == cudaSuccess;
-}
-extern "C" bool q4_dbg_fetch_stamps(unsigned long long *host, size_t n) {
-    return cudaMemcpyFromSymbol(host, q4_dbg_stamps, n * sizeof(unsigned long long)) == cudaSuccess;
-}
-#endif
 
 extern "C" bool q4_gpu_lse_merge(const float *parts, uint32_t n_parts, uint32_t n_head, uint32_t hd,
                                  const float *gate, float *out) {
@@ -1791,6 +1736,7 @@ extern "C" bool q4_gpu_kv_decode_noalloc(const q4_gpu_kv *kv, uint32_t layer, co
         a.pos = g_q4.pos_d;
         a.hint_rows = kv->max_kv;
     }
+    a.idx_bound_nkv = 1;
     a.scale = scale;
     a.scratch_part = part_dev[dev];
     a.scratch_counters = ctr_dev[dev];

@@ -21,7 +21,8 @@ enum {
 /* One cache as the kernels see it.  Row (layer, kv head kh, token p) of the K plane lives at
  * k + layer*layer_stride + kh*kvh_stride + p*tok_stride (same for v); for the native q8_0 store the
  * scale row is at s + layer*s_layer_stride + kh*s_kvh_stride + p*s_tok_stride and holds the K block
- * scales followed by the V block scales (fp16). */
+ * scales followed by the V block scales (fp16).  The native q8_0 layout is always the record
+ * {K codes hd | V codes hd | scales}: v = k + hd, s = k + 2*hd, equal strides (kernels rely on it). */
 struct Q4Cache {
     const uint8_t *k, *v, *s;
     uint64_t layer_stride, kvh_stride, s_layer_stride, s_kvh_stride;
@@ -137,6 +138,8 @@ struct Q4DecodeArgs {
     const int32_t *pos;          /* device positions: per session (many) or one word (one); may be null */
     uint32_t kv_base;            /* used when pos == nullptr: unit u attends kv_base + u + 1 rows */
     uint32_t hint_rows;          /* host's estimate of rows per unit, to size the split */
+    int idx_bound_nkv;           /* list entries >= the unit's row count (newest + 1) are out of range (stores:
+                                  * rows beyond it were never written); 0 = only max_kv bounds them (reference ABI) */
     float scale;
     /* optional caller-provided scratch (no-allocation entry point); null = library scratch */
     float *scratch_part;

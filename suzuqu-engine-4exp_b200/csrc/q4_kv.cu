@@ -59,6 +59,20 @@ __global__ void q4_f32_to_f16_k(const float *src, __half *dst, uint64_t n, const
     if (i < n) dst[i] = __float2half_rn(src[i]);
 }
 
+/* fp16 / fp32 rows of any length and alignment at the slot held in the device position word (the
+ * reference's kv_append_k takes any n for these kinds, src/q4_rocm.cu:7986-7999): one element per
+ * thread, blockIdx.y: 0 = K, 1 = V. */
+template <bool F16>
+__global__ void q4_append_flat_k(uint8_t *kc, uint8_t *vc, const float *k, const float *v, uint32_t n, uint32_t bpt,
+                                 const int32_t *pos) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    uint8_t *row = (blockIdx.y ? vc : kc) + (uint64_t)(uint32_t)*pos * bpt;
+    const float x = (blockIdx.y ? v : k)[i];
+    if (F16) reinterpret_cast<__half *>(row)[i] = __float2half_rn(x);
+    else reinterpret_cast<float *>(row)[i] = x;
+}
+
 /* Fused K+V append into a cache view.  blockIdx.y: 0 = K, 1 = V.  8 lanes per 32 values. */
 template <int LAY>
 __global__ void q4_append_k(const AppendParams P) {
@@ -212,7 +226,19 @@ extern "C" bool q4_hip_f32_to_f16_d(void *dst_base, uint32_t stride_elems, const
 extern "C" bool q4_hip_kv_append_d(void *kcache, void *vcache, const float *k, const float *v, uint32_t n,
                                    uint32_t bpt, int kind) {
     if (!g_q4.ok || !g_q4.pos_d || !kcache || !vcache || !k || !v || !n || !bpt) return false;
-    if (n % 32u) return false;   /* the reference requires it for q8 only; rows here are 32-multiples */
+    if (kind < 0 || kind > 2) return false;
+    if (kind == Q4K_Q8 && (n % 32u)) return false;   /* whole q8_0 blocks only, as the reference (:8003-8006) */
+    const bool vec_ok = (n % 32u) == 0 && (((uintptr_t)k | (uintptr_t)v) & 15u) == 0 &&
+                        (kind == Q4K_Q8 || ((((uintptr_t)kcache | (uintptr_t)vcache | bpt) & 15u) == 0));
+    if (!vec_ok) {
+        if (kind == Q4K_Q8) return q4i_fail(Q4E_ARG, "kv_append_d: q8_0 rows need 16-byte aligned fp32 sources");
+        dim3 grid((n + 255u) / 256u, 2);
+        if (kind == Q4K_F16)
+            q4_append_flat_k<true><<<grid, 256, 0, g_q4.stream>>>((uint8_t *)kcache, (uint8_t *)vcache, k, v, n, bpt, g_q4.pos_d);
+        else
+            q4_append_flat_k<false><<<grid, 256, 0, g_q4.stream>>>((uint8_t *)kcache, (uint8_t *)vcache, k, v, n, bpt, g_q4.pos_d);
+        return q4i_check(cudaGetLastError(), "kv_append_d launch");
+    }
     AppendParams p;
     memset(&p, 0, sizeof(p));
     p.one.k = (const uint8_t *)kcache;
@@ -281,9 +307,11 @@ extern "C" bool q4_hip_qsa_decode_idx(const float *d_q, const void *d_kcache, co
 /* ======================================================================= KV store ========== */
 
 extern "C" uint64_t q4_gpu_kv_bytes(uint32_t n_layers, uint32_t n_kvh, uint32_t hd, uint32_t max_kv, int kind) {
-    /* K+V: same total as q4_qsa_kv_bytes (src/q4_place.c:92-105); the record layout regroups bytes, it
-     * does not add any: hd codes + hd/32 fp16 scales per row = (hd/32)*34. */
-    if (kind == Q4K_Q8) return (uint64_t)n_layers * max_kv * 2ull * n_kvh * (hd / 32u) * 34u;
+    /* The bytes q4_gpu_kv_create allocates for the planes.  q8_0: one record per (kv head, position) of
+     * 2*hd codes + 2*hd/32 fp16 scales, padded to a multiple of 16 bytes: at hd 128 and 256 that is
+     * exactly the reference's K+V total (q4_qsa_kv_bytes, src/q4_place.c:92-105: 2 x (hd/32) x 34 per
+     * row); at hd 32 / 64 the padding adds 12 / 8 bytes per record (80 vs 68, 144 vs 136). */
+    if (kind == Q4K_Q8) return (uint64_t)n_layers * max_kv * n_kvh * q8_record_bytes(hd);
     return (uint64_t)n_layers * max_kv * 2ull * n_kvh * hd * (kind == Q4K_F16 ? 2u : 4u);
 }
 
@@ -479,6 +507,7 @@ static bool store_decode(const q4_gpu_kv *kv, uint32_t layer, const void *q, int
         a.pos = g_q4.pos_d;          /* rows = device position word + 1 */
         a.hint_rows = kv->max_kv;
     }
+    a.idx_bound_nkv = 1;
     a.scale = scale;
     return q4i_decode(a);
 }
@@ -530,6 +559,7 @@ extern "C" bool q4_gpu_kv_decode_idx_n(const q4_gpu_kv *kv, uint32_t layer, cons
 
 struct q4_gpu_batch {
     uint32_t max_sessions, n;
+    uint32_t n_active;            /* sessions of the latest q4_gpu_batch_set_pos: what every batch launch covers */
     q4_gpu_kv **kv;
     Q4Cache *d_views;             /* device array of the bound stores' views (one load, no pointer chase) */
     int32_t *pos_d, *pos_h;       /* pos_h: pinned ring of 8 uploads, each slot guarded by an event */
@@ -598,6 +628,7 @@ extern "C" bool q4_gpu_batch_set_pos(q4_gpu_batch *b, const int32_t *pos, uint32
         if (pos[i] > (int32_t)mx) mx = (uint32_t)pos[i];
     }
     b->max_pos = mx;
+    b->n_active = n_sessions;
     return q4i_check(cudaMemcpyAsync(b->pos_d, h, sizeof(int32_t) * n_sessions, cudaMemcpyHostToDevice, g_q4.stream),
                      "batch_set_pos upload") &&
            q4i_check(cudaEventRecord(b->pos_ev[slot], g_q4.stream), "batch_set_pos event");
@@ -605,9 +636,10 @@ extern "C" bool q4_gpu_batch_set_pos(q4_gpu_batch *b, const int32_t *pos, uint32
 extern "C" bool q4_gpu_batch_append(q4_gpu_batch *b, uint32_t layer, const float *k, const float *v) {
     if (!g_q4.ok) return q4i_fail(Q4E_INIT, "batch_append: library not initialised");
     Q4_REQUIRE(b && b->n && k && v && b->kv[0] && layer < b->kv[0]->n_layers, "batch_append: bad argument");
+    Q4_REQUIRE(b->n_active, "batch_append: no positions published (q4_gpu_batch_set_pos)");
     AppendParams p;
     memset(&p, 0, sizeof(p));
-    p.many = b->d_views; p.layer = layer; p.n_rows = b->n; p.n_kvh = b->kv[0]->n_kvh; p.hd = b->kv[0]->hd;
+    p.many = b->d_views; p.layer = layer; p.n_rows = b->n_active; p.n_kvh = b->kv[0]->n_kvh; p.hd = b->kv[0]->hd;
     p.k = k; p.v = v; p.pos = b->pos_d; p.err = g_q4.err_d;
     return launch_append(p, store_layout(b->kv[0]->kind));
 }
@@ -616,12 +648,13 @@ extern "C" bool q4_gpu_batch_decode(q4_gpu_batch *b, uint32_t layer, const void 
                                     uint32_t idx_sess_stride, uint32_t n_head, float scale) {
     if (!g_q4.ok) return q4i_fail(Q4E_INIT, "batch_decode: library not initialised");
     Q4_REQUIRE(b && b->n && q && out && b->kv[0] && layer < b->kv[0]->n_layers && n_head, "batch_decode: bad argument");
+    Q4_REQUIRE(b->n_active, "batch_decode: no positions published (q4_gpu_batch_set_pos)");
     Q4DecodeArgs a;
     memset(&a, 0, sizeof(a));
     a.many = b->d_views;
     a.layout = store_layout(b->kv[0]->kind);
     a.layer = layer;
-    a.n_units = b->n;
+    a.n_units = b->n_active;
     a.n_head = n_head;
     a.n_kvh = b->kv[0]->n_kvh;
     a.hd = b->kv[0]->hd;
@@ -629,6 +662,7 @@ extern "C" bool q4_gpu_batch_decode(q4_gpu_batch *b, uint32_t layer, const void 
     a.idx = idx; a.width = width; a.idx_kvh_stride = idx_kvh_stride; a.idx_unit_stride = idx_sess_stride;
     a.pos = b->pos_d;
     a.hint_rows = b->max_pos + 1;
+    a.idx_bound_nkv = 1;
     a.scale = scale;
     return q4i_decode(a);
 }
@@ -641,6 +675,7 @@ extern "C" bool q4_gpu_batch_append_decode(q4_gpu_batch *b, uint32_t layer, cons
     if (!g_q4.ok) return q4i_fail(Q4E_INIT, "batch_append_decode: library not initialised");
     Q4_REQUIRE(b && b->n && k && v && q && out && b->kv[0] && layer < b->kv[0]->n_layers && n_head,
                "batch_append_decode: bad argument");
+    Q4_REQUIRE(b->n_active, "batch_append_decode: no positions published (q4_gpu_batch_set_pos)");
     const bool fused = b->kv[0]->kind == Q4K_Q8 && b->kv[0]->hd == 128;
     if (!fused && !q4_gpu_batch_append(b, layer, k, v)) return false;
     Q4DecodeArgs a;
@@ -648,7 +683,7 @@ extern "C" bool q4_gpu_batch_append_decode(q4_gpu_batch *b, uint32_t layer, cons
     a.many = b->d_views;
     a.layout = store_layout(b->kv[0]->kind);
     a.layer = layer;
-    a.n_units = b->n;
+    a.n_units = b->n_active;
     a.n_head = n_head;
     a.n_kvh = b->kv[0]->n_kvh;
     a.hd = b->kv[0]->hd;
@@ -656,6 +691,7 @@ extern "C" bool q4_gpu_batch_append_decode(q4_gpu_batch *b, uint32_t layer, cons
     a.idx = idx; a.width = width; a.idx_kvh_stride = idx_kvh_stride; a.idx_unit_stride = idx_sess_stride;
     a.pos = b->pos_d;
     a.hint_rows = b->max_pos + 1;
+    a.idx_bound_nkv = 1;
     a.scale = scale;
     if (fused) { a.new_k = k; a.new_v = v; }
     return q4i_decode(a);
@@ -681,6 +717,7 @@ extern "C" bool q4_gpu_kv_append_decode_d(q4_gpu_kv *kv, uint32_t layer, const f
     a.idx = idx; a.width = width; a.idx_kvh_stride = idx_kvh_stride;
     a.pos = g_q4.pos_d;
     a.hint_rows = kv->max_kv;
+    a.idx_bound_nkv = 1;
     a.scale = scale;
     if (fused) { a.new_k = k; a.new_v = v; }
     return q4i_decode(a);

@@ -201,16 +201,6 @@ __global__ void __launch_bounds__(256) q4_pf_stage_k(const Q4Cache C, uint32_t l
     for (int i = 0; i < 4; i++) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
 }
 
-#ifdef Q4_PF_TIMING
-/* experiment builds only: cycles spent per wait kind, per block: [0..4] control (bar_s, bar_o, bar_p, full_v,
- * full_k), [5..8] softmax warp 0 lane 0 (bar_s, tcgen05.ld, bar_o, total), [9] tiles */
-__device__ unsigned long long q4_pf_dbg[4096 * 16];
-#define PF_T0() const long long t_ = clock64()
-#define PF_ACC(i) acc_[i] += clock64() - t_
-#else
-#define PF_T0() do { } while (0)
-#define PF_ACC(i) do { } while (0)
-#endif
 
 __global__ void __launch_bounds__(PF_THREADS, 2) q4_prefill_k(const PrefillParams P, const __grid_constant__ CUtensorMap map_k,
                                                               const __grid_constant__ CUtensorMap map_v) {
@@ -295,10 +285,6 @@ __global__ void __launch_bounds__(PF_THREADS, 2) q4_prefill_k(const PrefillParam
         return false;
     };
     bool ok = true;
-#ifdef Q4_PF_TIMING
-    long long acc_[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-    const long long t_begin_ = clock64();
-#endif
 
     if (warp == 5) {
         /* ================= producer: one thread keeps two tiles of K and of V^T in flight ================= */
@@ -326,12 +312,12 @@ __global__ void __launch_bounds__(PF_THREADS, 2) q4_prefill_k(const PrefillParam
                 const uint32_t st = tile % PF_STAGES, use = (tile / PF_STAGES) & 1u;
                 /* Q.K of this tile complete: its K stage takes the tile two ahead */
                 if (tile + 2 < n_tiles) {
-                    { PF_T0(); ok = wait(bar_s + 8 * st, use); PF_ACC(0); }
+                    ok = wait(bar_s + 8 * st, use);
                     if (ok) { load_k(tile + 2); k_issued = tile + 3; }
                 }
                 /* P.V of the previous tile complete: its V stage takes the tile after this one */
                 if (ok && tile > 0 && tile + 1 < n_tiles) {
-                    { PF_T0(); ok = wait(bar_o, (tile - 1u) & 1u); PF_ACC(1); }
+                    ok = wait(bar_o, (tile - 1u) & 1u);
                     if (ok) { load_v(tile + 1); v_issued = tile + 2; }
                 }
             }
@@ -371,10 +357,10 @@ __global__ void __launch_bounds__(PF_THREADS, 2) q4_prefill_k(const PrefillParam
                 const uint32_t st = tile % PF_STAGES, use = (tile / PF_STAGES) & 1u;
                 /* operands first (they land while the softmax runs), then the softmax's hand-over, so that
                  * nothing but the issue itself stands between "P is ready" and the two products */
-                { PF_T0(); ok = wait(full_v + 8 * st, use); PF_ACC(3); }
-                if (ok && tile + 2 < n_tiles) { PF_T0(); ok = wait(full_k + 8 * st, ((tile + 2) / PF_STAGES) & 1u); PF_ACC(4); }
+                ok = wait(full_v + 8 * st, use);
+                if (ok && tile + 2 < n_tiles) ok = wait(full_k + 8 * st, ((tile + 2) / PF_STAGES) & 1u);
                 /* softmax of this tile done: P is in shared memory, O is rescaled, S[st] has been read */
-                { PF_T0(); ok = ok && wait(bar_p, tile & 1u); PF_ACC(2); }
+                ok = ok && wait(bar_p, tile & 1u);
                 tc_fence_after();
                 if (ok) {
 #pragma unroll
@@ -387,12 +373,6 @@ __global__ void __launch_bounds__(PF_THREADS, 2) q4_prefill_k(const PrefillParam
                     if (tile + 2 < n_tiles) issue_qk(tile + 2);
                 }
             }
-#ifdef Q4_PF_TIMING
-            {
-                const uint32_t b_ = blockIdx.x + gridDim.x * blockIdx.y;
-                if (b_ < 4096) for (int i = 2; i < 5; i++) q4_pf_dbg[b_ * 16 + i] = (unsigned long long)acc_[i];
-            }
-#endif
         }
     } else {
         /* ================= softmax (warps 0-3): thread r owns row r ================= */
@@ -400,16 +380,12 @@ __global__ void __launch_bounds__(PF_THREADS, 2) q4_prefill_k(const PrefillParam
         float m_ref = -CUDART_INF_F, l_run = 0.f;
         for (uint32_t tile = 0; tile < n_tiles && ok; tile++) {
             const uint32_t st = tile % PF_STAGES, use = (tile / PF_STAGES) & 1u;
-            { PF_T0(); ok = __all_sync(0xffffffffu, wait(bar_s + 8 * st, use)); PF_ACC(5); }   /* a warp leaves the loop as one */
+            ok = __all_sync(0xffffffffu, wait(bar_s + 8 * st, use));   /* a warp leaves the loop as one */
             tc_fence_after();
             float s[64];
-            {
-                PF_T0();
-                tmem_ld32(t_lane + PF_S_COL + st * PF_BN, *reinterpret_cast<float(*)[32]>(&s[0]));
-                tmem_ld32(t_lane + PF_S_COL + st * PF_BN + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
-                tmem_wait_ld();
-                PF_ACC(6);
-            }
+            tmem_ld32(t_lane + PF_S_COL + st * PF_BN, *reinterpret_cast<float(*)[32]>(&s[0]));
+            tmem_ld32(t_lane + PF_S_COL + st * PF_BN + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+            tmem_wait_ld();
             const uint32_t p0 = tile * PF_BN;
             float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;
             if (!(p0 + PF_BN <= cta_min_nkv && row_live)) {
@@ -444,7 +420,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) q4_prefill_k(const PrefillParam
             l_run += ls0 + ls1;
             /* the previous P.V must have drained before P is overwritten and O is rescaled */
             if (tile > 0) {
-                { PF_T0(); ok = __all_sync(0xffffffffu, ok && wait(bar_o, (tile - 1u) & 1u)); PF_ACC(7); }
+                ok = __all_sync(0xffffffffu, ok && wait(bar_o, (tile - 1u) & 1u));
                 tc_fence_after();
                 if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll
@@ -471,16 +447,6 @@ __global__ void __launch_bounds__(PF_THREADS, 2) q4_prefill_k(const PrefillParam
         }
         if (ok && n_tiles > 0) ok = wait(bar_o, (n_tiles - 1u) & 1u);
         tc_fence_after();
-#ifdef Q4_PF_TIMING
-        if (tid == 0) {
-            const uint32_t b_ = blockIdx.x + gridDim.x * blockIdx.y;
-            if (b_ < 4096) {
-                for (int i = 5; i < 8; i++) q4_pf_dbg[b_ * 16 + i] = (unsigned long long)acc_[i];
-                q4_pf_dbg[b_ * 16 + 8] = (unsigned long long)(clock64() - t_begin_);
-                q4_pf_dbg[b_ * 16 + 9] = n_tiles;
-            }
-        }
-#endif
 
         /* ---- epilogue: O / l * sigmoid(gate) -> bf16 */
         if (ok) {
@@ -555,11 +521,6 @@ bool stage_reserve(size_t halves) {
 
 }  // namespace
 
-#ifdef Q4_PF_TIMING
-extern "C" bool q4_pf_dbg_fetch(unsigned long long *host, size_t n) {
-    return cudaMemcpyFromSymbol(host, q4_pf_dbg, n * sizeof(unsigned long long)) == cudaSuccess;
-}
-#endif
 
 void q4i_prefill_release() {
     if (g_stage) cudaFree(g_stage);

@@ -234,6 +234,13 @@ extern "C" int q4_hip_pos_dev_ok(void) { return g_q4.ok && g_q4.pos_d && g_q4.po
 
 extern "C" int q4_hip_graph_begin(void) {
     if (!g_q4.ok || g_q4.capturing) return 0;
+    if (g_q4.stream == cudaStreamLegacy || g_q4.stream == nullptr) {
+        /* the legacy default stream cannot be captured: a host that adopted it (q4_gpu_set_stream) has to
+         * hand over a real stream, or NULL to go back to the library's own, before it opens a capture */
+        q4i_fail(Q4E_ARG, "graph_begin: the adopted stream is the legacy default stream, which cannot be captured; "
+                          "call q4_gpu_set_stream(NULL) or adopt a created stream first");
+        return 0;
+    }
     if (cudaStreamBeginCapture(g_q4.stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
         (void)cudaGetLastError();
         return 0;
