@@ -11,13 +11,16 @@
  * scalar FMA pipe cannot keep up with B200's memory system (8 FMA per int8 byte at ~23 B/clk/SM
  * is more than the 128 FMA/clk an SM has), so the two contractions run on the tensor cores with
  * warp-level MMA.  Every byte of the cache is read from global memory once.  For the native q8_0
- * store at hd 128 each warp owns a 4-stage ring of 16-position tiles in shared memory that it fills
- * with 16-byte cp.async copies (whole 128-byte rows, gathered by position); an iteration computes two
- * tiles while the next two are in flight, so the gather latency of HBM is hidden behind the
- * arithmetic without spending registers; there is no block barrier in the main loop, warps stream
- * independently.  The rings are
- * swizzled so that the fragment reads are bank-conflict free.  The other layouts load fragments
- * straight into registers with sector-aligned 4/8/16-byte loads.
+ * store at hd 128 each warp owns a 4-stage ring of 16-position tiles in shared memory (the tile's
+ * records as they lie in the store, 272 bytes apart).  A tile of 16 consecutive positions is one
+ * contiguous span of the store: it comes in with fully coalesced 16-byte cp.async copies, or, in a
+ * dense scan, with one 4352-byte bulk copy (cp.async.bulk, completion on the stage's mbarrier); any
+ * other tile is gathered row by row with 16-byte cp.async copies.  Per tile the warp unloads the
+ * stage into MMA fragments (ldmatrix for the K rows, transposing ldmatrix for the V rows), refills
+ * the stage at once with the tile four ahead, and then computes from registers, so four tiles per
+ * warp are in flight all the time; there is no block barrier in the main loop, warps stream
+ * independently.  The other layouts load fragments straight into registers with sector-aligned
+ * 4/8/16-byte loads.
  *
  *   one warp-step = 16 positions:
  *     S^T[16 pos x 8 heads]  = K[16 x hd] . Q^T        (m16n8k16, K rows are the A operand)
@@ -25,9 +28,10 @@
  *     P^T -> fp16, 8x8 transposed in-warp (movmatrix) into the B operand
  *     O^T[hd x 8 heads]     += V^T[hd x 16 pos] . P^T   (V bytes are the A operand)
  *
- *   q8_0: int8 codes are converted to exact fp16 integers in registers (byte permute + magic
- *   subtract); K block scales multiply the four per-block partial dot products in fp32, V block
- *   scales are folded into P^T per 32-wide block of hd.  Nothing is rounded except Q (to fp16 once)
+ *   q8_0: int8 codes are converted to exact fp16 integers in registers (byte permute; the K side
+ *   folds the offset into the MMA's initial accumulator, the V side subtracts it); K block scales
+ *   multiply the four per-block partial dot products in fp32, V block scales are folded into P^T
+ *   per 32-wide block of hd.  Nothing is rounded except Q (to fp16 once; exact for bf16 queries)
  *   and the softmax weights (fp16, and the denominator sums the same rounded weights).
  *
  * grid = (splits, kv heads, units).  Every block reduces its warps' partials in shared memory.  Up to
@@ -75,6 +79,7 @@ struct DecParams {
     const float *new_k, *new_v;   /* fused append of the newest row (native q8_0 store), or null */
     uint32_t pdl;                 /* launched with programmatic stream serialization */
     uint32_t push_bytes;          /* > 0: the launch carries this much extra shared memory and merges by pushing */
+    uint32_t bulk_runs;           /* tiles of 16 consecutive positions come in by one bulk copy each (else by cp.async) */
 };
 
 /* ---- small device helpers ---------------------------------------------------------------- */
@@ -108,15 +113,39 @@ __device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void *gsrc, 
     else
         asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(smem_dst), "r"(0u) : "memory");
 }
-/* The K and the V chunk of one record (V codes follow the K codes at +HD in the native q8_0 record) into
- * the K tile and, 2048 bytes further, the V tile of a ring stage; nothing is copied for a padding position. */
+/* The K and the V chunk of one record (V codes follow the K codes at +HD, in the store and in a ring stage);
+ * nothing is copied for a padding position. */
 template <int HD>
 __device__ __forceinline__ void cp_async16_kv(uint32_t smem_dst, const void *gsrc, int32_t pos) {
     asm volatile(
         "{\n\t.reg .pred q;\n\tsetp.ge.s32 q, %2, 0;\n\t"
         "@q cp.async.cg.shared.global [%0], [%1], 16;\n\t"
-        "@q cp.async.cg.shared.global [%0+2048], [%1+%3], 16;\n\t}"
+        "@q cp.async.cg.shared.global [%0+%3], [%1+%3], 16;\n\t}"
         ::"r"(smem_dst), "l"(gsrc), "r"(pos), "n"(HD) : "memory");
+}
+/* 512 consecutive bytes per warp instruction: lane l copies bytes [OFF + 16 l, OFF + 16 l + 16) */
+template <int OFF>
+__device__ __forceinline__ void cp_async16_at(uint32_t smem_dst, const void *gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0+%2], [%1+%2], 16;" ::"r"(smem_dst), "l"(gsrc), "n"(OFF) : "memory");
+}
+/* one record, global -> shared, through the bulk-copy engine; completion is counted in bytes on the mbarrier */
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t smem_dst, const void *gsrc, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void ring_bar_init(uint32_t bar) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void ring_bar_expect(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool ring_bar_test(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0u;
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 /* four 8x8 matrices of 16-bit elements (eight 16-byte rows each; lanes 8i..8i+7 give the row addresses of
@@ -674,7 +703,18 @@ __global__ void __launch_bounds__(DEC_THREADS) q4_xchg_merge_k(const Q4XchgDev *
 
 /* ---- the kernel ---------------------------------------------------------------------------- */
 constexpr int RING_STAGES = 4;
-constexpr int RING_STAGE_BYTES = 2048 + 2048 + 256 + 64;   /* K rows, V rows, scale rows, positions */
+/* A stage holds the 16 records of a tile as they lie in the store: row r at r * 272 = K codes | V codes | K and V
+ * block scales.  Rows 272 bytes apart put the eight 16-byte row pieces of one 8x8 ldmatrix block into eight
+ * different bank groups ((17 r + c) mod 8), so no swizzle is needed, and a tile whose 16 positions are
+ * consecutive is one contiguous 4352-byte span of the store, which one bulk copy (cp.async.bulk, completion
+ * counted in bytes on the stage's mbarrier) brings in; other tiles are gathered with 16-byte cp.async copies. */
+constexpr int RING_ROW = 272;
+constexpr int RING_V_OFF = 128;                             /* V codes of a row relative to its K codes */
+constexpr int RING_MASK_OFF = 16 * RING_ROW;                /* bits 0-15: live positions, bit 16: brought in by a bulk copy */
+constexpr uint32_t RING_RUN_BIT = 1u << 16;
+constexpr int RING_STAGE_BYTES = 16 * RING_ROW + 32;        /* rows, mask word */
+constexpr int RING_BAR_BYTES = DEC_WARPS * RING_STAGES * 8; /* one mbarrier per stage, behind the rings of all warps */
+constexpr uint32_t RING_SPIN_LIMIT = 1u << 22;             /* probes of a stage's mbarrier before the block gives up */
 
 template <int LAY, int HD, int NHT>
 struct DecCfg {
@@ -682,7 +722,7 @@ struct DecCfg {
     static constexpr int HEADS = 8 * NHT;
     static constexpr int REC = HD + 4;          /* acc[HD], m, l, 2 pad: 16-byte aligned records */
     static constexpr size_t EPI_BYTES = (size_t)DEC_WARPS * HEADS * REC * sizeof(float);
-    static constexpr size_t RING_BYTES = STAGED ? (size_t)DEC_WARPS * RING_STAGES * RING_STAGE_BYTES : 0;
+    static constexpr size_t RING_BYTES = STAGED ? (size_t)DEC_WARPS * RING_STAGES * RING_STAGE_BYTES + RING_BAR_BYTES : 0;
     static constexpr size_t REC_BYTES = (size_t)HEADS * REC * sizeof(float);   /* the block's merged record */
     static constexpr size_t TAIL_BYTES = EPI_BYTES + REC_BYTES + MERGE_SCRATCH_FLOATS * sizeof(float);   /* after the loop */
     static constexpr size_t SMEM = TAIL_BYTES > RING_BYTES ? TAIL_BYTES : RING_BYTES;
@@ -972,25 +1012,32 @@ q4_decode_k(const DecParams P) {
          * ldmatrix for the V rows, the scale rows and the mask of live positions), refills the stage at once
          * with the tile RING_STAGES ahead, and only then does the arithmetic: all stages but the one being
          * unloaded are in flight all the time.  There is no block barrier in the loop.
-         * Stage = K tile (16 rows x 128 B) | V tile | 16 scale rows of 16 B | mask word.  16-byte chunk c of
-         * row r lies at chunk c ^ (r & 7) of its row in both tiles, so the eight row addresses of one 8x8
-         * ldmatrix block hit eight different bank groups.  Padding positions copy nothing: their scale row is
-         * zeroed (so they add nothing to P.V whatever the stale code bytes are) and their scores are masked. */
+         * Stage = the tile's 16 records, 272 bytes apart, as they lie in the store | mask word.  A tile of 16
+         * consecutive positions (every tile of a dense scan, the recent window of a selection list) is one
+         * contiguous span of the store and is copied 512 consecutive bytes per instruction; other tiles are
+         * gathered row by row.  Padding positions copy nothing: their scale row is zeroed (so they add nothing to
+         * P.V whatever the stale code bytes are) and their scores are masked. */
         const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem_raw) +
                               (uint32_t)warp * RING_STAGES * RING_STAGE_BYTES;
         const uint32_t n_my = s_begin + warp < s_end ? (s_end - s_begin - warp + DEC_WARPS - 1u) / DEC_WARPS : 0u;
         const uint32_t r16 = lane & 15, c8 = lane & 7;
-        uint32_t coff[4];   /* copy destination of row 4j + lane / 8, chunk lane % 8 */
-#pragma unroll
-        for (uint32_t j = 0; j < 4; j++) {
-            const uint32_t row = 4 * j + (lane >> 3);
-            coff[j] = row * 128 + ((c8 ^ (row & 7)) << 4);
-        }
         /* ldmatrix row address of this lane for block b: matrix lane / 8 = rows 8 * (that & 1) .., chunk 2b + lane / 16 */
         uint32_t moff[NB];
 #pragma unroll
         for (int b = 0; b < NB; b++)
-            moff[b] = (uint32_t)((lane & 7) + ((lane >> 3) & 1) * 8) * 128 + (((uint32_t)(2 * b + (lane >> 4)) ^ (uint32_t)(lane & 7)) << 4);
+            moff[b] = (uint32_t)((lane & 7) + ((lane >> 3) & 1) * 8) * RING_ROW + (uint32_t)(2 * b + (lane >> 4)) * 16;
+        /* one mbarrier per stage for the bulk copies, behind the rings of all warps (the epilogue never reaches
+         * them); par: the phase each stage's barrier completes next */
+        const uint32_t bars = (uint32_t)__cvta_generic_to_shared(smem_raw) + DEC_WARPS * RING_STAGES * RING_STAGE_BYTES +
+                              (uint32_t)warp * RING_STAGES * 8;
+        uint32_t par = 0;
+        bool ring_dead = false;   /* a bulk copy never arrived within the probe limit: the block reports it and stops computing */
+        if (P.bulk_runs) {
+            if (lane < RING_STAGES) ring_bar_init(bars + lane * 8);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+        }
 
         /* The list entry is only loaded here; its range check waits until issue() needs the value, several
          * tiles later, so the load latency stays off the critical path. */
@@ -1006,18 +1053,65 @@ q4_decode_k(const DecParams P) {
                     p = -1;
                 }
                 const uint32_t st = ring + (it % RING_STAGES) * RING_STAGE_BYTES;
-                const uint32_t livemask = __ballot_sync(0xffffffffu, p >= 0);
+                const uint32_t livemask = __ballot_sync(0xffffffffu, p >= 0) & 0xffffu;
+                /* 16 consecutive positions: the tile is one contiguous span of the store */
+                const int32_t p0 = __shfl_sync(0xffffffffu, p, 0);
+                const bool run = __all_sync(0xffffffffu, p0 >= 0 && p == p0 + (int32_t)r16);
+                if (run && P.bulk_runs) {
+                    if (lane == 0) {
+                        const uint32_t bar = bars + (it % RING_STAGES) * 8;
+                        /* the stage was last read (and perhaps written) through the generic proxy */
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        ring_bar_expect(bar, 16 * RING_ROW);
+                        bulk_copy_g2s(st, kbase + (uint64_t)(uint32_t)p0 * tok_stride, 16 * RING_ROW, bar);
+                        asm volatile("st.shared.u32 [%0], %1;" ::"r"(st + RING_MASK_OFF), "r"(livemask | RING_RUN_BIT) : "memory");
+                    }
+                } else {
+                    if (run) {
+                        const uint8_t *src = kbase + (uint64_t)(uint32_t)p0 * tok_stride + lane * 16;
+                        const uint32_t dst = st + lane * 16;
+                        cp_async16_at<0>(dst, src);    cp_async16_at<512>(dst, src);  cp_async16_at<1024>(dst, src);
+                        cp_async16_at<1536>(dst, src); cp_async16_at<2048>(dst, src); cp_async16_at<2560>(dst, src);
+                        cp_async16_at<3072>(dst, src); cp_async16_at<3584>(dst, src);
+                        if (lane < 16) cp_async16_at<4096>(dst, src);
+                    } else {
 #pragma unroll
-                for (uint32_t j = 0; j < 4; j++) {
-                    const int32_t pr = __shfl_sync(0xffffffffu, p, 4 * j + (lane >> 3));
-                    cp_async16_kv<HD>(st + coff[j], kbase + (uint64_t)(uint32_t)max(pr, 0) * tok_stride + c8 * 16, pr);
+                        for (uint32_t j = 0; j < 4; j++) {
+                            const uint32_t row = 4 * j + (lane >> 3);
+                            const int32_t pr = __shfl_sync(0xffffffffu, p, row);
+                            cp_async16_kv<HD>(st + row * RING_ROW + c8 * 16, kbase + (uint64_t)(uint32_t)max(pr, 0) * tok_stride + c8 * 16, pr);
+                        }
+                        if (lane < 16)
+                            cp_async16(st + r16 * RING_ROW + 2 * HD, kbase + (uint64_t)(uint32_t)max(p, 0) * tok_stride + 2 * HD, p >= 0);
+                    }
+                    if (lane == 0) asm volatile("st.shared.u32 [%0], %1;" ::"r"(st + RING_MASK_OFF), "r"(livemask) : "memory");
                 }
-                if (lane < 16)
-                    cp_async16(st + 4096 + r16 * 16, kbase + (uint64_t)(uint32_t)max(p, 0) * tok_stride + 2 * HD, p >= 0);
-                if (lane == 0) asm volatile("st.shared.u32 [%0], %1;" ::"r"(st + 4352), "r"(livemask) : "memory");
             }
             cp_async_commit();   /* one group per tile, empty or not, keeps the wait count uniform */
         };
+        /* ---- queries: the raw values are requested now, next to the list entries, and converted after the ring
+         * has been filled (lane (g, t) takes dims 16ks + 4t .. + 3 of head nt*8 + g) */
+        uint32_t qraw[NHT][KS][4];
+#pragma unroll
+        for (int nt = 0; nt < NHT; nt++) {
+            const uint32_t hg = nt * 8 + g;
+            const bool live = hg < P.gqa;
+            const size_t qoff = ((size_t)u * P.n_head + (size_t)kh * P.gqa + hg) * HD;
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++) {
+                qraw[nt][ks][0] = qraw[nt][ks][1] = qraw[nt][ks][2] = qraw[nt][ks][3] = 0u;
+                if (live) {
+                    const int d = 16 * ks + 4 * t;
+                    if (P.q_bf16) {
+                        const uint2 w = *reinterpret_cast<const uint2 *>(reinterpret_cast<const __nv_bfloat16 *>(P.q) + qoff + d);
+                        qraw[nt][ks][0] = w.x; qraw[nt][ks][1] = w.y;
+                    } else {
+                        const uint4 w = *reinterpret_cast<const uint4 *>(reinterpret_cast<const float *>(P.q) + qoff + d);
+                        qraw[nt][ks][0] = w.x; qraw[nt][ks][1] = w.y; qraw[nt][ks][2] = w.z; qraw[nt][ks][3] = w.w;
+                    }
+                }
+            }
+        }
         int32_t pa = my_pos(0), pb = my_pos(1), pc = my_pos(2), pd = my_pos(3);
         int32_t pn0 = my_pos(4), pn1 = my_pos(5), pn2 = my_pos(6);
         /* ---- fused append, second half.  Every split of the unit quantises and stores the unit's newest row
@@ -1039,42 +1133,35 @@ q4_decode_k(const DecParams P) {
                 if (ap_sub == 0) reinterpret_cast<__half *>(row + 2 * HD)[(ap_which ? NB : 0) + ap_b] = __float2half_rn(d);
             }
             if (newest >= max_kv && threadIdx.x == 0) atomicOr(P.err, (uint32_t)Q4E_RANGE);
+            if (P.bulk_runs) asm volatile("fence.proxy.async;" ::: "memory");   /* the row may be read back by the bulk-copy engine */
             __syncthreads();
         }
         if (hold) { issue(0, pa); issue(1, pb); issue(2, pc); issue(3, pd); }
 
-        /* Q fragments with scale * log2(e) folded in, rounded to fp16 once: lane (g, t) holds dims 16ks + 4t ..
-         * + 3 of head nt*8 + g, the columns the K fragments below carry in k-slots 2t, 2t+1, 2t+8, 2t+9.  And,
+        /* Q fragments as fp16 (exact for bf16 queries; scale * log2(e) multiplies the scores in fp32 later):
+         * lane (g, t) holds dims 16ks + 4t .. + 3 of head nt*8 + g, the columns the K fragments below carry in
+         * k-slots 2t, 2t+1, 2t+8, 2t+9.  And,
          * per 32-wide block, -1152 * sum(q): K codes enter the MMA as the fp16 numbers 1152 + code (one byte
          * permute per pair, no subtract), so each block's partial product starts from that correction. */
         uint32_t qs[NHT][KS][2];
         float qcorr[NHT][NB][2];
 #pragma unroll
         for (int nt = 0; nt < NHT; nt++) {
-            const uint32_t hg = nt * 8 + g;
-            const bool live = hg < P.gqa;
-            const size_t qoff = ((size_t)u * P.n_head + (size_t)kh * P.gqa + hg) * HD;
             float bsum[NB];
 #pragma unroll
             for (int ks = 0; ks < KS; ks++) {
-                float x0 = 0.f, x1 = 0.f, x2 = 0.f, x3 = 0.f;
-                if (live) {
-                    const int d = 16 * ks + 4 * t;
-                    if (P.q_bf16) {
-                        const uint2 w = *reinterpret_cast<const uint2 *>(
-                            reinterpret_cast<const __nv_bfloat16 *>(P.q) + qoff + d);
-                        x0 = __uint_as_float(w.x << 16);
-                        x1 = __uint_as_float(w.x & 0xffff0000u);
-                        x2 = __uint_as_float(w.y << 16);
-                        x3 = __uint_as_float(w.y & 0xffff0000u);
-                    } else {
-                        const float4 w =
-                            *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(P.q) + qoff + d);
-                        x0 = w.x; x1 = w.y; x2 = w.z; x3 = w.w;
-                    }
+                float x0, x1, x2, x3;
+                if (P.q_bf16) {
+                    x0 = __uint_as_float(qraw[nt][ks][0] << 16);
+                    x1 = __uint_as_float(qraw[nt][ks][0] & 0xffff0000u);
+                    x2 = __uint_as_float(qraw[nt][ks][1] << 16);
+                    x3 = __uint_as_float(qraw[nt][ks][1] & 0xffff0000u);
+                } else {
+                    x0 = __uint_as_float(qraw[nt][ks][0]); x1 = __uint_as_float(qraw[nt][ks][1]);
+                    x2 = __uint_as_float(qraw[nt][ks][2]); x3 = __uint_as_float(qraw[nt][ks][3]);
                 }
-                const __half2 h0 = __floats2half2_rn(x0 * P.scale_log2e, x1 * P.scale_log2e);
-                const __half2 h1 = __floats2half2_rn(x2 * P.scale_log2e, x3 * P.scale_log2e);
+                const __half2 h0 = __floats2half2_rn(x0, x1);
+                const __half2 h1 = __floats2half2_rn(x2, x3);
                 qs[nt][ks][0] = h2u(h0);
                 qs[nt][ks][1] = h2u(h1);
                 const float part = (__low2float(h0) + __high2float(h0)) + (__low2float(h1) + __high2float(h1));
@@ -1091,9 +1178,22 @@ q4_decode_k(const DecParams P) {
         }
 
         for (uint32_t it = 0; it < n_my; it++) {
-            cp_async_wait<RING_STAGES - 1>();    /* all but the newest RING_STAGES - 1 tiles have landed: tile `it` is in */
+            cp_async_wait<RING_STAGES - 1>();    /* all but the newest RING_STAGES - 1 tiles have landed: tile `it` is in, if gathered */
             __syncwarp();
             const uint32_t st = ring + (it % RING_STAGES) * RING_STAGE_BYTES;
+            const uint32_t livemask = lds32(st + RING_MASK_OFF);
+            if (livemask & RING_RUN_BIT) {
+                /* brought in by a bulk copy: bounded wait for its bytes on the stage's mbarrier; if they never come
+                 * the block reports it and stops computing */
+                const uint32_t sbit = 1u << (it % RING_STAGES), bar = bars + (it % RING_STAGES) * 8;
+                uint32_t probes = 0;
+                while (!ring_bar_test(bar, (par & sbit) ? 1u : 0u) && ++probes < RING_SPIN_LIMIT) {}
+                par ^= sbit;
+                if (__any_sync(0xffffffffu, probes >= RING_SPIN_LIMIT)) {
+                    ring_dead = true;
+                    break;
+                }
+            }
             /* ---- the tile into registers.  K: matrix i of block b = rows 8 (i & 1).., 16 dims from 32b + 16 (i >> 1):
              * kf[b][i] = position g (+8 for odd i), 4 codes of dims 32b + 16 (i >> 1) + 4t.  V, transposed:
              * vf[b][i] = positions 2t, 2t+1 (+8 for odd i), 2 codes each of dims 32b + 16 (i >> 1) + 2g, + 1. */
@@ -1101,12 +1201,13 @@ q4_decode_k(const DecParams P) {
 #pragma unroll
             for (int b = 0; b < NB; b++) ldmatrix_x4(kf[b], st + moff[b]);
 #pragma unroll
-            for (int b = 0; b < NB; b++) ldmatrix_x4_trans(vf[b], st + 2048 + moff[b]);
-            const uint2 ks0 = lds64(st + 4096 + g * 16), ks1 = lds64(st + 4096 + (g + 8) * 16);
+            for (int b = 0; b < NB; b++) ldmatrix_x4_trans(vf[b], st + RING_V_OFF + moff[b]);
+            /* scale row of position r: K block scales, then V block scales */
+            auto srow = [&](int r) -> uint32_t { return st + r * RING_ROW + 2 * HD; };
+            const uint2 ks0 = lds64(srow(g)), ks1 = lds64(srow(g + 8));
             uint2 vs[4];
 #pragma unroll
-            for (int r = 0; r < 4; r++) vs[r] = lds64(st + 4096 + (2 * t + (r & 1) + 8 * (r >> 1)) * 16 + 8);
-            const uint32_t livemask = lds32(st + 4352);
+            for (int r = 0; r < 4; r++) vs[r] = lds64(srow(2 * t + (r & 1) + 8 * (r >> 1)) + 8);
             /* codes to offset binary: (code ^ 0x80) under the exponent byte 0x64 is the fp16 number 1152 + code */
 #pragma unroll
             for (int b = 0; b < NB; b++)
@@ -1158,12 +1259,14 @@ q4_decode_k(const DecParams P) {
                 }
             }
 
-            /* ---- online softmax; lanes (g, t) hold positions g / g+8 for heads 2t, 2t+1 */
+            /* ---- online softmax in the log2 domain; lanes (g, t) hold positions g / g+8 for heads 2t, 2t+1 */
             uint32_t pb0[NHT], pb1[NHT];
 #pragma unroll
             for (int nt = 0; nt < NHT; nt++) {
-                if (!kok0) sc[nt][0] = sc[nt][1] = -CUDART_INF_F;
-                if (!kok1) sc[nt][2] = sc[nt][3] = -CUDART_INF_F;
+                sc[nt][0] = kok0 ? sc[nt][0] * P.scale_log2e : -CUDART_INF_F;
+                sc[nt][1] = kok0 ? sc[nt][1] * P.scale_log2e : -CUDART_INF_F;
+                sc[nt][2] = kok1 ? sc[nt][2] * P.scale_log2e : -CUDART_INF_F;
+                sc[nt][3] = kok1 ? sc[nt][3] * P.scale_log2e : -CUDART_INF_F;
                 const float mx0 = warp_max_over_g(fmaxf(sc[nt][0], sc[nt][2]));
                 const float mx1 = warp_max_over_g(fmaxf(sc[nt][1], sc[nt][3]));
                 const float mn0 = fmaxf(m_run[nt][0], mx0), mn1 = fmaxf(m_run[nt][1], mx1);
@@ -1214,6 +1317,13 @@ q4_decode_k(const DecParams P) {
             }
         }
         cp_async_wait<0>();
+        if (ring_dead) {
+            /* bulk copies that may still be in flight must land (or the probe limit pass again) before the block
+             * leaves its shared memory behind; barriers whose phase completed answer at once */
+            for (uint32_t s_i = 0; s_i < RING_STAGES; s_i++)
+                for (uint32_t probes = 0; probes < (RING_SPIN_LIMIT >> 6) && !ring_bar_test(bars + s_i * 8, (par >> s_i) & 1u); probes++) {}
+            if (lane == 0) atomicOr(P.err, (uint32_t)Q4E_CUDA);
+        }
         __syncthreads();    /* the epilogue below reuses the ring memory of all warps */
     } else {
         for (uint32_t step = s_begin + warp; step < s_end; step += DEC_WARPS) {
@@ -1624,6 +1734,15 @@ bool q4i_decode(const Q4DecodeArgs &a) {
     p.scratch = scratch;
     p.counters = counters;
     p.err = g_q4.err_d;
+    {
+        /* Bulk copies for runs of consecutive positions pay off on dense scans (every tile is a run: one copy
+         * instruction per tile instead of nine); in a gathered list they are slower than coalesced cp.async
+         * (measured: 64-session batch 27.4 vs 26.6 us, single session 8.3 vs 7.9 us).  Q4_DEC_BULK=0 / 1 forces
+         * the choice. */
+        static int bulk = -2;
+        if (bulk == -2) { const char *e = getenv("Q4_DEC_BULK"); bulk = e ? atoi(e) : -1; }
+        p.bulk_runs = bulk >= 0 ? (bulk ? 1u : 0u) : (a.idx ? 0u : 1u);
+    }
     p.xchg = a.xchg;
     p.xchg_phase = (uint32_t)a.xchg_phase;
     p.new_k = a.new_k;

@@ -408,3 +408,42 @@ def test_graph_captured_decode_follows_the_position_word(oracle):
     L.q4_hip_graph_free(g)
     q4gpu.use_torch_stream()
     st.close()
+
+
+@pytest.mark.parametrize("q_bf16", [False, True])
+@pytest.mark.parametrize("mode", ["sigma8", "head_x50"])
+def test_large_magnitude_queries(oracle, mode, q_bf16):
+    """Queries far larger than N(0,1) -- every element ~ N(0, 8^2), or one head of each kv group scaled by
+    50 -- through the sparse and the dense decode of the q8_0 store.  The K side of the kernel enters the
+    codes as 1152 + code and removes 1152 * sum(q) through the accumulator, so the cancellation error
+    grows with sum |q|; the outputs must stay within the stated tolerance of the fp32 oracle."""
+    lib()
+    n_head, n_kvh, hd, ctx, width = 16, 2, 128, 6000, 2051
+    k, v, q = make_case(oracle, 4100, ctx, n_head, n_kvh, hd, rope=False)
+    q = q.copy()
+    if mode == "sigma8":
+        q *= 8.0
+    else:
+        q[3] *= 50.0
+        q[12] *= 50.0
+    if q_bf16:
+        qb = oracle.f32_to_bf16(q)
+        q = oracle.bf16_to_f32(qb)
+        dq = torch.from_numpy(qb.view(np.int16).reshape(-1)).cuda()
+    else:
+        dq = dev(q)
+    gate = oracle.normal(4101, 0, n_head * hd)
+    kc, vc = oracle.kv_write(k, 2), oracle.kv_write(v, 2)
+    st = q4gpu.KVStore(1, n_kvh, hd, ctx, 2)
+    st.append(0, dev(k), dev(v), 0, ctx)
+    scale = 1.0 / np.sqrt(hd)
+    idx = selection(oracle, 4102, ctx, n_kvh)
+    out = torch.empty(n_head * hd, device="cuda")
+    st.decode(0, dq, out, n_head, scale, gate=dev(gate), idx=dev(idx), width=width, idx_kvh_stride=width, n_kv=ctx,
+              q_bf16=q_bf16)
+    ref = oracle.attn(q, kc, vc, gate, n_head, n_kvh, hd, 1, 0, ctx, scale, 2, idx=idx, width=width, idx_kvh_stride=width)[0]
+    assert_close(host(out).reshape(n_head, hd), ref, "sparse, %s" % mode)
+    st.decode(0, dq, out, n_head, scale, gate=dev(gate), n_kv=ctx, q_bf16=q_bf16)
+    ref = oracle.attn(q, kc, vc, gate, n_head, n_kvh, hd, 1, ctx - 1, ctx, scale, 2)[0]
+    assert_close(host(out).reshape(n_head, hd), ref, "dense, %s" % mode)
+    st.close()

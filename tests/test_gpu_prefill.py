@@ -11,12 +11,16 @@ from gpu_util import dev, host, lib
 pytestmark = pytest.mark.gpu
 
 
-def check(got, ref, what):
+def check(got, ref, what, out_scale=1.0):
+    """2e-3 max-abs (times out_scale, the magnitude of the outputs, for the large-magnitude cases) + 1e-3
+    relative, plus one bf16 rounding of the result"""
     got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
     assert np.isfinite(got).all(), what
-    bound = 2e-3 + (1e-3 + 2.0 ** -8) * np.abs(ref)
+    bound = 2e-3 * out_scale + (1e-3 + 2.0 ** -8) * np.abs(ref)
     err = np.abs(got - ref)
-    assert (err <= bound).all(), "%s: max abs err %.3e at ref %.3f" % (what, err.max(), ref.reshape(-1)[err.argmax()])
+    worst = (err / bound).argmax()
+    assert (err <= bound).all(), "%s: max abs err %.3e at ref %.3f; worst err %.3e against bound %.3e at ref %.3f" % (
+        what, err.max(), ref.reshape(-1)[err.argmax()], err.reshape(-1)[worst], bound.reshape(-1)[worst], ref.reshape(-1)[worst])
     return err.max()
 
 
@@ -90,4 +94,44 @@ def test_prefill_rejects_unsupported(oracle):
     buf = torch.zeros(16 * 128, dtype=torch.bfloat16, device="cuda")
     assert not L.q4_gpu_kv_prefill(st.h, 0, buf.data_ptr(), None, buf.data_ptr(), 16, 1, 0, 0.1)
     assert L.q4_gpu_last_error() & 1
+    st.close()
+
+
+@pytest.mark.parametrize("mode", ["sigma8", "head_x50"])
+def test_prefill_large_magnitude_queries(oracle, mode):
+    """queries ~ N(0, 8^2), or one head of each kv group scaled by 50: scores of several hundred in the
+    exponent, softmax close to one-hot.  This checks the running-max rescale, the fp16 weights and the
+    accumulators at such magnitudes.  The tensor-core path stages K and V as fp16(code * scale) (the
+    reference's own fp16 tile), a rounding that |q| multiplies; to keep it out of this check every 32-value
+    block of the rows gets one element of magnitude 127/32, which makes its scale exactly 1/32 and every
+    dequantised value exact in fp16 (the rounding itself is covered by the N(0,1) cases at the stated
+    tolerance).  The absolute part of the tolerance is relative to the magnitude of the outputs."""
+    lib()
+    n_tok, kv_base, n_head, n_kvh, hd = 96, 400, 16, 2, 128
+    ctx, kvw = kv_base + n_tok, n_kvh * hd
+
+    def rows(stream):
+        x = np.clip(oracle.normal(5200, stream, ctx * kvw), -3.9, 3.9).reshape(-1, 32)
+        sign = np.where(x[:, 7] < 0, -1.0, 1.0).astype(np.float32)
+        x[:, 7] = sign * np.float32(127.0 / 32.0)
+        return x.reshape(ctx, kvw)
+    k, v = rows(0), rows(1)
+    q = oracle.normal(5200, 2, n_tok * n_head * hd).reshape(n_tok, n_head, hd).copy()
+    if mode == "sigma8":
+        q *= 8.0
+    else:
+        q[:, 3] *= 50.0
+        q[:, 12] *= 50.0
+    g = oracle.normal(5200, 3, n_tok * n_head * hd)
+    qb = oracle.f32_to_bf16(q)
+    scale = 1.0 / np.sqrt(hd)
+    kc, vc = oracle.kv_write(k, 2), oracle.kv_write(v, 2)
+    assert (kc.reshape(-1, 34)[:, :2].view(np.uint16) == 0x2800).all()      # every block scale is fp16 1/32
+    st = q4gpu.KVStore(1, n_kvh, hd, ctx, 2)
+    st.append(0, dev(k), dev(v), 0, ctx)
+    dq = torch.from_numpy(qb.view(np.int16).reshape(-1)).cuda()
+    dout = torch.empty(n_tok * n_head * hd, dtype=torch.bfloat16, device="cuda")
+    st.prefill(0, dq, dout, n_head, n_tok, kv_base, scale, gate=dev(g))
+    ref = oracle.attn(oracle.bf16_to_f32(qb), kc, vc, g, n_head, n_kvh, hd, n_tok, kv_base, ctx, scale, 2, threads=8)
+    check(host(dout.float()).reshape(n_tok, n_head, hd), ref, "prefill, %s" % mode, out_scale=max(1.0, float(np.abs(ref).max())))
     st.close()

@@ -27,6 +27,18 @@ def test_noalloc_decode_matches_regular_entry_point_twice(oracle):
     scale = 1.0 / np.sqrt(hd)
     want = torch.empty(n_head * hd, device="cuda")
     got = torch.empty(n_head * hd, device="cuda")
+
+    def noalloc(*args):
+        """the call, with the device's free memory read right before and right after it: the defining
+        property of the entry point is that the two readings are equal (cudaMemGetInfo through torch;
+        nothing in between goes through an allocator)"""
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        ok = L.q4_gpu_kv_decode_noalloc(*args)
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before, "the allocation-free entry point changed the free device memory"
+        return ok
+
     for call in range(2):                       # second call starts from the first one's leftovers
         q = oracle.normal(902, call, n_head * hd)
         gate = oracle.normal(903, call, n_head * hd)
@@ -35,13 +47,11 @@ def test_noalloc_decode_matches_regular_entry_point_twice(oracle):
         # sparse
         assert L.q4_gpu_kv_decode(st.h, 1, dq.data_ptr(), 0, dg.data_ptr(), want.data_ptr(), n_head, di.data_ptr(),
                                   width, width, ctx, scale)
-        assert L.q4_gpu_kv_decode_noalloc(st.h, 1, dq.data_ptr(), 0, dg.data_ptr(), got.data_ptr(), n_head,
-                                          di.data_ptr(), width, width, ctx, scale)
+        assert noalloc(st.h, 1, dq.data_ptr(), 0, dg.data_ptr(), got.data_ptr(), n_head, di.data_ptr(), width, width, ctx, scale)
         assert_close(host(got), host(want), "noalloc sparse, call %d" % call)
         # dense over all rows (many splits: exercises the clamp to the built-in scratch)
         assert L.q4_gpu_kv_decode(st.h, 1, dq.data_ptr(), 0, None, want.data_ptr(), n_head, None, 0, 0, ctx, scale)
-        assert L.q4_gpu_kv_decode_noalloc(st.h, 1, dq.data_ptr(), 0, None, got.data_ptr(), n_head, None, 0, 0, ctx,
-                                          scale)
+        assert noalloc(st.h, 1, dq.data_ptr(), 0, None, got.data_ptr(), n_head, None, 0, 0, ctx, scale)
         assert_close(host(got), host(want), "noalloc dense, call %d" % call)
         ref = oracle.attn(q, oracle.kv_write(k, 2), oracle.kv_write(v, 2), None, n_head, n_kvh, hd, 1, ctx - 1, ctx,
                           scale, 2)[0]
