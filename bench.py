@@ -45,9 +45,11 @@ SCALE = 1.0 / math.sqrt(HD)
 SEED = 20261125
 PAD = 64                              # token slots appended during the run
 L2_BYTES = 126e6
-# dram bytes per algorithmic byte of the batched decode kernel, from the ncu capture summarised in
-# profiles/ (None until a capture exists)
-DECODE_TRAFFIC_RATIO = 1.14    # profiles/decode_q8_batched_sparse.md: (79.0 + 2.1) MB dram per 71.1 MB algorithmic
+# dram bytes (read + write) per algorithmic byte of the batched decode kernel, from one ncu capture of the
+# kernel on a small case: 81.1 MB of dram traffic for 71.1 MB gathered (272-byte records are 16-byte, not
+# sector aligned); traffic grows with the rows gathered, so a full launch scales by the same ratio
+DECODE_TRAFFIC_RATIO = 1.14
+TIMED_BLOCKS = 15              # the --steps block is timed this many times; the median block is reported
 
 
 def draw_contexts(n, lo=1024, hi=131072, seed=SEED + 4):
@@ -209,21 +211,28 @@ def cpu_step(items, news, threads):
 
 
 def cpu_baseline(ctxs, budget_s, n_sessions=4):
+    """the oracle port on all host processors, and on one thread (the reference's CPU attention loop is
+    serial, src/q4_fwd.c:369-397), each on the same bounded sample"""
     from oracle import q4_oracle as oracle
     threads = max(1, oracle.host_procs())
     items, news = cpu_sample_problem(ctxs, n_sessions, SEED + 9)
-    cpu_step(items, news, threads)            # warm-up
-    t0 = time.perf_counter()
-    reps = 0
-    while reps < 3 or time.perf_counter() - t0 < budget_s:
-        cpu_step(items, news, threads)
-        reps += 1
-        if time.perf_counter() - t0 > 3 * budget_s:
-            break
-    dt = time.perf_counter() - t0
-    return {"value": n_sessions * reps / dt, "unit": "session*tok/s", "cores": threads, "kind": "port",
+
+    def run(n_threads, budget):
+        cpu_step(items, news, n_threads)            # warm-up
+        t0 = time.perf_counter()
+        reps = 0
+        while reps < 2 or time.perf_counter() - t0 < budget:
+            cpu_step(items, news, n_threads)
+            reps += 1
+            if time.perf_counter() - t0 > 3 * budget:
+                break
+        return n_sessions * reps / (time.perf_counter() - t0), reps, time.perf_counter() - t0
+    v, reps, dt = run(threads, budget_s)
+    v1, reps1, dt1 = run(1, budget_s / 2)
+    return {"value": v, "unit": "session*tok/s", "cores": threads, "kind": "port",
             "sample": "%d of the 64 sessions x 12 layers x %d reps (%.1f s); compact caches of the selected rows"
-                      % (n_sessions, reps, dt)}
+                      % (n_sessions, reps, dt),
+            "value_1_thread": v1, "sample_1_thread": "same sample, %d reps (%.1f s) on one thread" % (reps1, dt1)}
 
 
 def run_reference_arm(args, rank):
@@ -244,7 +253,7 @@ def run_reference_arm(args, rank):
     line = {"impl": "reference", "metric": "decode_attn_session_tok_per_s", "value": v, "unit": "session*tok/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "q8_0+f32",
-            "data": "synthetic", "config": workload_config(args.sessions, 1),
+            "data": "synthetic", "config": workload_config(args.sessions),
             "cpu_baseline": {"value": v, "unit": "session*tok/s", "cores": threads, "kind": "port",
                              "sample": "each step = %d of the 64 sessions x 12 layers (compact caches of the "
                                        "selected rows), all host threads" % n_s},
@@ -253,13 +262,13 @@ def run_reference_arm(args, rank):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(sessions, groups):
+def workload_config(sessions):
     return {"workload": "configs[3]: multi-session batched QSA decode, %d sessions, ctx ~ U[1024,131072], "
                         "q8_0 KV, 12 layers x (fused K/V append + sparse decode attention), 16 Q / 2 KV heads, "
                         "hd 128, 2051 selected positions per kv head" % sessions,
             "sessions": sessions, "layers": N_LAYERS, "selected_positions": WIDTH, "kv": "q8_0", "q": "bf16",
             "parallelism": "sessions sharded round-robin, no collective",
-            "l2": "rotation over %d replicas of the session group (>=512 MB of distinct rows between reuse)" % groups}
+            "l2": "rotation over replicas of the session group (>=512 MB of distinct rows between two uses of a row)"}
 
 
 # ------------------------------------------------------------------------------------------ GPU arm
@@ -371,6 +380,43 @@ def fill_store(torch, st, rows, chunk=32768):
             st.append(layer, k, v, p0, n)
 
 
+def close_enough(got, ref, extra_rel=0.0):
+    """the stated tolerance of the path: 2e-3 max-abs + 1e-3 relative against the fp32 oracle (extra_rel: one
+    bf16 rounding of the result where the output type is bf16); returns (ok, max abs error)"""
+    got, ref = np.asarray(got, np.float64).reshape(-1), np.asarray(ref, np.float64).reshape(-1)
+    err = np.abs(got - ref)
+    ok = bool(np.isfinite(got).all() and (err <= 2e-3 + (1e-3 + extra_rel) * np.abs(ref)).all())
+    return ok, float(err.max())
+
+
+def export_layer(torch, L, st, layer, rows):
+    """rows [0, rows) of one layer of a store as the reference-layout bytes the oracle reads (K, V)"""
+    out = []
+    for which in (0, 1):
+        buf = torch.empty(rows * st.token_bytes, dtype=torch.uint8, device="cuda")
+        st.export(layer, which, 0, rows, buf)
+        assert L.q4_hip_stream_sync()
+        out.append(buf.cpu().numpy())
+    return out
+
+
+def verify_decode(torch, L, st, layer, q_bf16_t, out_t, rows, idx=None, kind=2, n_kv=None):
+    """one decode result (out_t, computed from the bf16 query q_bf16_t over the store's layer) against the
+    CPU oracle on the exported cache bytes: a list of positions per kv head (idx [N_KVH][WIDTH]) or dense"""
+    from oracle import q4_oracle as oracle
+    kc, vc = export_layer(torch, L, st, layer, rows)
+    assert L.q4_hip_stream_sync()
+    torch.cuda.synchronize()
+    q = q_bf16_t.float().cpu().numpy().reshape(-1)
+    threads = max(1, oracle.host_procs())
+    if idx is not None:
+        ref = oracle.attn(q, kc, vc, None, N_HEAD, N_KVH, HD, 1, 0, rows, SCALE, kind, idx=np.ascontiguousarray(idx, np.int32),
+                          width=idx.shape[-1], idx_kvh_stride=idx.shape[-1] if idx.ndim > 1 else 0, threads=threads)[0]
+    else:
+        ref = oracle.attn(q, kc, vc, None, N_HEAD, N_KVH, HD, 1, n_kv - 1, rows, SCALE, kind, threads=threads)[0]
+    return close_enough(out_t.float().cpu().numpy(), ref)
+
+
 def timed(torch, ext, fn, reps):
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record(ext)
@@ -425,6 +471,11 @@ def extras_single_session(torch, q4gpu, L, ext, peak_gbs):
         n = 10 * R
         dt = timed(torch, ext, one, n)
         res[name] = 1e6 * dt / (n * N_LAYERS)
+    # check: one layer of one replica, recomputed outside the graph, against the oracle on the exported rows
+    L.q4_hip_pos_push(ctx)
+    st.decode(3, q[5, 3], out[3], N_HEAD, SCALE, idx=idx_d[5, 3], width=WIDTH, idx_kvh_stride=WIDTH, n_kv=0, q_bf16=True)
+    ok, err = verify_decode(torch, L, st, 3, q[5, 3], out[3], ctx + PAD, idx=idx[5, 3])
+    res["verified"], res["max_err"] = ok, err
     by = gathered_bytes(ctx)
     gbs = by / (res["us_per_layer"] * 1e-6) / 1e9
     res.update({"workload": "configs[1]: single-session QSA decode, ctx 262144, batch 1, 12 layers, graph replay, "
@@ -461,6 +512,16 @@ def extras_prefill(torch, q4gpu, L, ext, peaks):
     t_app = timed(torch, ext, app, 4 * n_layers) / (4 * n_layers)
     timed(torch, ext, att, n_layers)
     t_att = timed(torch, ext, att, 2 * n_layers) / (2 * n_layers)
+    # check: sampled queries of the last call against the oracle (bf16 result: one more rounding allowed)
+    from oracle import q4_oracle as oracle
+    lay = (2 * n_layers - 1) % n_layers
+    kc, vc = export_layer(torch, L, st, lay, base + n_tok)
+    ok, err = True, 0.0
+    for t in (0, 4097, n_tok - 1):
+        ref = oracle.attn(q[lay, t].float().cpu().numpy().reshape(-1), kc, vc, None, N_HEAD, N_KVH, HD, 1, base + t, base + n_tok,
+                          SCALE, 2, threads=max(1, oracle.host_procs()))[0]
+        o, e = close_enough(out[lay, t].float().cpu().numpy(), ref, extra_rel=2.0 ** -8)
+        ok, err = ok and o, max(err, e)
     pairs = sum(base + t + 1 for t in range(n_tok))
     flop = pairs * 4 * HD * N_HEAD
     peak_tf = float(peaks.get("bf16_tflops", 1590.0))
@@ -470,7 +531,7 @@ def extras_prefill(torch, q4gpu, L, ext, peaks):
             "append_us": t_app * 1e6, "append_gbs": 2 * n_tok * (KVW * 4 + N_KVH * ROW_BYTES) / t_app / 1e9,
             "attn_ms_per_layer": t_att * 1e3, "flop_per_layer": flop, "achieved_tflops": flop / t_att / 1e12,
             "peak_tflops_measured_bf16": peak_tf, "frac_of_measured_tensor": flop / t_att / 1e12 / peak_tf,
-            "queries_per_s": n_tok / (t_app + t_att)}
+            "queries_per_s": n_tok / (t_app + t_att), "verified": ok, "max_err": err}
 
 
 def extras_indexer(torch, q4gpu, L, ext, peak_gbs):
@@ -504,6 +565,16 @@ def extras_indexer(torch, q4gpu, L, ext, peak_gbs):
         timed(torch, ext, one, 3)
         res[name] = 1e6 * timed(torch, ext, one, 10) / (10 * N_LAYERS)
         L.q4_hip_graph_free(gr)
+    # check: the last layer's list against the oracle's selection on the oracle's scores (exact equality)
+    from oracle import q4_oracle as oracle
+    enqueue(True)
+    assert L.q4_hip_stream_sync()
+    torch.cuda.synchronize()
+    l_chk = N_LAYERS - 1
+    sc_ref = oracle.ix_score(q[l_chk].cpu().numpy(), pool[l_chk].cpu().numpy(), 1, nb, nb, n_head, pos, ratio)
+    sel_ref = oracle.ix_topk(sc_ref, 1, nb, k_blk, ratio, pos, WIDTH)[0]
+    res["verified"] = bool(np.array_equal(sel[l_chk].cpu().numpy(), sel_ref) and
+                           np.array_equal(score[l_chk].cpu().numpy().view(np.uint32), sc_ref[0].view(np.uint32)))
     # ---- the whole decode-attention step of one session at ctx 262144, selection included: per layer score,
     # select, then the fused append + sparse decode over the list just produced (one list shared by both kv
     # heads, as the reference's); 24 graphs with different indexer queries rotate so that the gathered rows
@@ -602,8 +673,9 @@ def extras_dense(torch, q4gpu, L, ext, peak_gbs, kinds=("q8_0", "f16", "f32")):
         dt = timed(torch, ext, one, n)
         by = ctx * N_KVH * rowb * 2
         us = 1e6 * dt / n
+        ok, err = verify_decode(torch, L, st, N_LAYERS - 1, q[N_LAYERS - 1], out[N_LAYERS - 1], ctx, kind=kind, n_kv=ctx)
         res[name] = {"us_per_layer": us, "bytes_per_layer": by, "achieved_gbs": by / us / 1e3,
-                     "frac_of_measured_hbm": by / us / 1e3 / peak_gbs}
+                     "frac_of_measured_hbm": by / us / 1e3 / peak_gbs, "verified": ok, "max_err": err}
         st.close()
     res["workload"] = "configs[4] on 1 GPU: dense decode over ctx 262144, 12 layers, inputs 12 x bytes_per_layer >> L2"
     return res
@@ -647,6 +719,20 @@ def extras_snapshot(torch, q4gpu, L, ext):
         t3 = time.perf_counter()
     finally:
         os.close(fd)
+    # check: the restored store (device pool, host, file: the last restore was the file's) exports the bytes it held
+    probe = torch.empty(512 * st.token_bytes, dtype=torch.uint8, device="cuda")
+    st.export(7, 1, n_kv - 512, 512, probe)
+    before = probe.clone()
+    st.save(n_kv, pool[0])
+    z = torch.zeros(512, KVW, device="cuda")
+    q4gpu.use_torch_stream()
+    st.append(7, z, z, n_kv - 512, 512)
+    torch.cuda.synchronize()
+    L.q4_gpu_set_stream(None)
+    st.restore(n_kv, pool[0])
+    st.export(7, 1, n_kv - 512, 512, probe)
+    assert L.q4_hip_stream_sync()
+    res["verified"] = bool(torch.equal(before, probe))
     res["write_fd"] = {"ms": (t1 - t0) * 1e3, "gbs": file_bytes / (t1 - t0) / 1e9, "file_bytes": file_bytes}
     res["read_fd"] = {"ms": (t3 - t2) * 1e3, "gbs": file_bytes / (t3 - t2) / 1e9}
     st.close()
@@ -685,19 +771,23 @@ def extras_sparse_prefill(torch, q4gpu, L, ext, peak_gbs):
     dt = timed(torch, ext, one, n) / n
     gathered = n_tok * N_KVH * WIDTH * 272
     distinct = int(torch.unique(idx[:, 0]).numel() + torch.unique(idx[:, 1]).numel()) * 272
+    lay = (2 * N_LAYERS - 1) % N_LAYERS
+    ok, err = verify_decode(torch, L, st, lay, q[lay, 17], out[lay, 17], ctx, idx=idx[17].cpu().numpy())
     st.close()
     return {"workload": "512 queries x 2051 rows per kv head over ctx 262144, q8_0, one launch per layer",
             "us_per_layer": dt * 1e6, "us_per_query": dt * 1e6 / n_tok, "gathered_bytes_per_layer": gathered,
             "distinct_row_bytes_per_layer": distinct, "gathered_gbs": gathered / dt / 1e9,
             "distinct_gbs": distinct / dt / 1e9, "distinct_frac_of_measured_hbm": distinct / dt / 1e9 / peak_gbs,
+            "verified": ok, "max_err": err,
             "note": "lists of neighbouring queries overlap, so most gathers hit L2; the HBM floor is the distinct rows"}
 
 
-def run_seqshard(args, torch, q4gpu, L, dist, rank, world, peak_gbs):
+def measure_seqshard(args, torch, q4gpu, L, dist, rank, world, peak_gbs):
     """configs[4]: one session at ctx 262144, dense attention; rank r owns an even contiguous slice of the
     rows and attends them; the (acc, m, l) records are exchanged and merged on every rank, either inside the
     decode kernel (peer stores over NVLink, q4_gpu_kv_decode_xchg: the product) or by an NCCL all-gather
-    plus a merge kernel (timed beside it).  One step = 12 layers; time = max over ranks, on the device."""
+    plus a merge kernel (timed beside it; the two results must agree).  One step = 12 layers; time = max over
+    ranks, on the device.  Returns {kind: {...}} (the same on every rank)."""
     from q4gpu import shard
     ctx = 262144
     b, e = shard.rows_for_rank(ctx, rank, world)
@@ -773,23 +863,133 @@ def run_seqshard(args, torch, q4gpu, L, dist, rank, world, peak_gbs):
             stream.synchronize()
             status = L.q4_gpu_last_error()
             assert status == 0, "device status %#x" % status
+            agree = None
             if world > 1:      # the two exchanges must agree (same records, same merge arithmetic up to rounding)
-                err = float((out_f - out).abs().max())
-                assert err < 2e-3, "fused exchange differs from the all-gather path: %g" % err
+                agree = float((out_f - out).abs().max())
+                assert agree < 2e-3, "fused exchange differs from the all-gather path: %g" % agree
         by = ctx * N_KVH * rowb * 2
         res[name] = {"us_per_layer": us, "us_per_layer_nccl_allgather": us_nccl, "bytes_per_layer_all_ranks": by,
                      "achieved_gbs_all_ranks": by / us / 1e3,
-                     "frac_of_measured_hbm_x_ranks": by / us / 1e3 / (peak_gbs * world)}
+                     "frac_of_measured_hbm_x_ranks": by / us / 1e3 / (peak_gbs * world),
+                     "max_abs_diff_in_kernel_vs_nccl": agree}
         st.close()
     L.q4_gpu_set_stream(None)
     xw.close()
-    if rank == 0:
-        print(json.dumps({"metric": "dense_decode_us_per_layer_ctx262144", "mode": "seqshard", "n_gpus": world,
-                          "steps": args.steps,
-                          "exchange": "in-kernel: %d B of {value, epoch} packets stored per peer per layer over NVLink, "
-                                      "polled and merged by the same launch; us_per_layer_nccl_allgather is the same step "
-                                      "with an NCCL all-gather + merge kernel" % (N_HEAD * (HD + 4) * 8),
-                          "result": res}), flush=True)
+    res["exchange"] = ("in-kernel: %d B of {value, epoch} packets stored per peer per layer over NVLink, polled and merged "
+                       "by the same launch; us_per_layer_nccl_allgather is the same step with an NCCL all-gather + merge "
+                       "kernel" % (N_HEAD * (HD + 4) * 8))
+    return res
+
+
+def measure_sessions(args, torch, q4gpu, L, dist, rank, world, local, mine, seed0, blocks, e2e=True, verify=True):
+    """Times the batched decode step of this rank's sessions (`mine`: their context lengths): `blocks` blocks of
+    --steps steps, each block bracketed by a barrier + synchronize on both sides and timed with CUDA events on
+    the library's stream, max over ranks per block; the median block is reported.  Then the same with host
+    buffers (uploads, downloads inside the timed region), then one session's output of the last step against
+    the CPU oracle.  Returns a dict; frees everything it built."""
+    step_bytes = N_LAYERS * sum(gathered_bytes(c) for c in mine)
+    groups_n = args.groups or max(2, int(math.ceil(512e6 / max(step_bytes, 1))))
+    torch.manual_seed(seed0)
+    q4gpu.use_torch_stream()
+    groups = [Group(q4gpu, torch, mine, seed0 + g) for g in range(groups_n)]
+    torch.cuda.synchronize()
+    L.q4_gpu_set_stream(None)                 # capture and timing on the library's own stream
+    ext = torch.cuda.ExternalStream(L.q4_gpu_stream())
+    for g in groups:
+        g.batch.set_pos(g.ctxs)
+        g.enqueue_layers()                    # eager once: scratch grows outside the capture
+        g.capture(L)
+    assert L.q4_hip_stream_sync()
+
+    def barrier():
+        L.q4_hip_stream_sync()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if dist is None:
+            return x
+        t = torch.tensor([x], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing
+    sampler = ClockSampler(local, "GPU-" + str(torch.cuda.get_device_properties(local).uuid)) if rank == 0 else None
+    for i in range(args.warmup):
+        groups[i % groups_n].step(L)
+    windows, block_dt = [], []
+    step_no = args.warmup
+    for blk in range(blocks):
+        barrier()
+        w0 = time.perf_counter()
+        if blk == 0:
+            torch.cuda.profiler.start()       # profilers started with capture off see one timed block only
+        base = step_no
+        dt = timed(torch, ext, lambda i: groups[(base + i) % groups_n].step(L), args.steps)
+        if blk == 0:
+            torch.cuda.profiler.stop()
+        windows.append((w0, time.perf_counter()))
+        step_no += args.steps
+        barrier()
+        block_dt.append(max_over_ranks(dt))
+    dt = float(np.median(block_dt))
+    res = {"dt": dt, "block_ms": [1e3 * x for x in block_dt], "groups": groups_n, "sessions_here": len(mine),
+           "algorithmic_bytes_per_launch": groups[0].algorithmic_bytes_per_layer()}
+    # ---- end to end: host buffers in, outputs out, every step
+    # Uploads ride the library's copy stream (q4_hip_copy_h2d) and are ordered against the compute
+    # stream with events, so the inputs of step i+1 travel while step i computes; every step's copies in
+    # and out are inside the timed region.
+    if e2e:
+        cs = torch.cuda.ExternalStream(L.q4_gpu_copy_stream())
+        ds = torch.cuda.ExternalStream(L.q4_gpu_download_stream())
+
+        def e2e_loop(n):
+            groups[0].copy_in(L, torch, cs)
+            for i in range(n):
+                if i + 1 < n and groups_n > 1:
+                    groups[(i + 1) % groups_n].copy_in(L, torch, cs)
+                groups[i % groups_n].run_e2e(L, torch, ext, ds)
+                if i + 1 < n and groups_n == 1:          # one set of device buffers: no overlap possible
+                    groups[0].copy_in(L, torch, cs)
+        e2e_loop(3)
+        e2e_dt = []
+        for blk in range(max(3, blocks // 3)):
+            barrier()
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            w0 = time.perf_counter()
+            ev0.record(ext)
+            cs.wait_event(ev0)                     # no copy starts before the clock does
+            e2e_loop(args.steps)
+            ext.wait_stream(ds)                    # the last result is on the host before the clock stops
+            ev1.record(ext)
+            ev1.synchronize()
+            windows.append((w0, time.perf_counter()))
+            barrier()
+            e2e_dt.append(max_over_ranks(ev0.elapsed_time(ev1) * 1e-3))
+        res["dt_e2e"] = float(np.median(e2e_dt))
+        res["e2e_block_ms"] = [1e3 * x for x in e2e_dt]
+        res["h2d"], res["d2h"] = groups[0].e2e_bytes()
+    res["clocks"] = sampler.stop(windows) if sampler else None
+    status = L.q4_gpu_last_error()
+    assert status == 0, "device status %#x" % status
+    # ---- check: the shortest session's output of the last step of group 0, one layer, against the oracle
+    if verify and rank == 0:
+        g = groups[0]
+        s_i = int(np.argmin(g.ctxs))
+        layer = 5
+        ok, err = verify_decode(torch, L, g.stores[s_i], layer, g.q[layer, s_i], g.out[layer, s_i], g.ctxs[s_i] + PAD,
+                                idx=g.idx_h[layer, s_i].numpy())
+        res["verified"], res["max_err"] = ok, err
+    for g in groups:
+        L.q4_hip_graph_free(g.graph)
+        g.batch.close()
+        for st in g.stores:
+            st.close()
+    groups.clear()
+    torch.cuda.empty_cache()
+    return res
 
 
 def main():
@@ -802,6 +1002,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--groups", type=int, default=0, help="replicas of the session group (0 = enough to defeat L2)")
+    ap.add_argument("--blocks", type=int, default=TIMED_BLOCKS, help="how many times the --steps block is timed (median reported)")
     ap.add_argument("--ctx-max", type=int, default=131072, help="upper end of the context-length draw (profiling: small)")
     ap.add_argument("--only", default="", choices=["", "single", "dense", "prefill", "indexer", "snapshot", "sparse_prefill"],
                     help="run just one of the ctx-262144 extras (for profiler captures)")
@@ -840,7 +1041,10 @@ def main():
     peak_src = "measured (MEASURED_PEAKS.json)" if "hbm_gbs" in peaks else "fallback 6.65 TB/s"
 
     if args.mode == "seqshard":
-        run_seqshard(args, torch, q4gpu, L, dist, rank, world, peak_gbs)
+        res = measure_seqshard(args, torch, q4gpu, L, dist, rank, world, peak_gbs)
+        if rank == 0:
+            print(json.dumps({"metric": "dense_decode_us_per_layer_ctx262144", "mode": "seqshard", "n_gpus": world,
+                              "steps": args.steps, "exchange": res.pop("exchange"), "result": res}), flush=True)
         if dist is not None:
             dist.barrier()
             dist.destroy_process_group()
@@ -862,82 +1066,34 @@ def main():
             res = extras_dense(torch, q4gpu, L, ext, peak_gbs, args.dense_kinds.split(","))
         print(json.dumps({"only": args.only, "result": res}), flush=True)
         return
+
+    # ---- headline: the sessions of the whole job, sharded round-robin over the ranks (strong scaling)
     ctxs = draw_contexts(args.sessions, hi=args.ctx_max)
     mine = [int(c) for i, c in enumerate(ctxs) if i % world == rank]
-    step_bytes = N_LAYERS * sum(gathered_bytes(c) for c in mine)
-    groups_n = args.groups or max(2, int(math.ceil(512e6 / max(step_bytes, 1))))
-    torch.manual_seed(SEED + rank)
-    q4gpu.use_torch_stream()
-    groups = [Group(q4gpu, torch, mine, SEED + 100 * rank + g) for g in range(groups_n)]
-    torch.cuda.synchronize()
-    L.q4_gpu_set_stream(None)                 # capture and timing on the library's own stream
-    ext = torch.cuda.ExternalStream(L.q4_gpu_stream())
-    for g in groups:
-        g.batch.set_pos(g.ctxs)
-        g.enqueue_layers()                    # eager once: scratch grows outside the capture
-        g.capture(L)
-    assert L.q4_hip_stream_sync()
-
-    def barrier():
-        L.q4_hip_stream_sync()
-        torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def max_over_ranks(x):
-        if dist is None:
-            return x
-        t = torch.tensor([x], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    # ---- device-resident timing
-    sampler = ClockSampler(local, "GPU-" + str(torch.cuda.get_device_properties(local).uuid)) if rank == 0 else None
-    for i in range(args.warmup):
-        groups[i % groups_n].step(L)
-    barrier()
-    windows = []
-    w0 = time.perf_counter()
-    torch.cuda.profiler.start()               # profilers started with capture off see the timed steps only
-    dt = timed(torch, ext, lambda i: groups[i % groups_n].step(L), args.steps)
-    torch.cuda.profiler.stop()
-    windows.append((w0, time.perf_counter()))
-    barrier()
-    dt = max_over_ranks(dt)
-    # ---- end to end: host buffers in, outputs out, every step
-    # Uploads ride the library's copy stream (q4_hip_copy_h2d) and are ordered against the compute
-    # stream with events, so the inputs of step i+1 travel while step i computes; every step's copies in
-    # and out are inside the timed region.
-    cs = torch.cuda.ExternalStream(L.q4_gpu_copy_stream())
-    ds = torch.cuda.ExternalStream(L.q4_gpu_download_stream())
-
-    def e2e_loop(n):
-        groups[0].copy_in(L, torch, cs)
-        for i in range(n):
-            if i + 1 < n and groups_n > 1:
-                groups[(i + 1) % groups_n].copy_in(L, torch, cs)
-            groups[i % groups_n].run_e2e(L, torch, ext, ds)
-            if i + 1 < n and groups_n == 1:          # one set of device buffers: no overlap possible
-                groups[0].copy_in(L, torch, cs)
-    e2e_loop(3)
-    barrier()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    w0 = time.perf_counter()
-    ev0.record(ext)
-    cs.wait_event(ev0)                     # no copy starts before the clock does
-    e2e_loop(args.steps)
-    ext.wait_stream(ds)                    # the last result is on the host before the clock stops
-    ev1.record(ext)
-    ev1.synchronize()
-    windows.append((w0, time.perf_counter()))
-    dt_e2e = ev0.elapsed_time(ev1) * 1e-3
-    barrier()
-    dt_e2e = max_over_ranks(dt_e2e)
-    clocks = sampler.stop(windows) if sampler else None
-
-    status = L.q4_gpu_last_error()
-    assert status == 0, "device status %#x" % status
+    m = measure_sessions(args, torch, q4gpu, L, dist, rank, world, local, mine, SEED + 100 * rank, args.blocks)
+    dt, dt_e2e = m["dt"], m["dt_e2e"]
+    extras = {}
+    if world > 1 and not args.no_extras:
+        # weak scaling beside it: the full 64-session batch on EVERY rank (own contexts per rank), so the curve
+        # separates the fixed per-launch time (which strong scaling of 64 sessions runs into) from anything else
+        wctx = [int(c) for c in draw_contexts(args.sessions, hi=args.ctx_max, seed=SEED + 4 + 1000 * (rank + 1))]
+        w = measure_sessions(args, torch, q4gpu, L, dist, rank, world, local, wctx, SEED + 7000 + 100 * rank,
+                             max(3, args.blocks // 3), e2e=False, verify=False)
+        extras["weak_scaling"] = {"scaling": "weak", "sessions_per_gpu": args.sessions, "n_gpus": world,
+                                  "value": world * args.sessions * args.steps / w["dt"], "unit": "session*tok/s",
+                                  "ms_per_step": 1e3 * w["dt"] / args.steps,
+                                  "us_per_launch": 1e6 * w["dt"] / (args.steps * N_LAYERS)}
+        # configs[4]: the sequence-sharded dense decode on the same ranks
+        seq = measure_seqshard(args, torch, q4gpu, L, dist, rank, world, peak_gbs)
+        if rank == 0:          # the one-GPU figure beside it, while the other ranks wait
+            one = extras_dense(torch, q4gpu, L, torch.cuda.ExternalStream(L.q4_gpu_stream()), peak_gbs)
+            for kname in ("q8_0", "f16", "f32"):
+                if kname in seq and kname in one:
+                    seq[kname]["us_per_layer_1_gpu"] = one[kname]["us_per_layer"]
+                    seq[kname]["verified_1_gpu"] = one[kname]["verified"]
+        dist.barrier()
+        seq["workload"] = "configs[4]: one session, ctx 262144, dense attention, rows sharded evenly over %d GPUs" % world
+        extras["seqshard_ctx262144"] = seq
     if rank != 0:
         if dist is not None:
             dist.barrier()
@@ -947,33 +1103,32 @@ def main():
     # ---- roofline of the dominant kernel.  A step is 12 launches of one kernel (append fused into the sparse
     # decode), so its average launch duration is the device-timed region divided by the launches in it.
     dt_dec = dt / (args.steps * N_LAYERS)
-    alg = groups[0].algorithmic_bytes_per_layer()
+    alg = m["algorithmic_bytes_per_launch"]
     achieved = alg / dt_dec / 1e9
     roofline = {"kernel": "q4_decode_k<q8_0 records, hd 128> (fused append + batched sparse decode, %d sessions per launch)" % len(mine),
                 "bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
                 "peak_source": peak_src, "algorithmic_bytes_per_launch": alg, "us_per_launch": dt_dec * 1e6,
                 "traffic": (alg * DECODE_TRAFFIC_RATIO) if DECODE_TRAFFIC_RATIO else None}
-    h2d, d2h = groups[0].e2e_bytes()
     line = {"metric": "decode_attn_session_tok_per_s", "value": args.sessions * args.steps / dt,
             "unit": "session*tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "q8_0 KV, f16 tensor-core products, f32 accumulate", "data": "synthetic",
-            "config": workload_config(args.sessions, groups_n),
+            "config": workload_config(args.sessions), "l2_replicas": m["groups"],
+            "timing": {"blocks": len(m["block_ms"]), "steps_per_block": args.steps, "reported": "median block",
+                       "block_ms_min": min(m["block_ms"]), "block_ms_max": max(m["block_ms"]),
+                       "e2e_blocks": len(m["e2e_block_ms"])},
             "e2e": {"value": args.sessions * args.steps / dt_e2e, "unit": "session*tok/s",
-                    "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
+                    "h2d_bytes_per_step": m["h2d"] * world, "d2h_bytes_per_step": m["d2h"] * world,
                     "ms_per_step": 1e3 * dt_e2e / args.steps},
-            "gpu_launches": args.steps * N_LAYERS * world, "clocks": clocks, "roofline": roofline,
+            "gpu_launches": args.steps * N_LAYERS * world, "clocks": m["clocks"], "roofline": roofline,
             "us_per_layer": 1e6 * dt / (args.steps * N_LAYERS),
             "attn_roofline_session_tok_per_s": args.sessions / (N_LAYERS * sum(gathered_bytes(c) for c in ctxs)
                                                                 / world / (peak_gbs * 1e9))}
-    for g in groups:
-        L.q4_hip_graph_free(g.graph)
-        g.batch.close()
-        for st in g.stores:
-            st.close()
-    groups.clear()
-    torch.cuda.empty_cache()
+    checks = {"headline": {"verified": m.get("verified"), "max_err": m.get("max_err"),
+                           "what": "one session x one layer of the last step against the CPU oracle on the exported cache"}}
+    line.update(extras)
     if world == 1 and not args.no_extras:
+        ext = torch.cuda.ExternalStream(L.q4_gpu_stream())
         line["single_session_ctx262144"] = extras_single_session(torch, q4gpu, L, ext, peak_gbs)
         line["dense_ctx262144"] = extras_dense(torch, q4gpu, L, ext, peak_gbs)
         line["prefill_8192_over_16384"] = extras_prefill(torch, q4gpu, L, ext, peaks)
@@ -981,6 +1136,15 @@ def main():
         line["sparse_prefill_512_ctx262144"] = extras_sparse_prefill(torch, q4gpu, L, ext, peak_gbs)
         line["session_snapshot"] = extras_snapshot(torch, q4gpu, L, ext)
         line["cpu_baseline"] = cpu_baseline(ctxs, args.cpu_seconds)
+        for name in ("single_session_ctx262144", "prefill_8192_over_16384", "indexer_ctx262144", "sparse_prefill_512_ctx262144",
+                     "session_snapshot"):
+            checks[name] = {"verified": line[name].get("verified"), "max_err": line[name].get("max_err")}
+        for kname in ("q8_0", "f16", "f32"):
+            d = line["dense_ctx262144"].get(kname)
+            if d:
+                checks["dense_ctx262144/" + kname] = {"verified": d["verified"], "max_err": d["max_err"]}
+    line["checks"] = checks
+    line["verified"] = all(c["verified"] is True for c in checks.values())
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()

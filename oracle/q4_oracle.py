@@ -20,8 +20,10 @@ i32p = C.POINTER(C.c_int32)
 u16p = C.POINTER(C.c_uint16)
 
 
-def build(ref_tree="/root/reference"):
-    """make -C oracle: the restatement always, _ref only when the reference tree is present."""
+def build(ref_tree=None):
+    """make -C oracle: the restatement always; the reference's own dequantiser and quantiser (oracle/_ref)
+    only when a reference tree is given (argument, or the Q4_REF_TREE environment variable) and present."""
+    ref_tree = ref_tree or os.environ.get("Q4_REF_TREE", "")
     subprocess.run(["make", "-C", _HERE, "REF=" + ref_tree], check=True,
                    stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
 
@@ -95,6 +97,31 @@ def ref_lib():
         R.q4_dequant_row.argtypes = [C.c_uint32, C.c_void_p, C.c_uint64, C.c_void_p]
         _REF = R
     return _REF
+
+
+_REFQ = None
+
+
+def ref_quant_lib():
+    """The reference's own q8_0 quantiser (the body of f32_to_q8_k, src/q4_rocm.cu:7221-7238, compiled for
+    the host); None when it was never built."""
+    global _REFQ
+    if _REFQ is None:
+        path = os.path.join(_HERE, "_ref", "libq4refquant.so")
+        if not os.path.exists(path):
+            return None
+        R = C.CDLL(path)
+        R.q4ref_f32_to_q8.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64]
+        _REFQ = R
+    return _REFQ
+
+
+def ref_quant_q8_0(x):
+    x = np.ascontiguousarray(x, np.float32)
+    assert x.size % 32 == 0
+    out = np.empty(x.size // 32 * 34, np.uint8)
+    ref_quant_lib().q4ref_f32_to_q8(_p(x), _p(out), x.size // 32)
+    return out
 
 
 Q4_T_Q8_0 = 8  # src/q4.h:26

@@ -121,6 +121,37 @@ def test_quantiser_contract(oracle):
         assert ok[2:].all()
 
 
+def test_quantiser_matches_the_reference_source_compiled_in_place(oracle):
+    """q4o_quant_q8_0 against the reference's own quantiser -- the body of f32_to_q8_k cut out of
+    src/q4_rocm.cu:7221-7238 at build time and compiled for the host (oracle/Makefile, ref_quant_shim.c) --
+    bit for bit on 2 Mi blocks of N(0,1) values at several magnitudes and on the edge cases: all-zero blocks,
+    scales below the fp16 range, +-amax, ties of rint at .5, fp16 scale overflow to infinity."""
+    if oracle.ref_quant_lib() is None:
+        pytest.skip("oracle/_ref/libq4refquant.so not built (no reference tree)")
+    rng = np.random.default_rng(2026)
+    n_blocks = 1 << 21
+    x = rng.standard_normal(n_blocks * 32, dtype=np.float32)
+    x.reshape(-1, 32)[1::4] *= np.float32(1e-3)
+    x.reshape(-1, 32)[2::4] *= np.float32(37.0)
+    x.reshape(-1, 32)[3::4] *= rng.uniform(0, 50, (n_blocks // 4, 1)).astype(np.float32)
+    e = x[:32 * 16].reshape(16, 32)
+    e[0] = 0.0
+    e[1] = np.float32(1e-9) * np.arange(32)
+    e[2] = 0.0; e[2, 5] = -3.0
+    e[3] = np.float32(1e-40)                                   # denormal inputs
+    e[4] = np.arange(32, dtype=np.float32) - 15.5              # x * id lands on .5 ties
+    e[5] = 127.0; e[5, 1:] = np.arange(31, dtype=np.float32) + 0.5
+    e[6] = np.float32(9e6)                                     # d = 70866 > fp16 max: scale rounds to infinity
+    e[7] = np.float32(-65504.0 * 127.0)
+    e[8] = np.float32(2.0 ** -24 * 127.0)                      # d is the smallest fp16 denormal
+    e[9] = np.float32(2.0 ** -25 * 127.0)                      # d halfway to it: ties to even -> 0
+    got = oracle.quant_q8_0(x)
+    want = oracle.ref_quant_q8_0(x)
+    assert got.shape == want.shape
+    bad = np.nonzero(got != want)[0]
+    assert bad.size == 0, "first differing byte %d (block %d)" % (bad[0], bad[0] // 34)
+
+
 def test_rope_and_prep(oracle):
     hd, n_rot, base = 128, 128, 1e7
     x = oracle.normal(5, 1, hd)
