@@ -233,13 +233,64 @@ uint64_t q4_gpu_kv_snapshot_bytes(const q4_gpu_kv *kv, uint32_t n_kv);
 bool q4_gpu_kv_save(const q4_gpu_kv *kv, uint32_t n_kv, void *buf, int host);
 bool q4_gpu_kv_restore(q4_gpu_kv *kv, uint32_t n_kv, const void *buf, int host);
 
-/* The KV section of the reference's session file, streamed to / from a file descriptor positioned by
- * the caller: for every layer the K rows [0, n_kv) then the V rows, in the reference layout
- * (src/q4_fwd.c:2353-2360 save, :2437-2445 restore; the header, ids and the other state stay with the
- * host).  Conversion on the device, double-buffered pinned staging.  Blocking; returns false on a
- * short file or I/O error. */
+/* The KV section of the reference's session file, streamed to / from a file descriptor at its current
+ * position (which ends up behind the section): for every layer the K rows [0, n_kv) then the V rows, in
+ * the reference layout (src/q4_fwd.c:2353-2360 save, :2437-2445 restore).  Rows are converted on the
+ * device and pass through pinned staging buffers; a seekable descriptor is written / read by several I/O
+ * threads at once (pwrite / pread at precomputed offsets, $Q4_SESS_IO_THREADS), a pipe or socket in order.
+ * Blocking; returns false on a short file or I/O error, and a regular file that is too short is refused
+ * before any row is applied. */
 bool q4_gpu_kv_write_fd(const q4_gpu_kv *kv, uint32_t n_kv, int fd);
 bool q4_gpu_kv_read_fd(q4_gpu_kv *kv, uint32_t n_kv, int fd);
+
+/* ---- the whole session file, format version 5 (q4_sess_save / q4_sess_restore / q4_sess_peek_ids and
+ * q4_sess_hdr, src/q4_fwd.c:2256-2477, 2636-2657).  The store supplies the KV section and the header
+ * fields it knows (max_kv, n_kv, number of attention layers, row width, KV kind tag); everything else is
+ * the host's and travels through this descriptor: header fields, token ids, and the state sections as
+ * opaque host bytes in file order.  A file written by q4_gpu_sess_file_write is byte for byte what the
+ * reference host writes for the same state, and the other way round.
+ *   state_a : last residual + PLE convolution state, 11 * hc_dim floats                  (:2345-2347)
+ *   state_b : recurrent-layer state n_gdn*n_v_h*d_v*d_v floats + convolution history
+ *             n_gdn*conv_hist*conv_ch floats                                             (:2357-2362)
+ *   idx_raw : the indexer's fp16 raw keys, n_layers * n_kv * idx_dim * 2 bytes in layer order, or NULL
+ *             (the file then records "no keys")                                          (:2363-2372)
+ * The sizes must be exactly what the header dimensions imply, else the call is rejected. */
+typedef struct q4_gpu_sess_desc {
+    uint64_t bytes_total;                 /* model guard */
+    uint32_t n_layer, n_expert;
+    uint32_t pos;                         /* written from / restored into */
+    uint32_t n_gdn, n_v_h, d_v, conv_hist, conv_ch, hc_dim;
+    uint32_t prompt_n, nmsg;
+    uint64_t user_hash;
+    const int32_t *ids;                   /* write: the ids that produced the state; read: not used (see `ids` argument) */
+    uint32_t n_ids;                       /* write: their count; read: set to the saved count */
+    int32_t ple_hist[8];
+    void *state_a;
+    uint64_t state_a_bytes;
+    void *state_b;
+    uint64_t state_b_bytes;
+    uint32_t idx_dim;
+    uint32_t idx_has_raw;                 /* read: 1 if the file carried raw keys (copied to idx_raw) */
+    void *idx_raw;
+    uint64_t idx_raw_bytes;               /* write: exact size; read: capacity of idx_raw */
+} q4_gpu_sess_desc;
+/* Size of the file q4_gpu_sess_file_write would produce. */
+uint64_t q4_gpu_sess_file_bytes(const q4_gpu_kv *kv, uint32_t n_kv, const q4_gpu_sess_desc *d);
+/* q4_sess_save: writes "<path>.tmp" and renames it over path, so a reader never sees a torn file; on any
+ * failure the temporary file is removed and false is returned. */
+bool q4_gpu_sess_file_write(const q4_gpu_kv *kv, uint32_t n_kv, const q4_gpu_sess_desc *d, const char *path);
+/* q4_sess_restore: returns the saved prefix length when the file is accepted (rows [0, n_kv) of every
+ * layer restored into the store, state sections copied into the descriptor's buffers, pos / prompt_n / nmsg /
+ * user_hash / ple_hist / n_ids set), else 0.  Accepted only if magic, version, model guard and every
+ * dimension match, max_kv and the KV kind are those of the store (the rows are raw: :2405-2408), the file
+ * holds exactly n_kv == n_ids rows, n_ids <= the caller's n_ids and every saved id equals ids[i] (exact
+ * prefix: :2417-2432).  The file's length is checked before anything is applied; after a failure in the
+ * middle of the KV section the store's rows are unspecified, as in the reference (which resets the session). */
+int q4_gpu_sess_file_read(q4_gpu_kv *kv, q4_gpu_sess_desc *d, const int32_t *ids, int n_ids, const char *path);
+/* q4_sess_peek_ids: the saved ids and prompt metadata without touching any state; -1 if the file is not a
+ * version-5 session of this model (bytes_total, n_layer, n_expert of `model`) or holds more than max_ids. */
+int q4_gpu_sess_file_peek_ids(const q4_gpu_sess_desc *model, const char *path, int32_t *ids, int max_ids,
+                              uint32_t *prompt_n, uint32_t *nmsg, uint64_t *user_hash);
 
 /* ---- decode attention over a store.  One launch covers every kv head and query head of the
  * layer (split-KV over the position list, merged by the last block to finish).

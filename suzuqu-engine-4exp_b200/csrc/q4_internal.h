@@ -119,8 +119,9 @@ struct q4_gpu_xchg {
 /* wait-and-merge half alone (q4_decode.cu): the records of the latest push on every rank -> out */
 bool q4i_xchg_merge(const q4_gpu_xchg *x, const float *gate, float *out);
 
-/* frees the prefill staging buffer (q4_prefill.cu); called at shutdown */
+/* frees the prefill staging buffer (q4_prefill.cu) / the session-file staging (q4_sess.cu); called at shutdown */
 void q4i_prefill_release();
+void q4i_sess_release();
 
 /* decode attention launcher (q4_decode.cu) */
 struct Q4DecodeArgs {

@@ -722,119 +722,3 @@ extern "C" bool q4_gpu_kv_append_decode_d(q4_gpu_kv *kv, uint32_t layer, const f
     if (fused) { a.new_k = k; a.new_v = v; }
     return q4i_decode(a);
 }
-
-/* ======================================================================= snapshot to a file == */
-/* The KV section of the reference's session file (q4_sess_save / q4_sess_restore,
- * src/q4_fwd.c:2353-2360,2437-2445): for every layer, the K rows [0, n_kv) then the V rows, in the
- * reference layout.  Rows are converted on the device into a staging buffer and moved through two
- * pinned host buffers, so the device->host copy of one chunk overlaps the write() of the previous one
- * (the reference does a synchronous 16 MiB d2h + fwrite loop, :2276-2284). */
-#include <unistd.h>
-
-namespace {
-constexpr size_t SNAP_CHUNK = (size_t)16 << 20;
-
-struct SnapBufs {
-    uint8_t *dev = nullptr, *host[2] = {nullptr, nullptr};
-    cudaEvent_t ev[2] = {nullptr, nullptr};
-    bool ok = false;
-    SnapBufs() {
-        ok = cudaMalloc(&dev, 2 * SNAP_CHUNK) == cudaSuccess && cudaMallocHost(&host[0], SNAP_CHUNK) == cudaSuccess &&
-             cudaMallocHost(&host[1], SNAP_CHUNK) == cudaSuccess && cudaEventCreate(&ev[0]) == cudaSuccess &&
-             cudaEventCreate(&ev[1]) == cudaSuccess;
-    }
-    ~SnapBufs() {
-        if (dev) cudaFree(dev);
-        for (int i = 0; i < 2; i++) {
-            if (host[i]) cudaFreeHost(host[i]);
-            if (ev[i]) cudaEventDestroy(ev[i]);
-        }
-    }
-};
-bool write_all(int fd, const uint8_t *p, size_t n) {
-    while (n) {
-        ssize_t w = write(fd, p, n);
-        if (w <= 0) return false;
-        p += w;
-        n -= (size_t)w;
-    }
-    return true;
-}
-bool read_all(int fd, uint8_t *p, size_t n) {
-    while (n) {
-        ssize_t r = read(fd, p, n);
-        if (r <= 0) return false;
-        p += r;
-        n -= (size_t)r;
-    }
-    return true;
-}
-uint32_t ref_token_bytes(const q4_gpu_kv *kv) {
-    const uint32_t kvw = kv->n_kvh * kv->hd;
-    return kv->kind == Q4K_Q8 ? kvw / 32u * 34u : kvw * (kv->kind == Q4K_F16 ? 2u : 4u);
-}
-}  // namespace
-
-extern "C" bool q4_gpu_kv_write_fd(const q4_gpu_kv *kv, uint32_t n_kv, int fd) {
-    if (!g_q4.ok) return q4i_fail(Q4E_INIT, "kv_write_fd: library not initialised");
-    Q4_REQUIRE(kv && n_kv && n_kv <= kv->max_kv && fd >= 0 && !g_q4.capturing, "kv_write_fd: bad argument");
-    SnapBufs B;
-    if (!B.ok) return q4i_fail(Q4E_CUDA, "kv_write_fd: staging allocation failed");
-    const uint32_t tb = ref_token_bytes(kv);
-    const uint32_t rows_per_chunk = (uint32_t)(SNAP_CHUNK / tb);
-    size_t pending[2] = {0, 0};
-    int slot = 0;
-    bool ok = true;
-    for (uint32_t layer = 0; layer < kv->n_layers && ok; layer++)
-        for (int which = 0; which < 2 && ok; which++)
-            for (uint32_t t0 = 0; t0 < n_kv && ok; t0 += rows_per_chunk) {
-                const uint32_t n = n_kv - t0 < rows_per_chunk ? n_kv - t0 : rows_per_chunk;
-                if (pending[slot]) {   /* this slot's previous chunk: wait for its copy, then write it */
-                    ok = cudaEventSynchronize(B.ev[slot]) == cudaSuccess && write_all(fd, B.host[slot], pending[slot]);
-                    pending[slot] = 0;
-                    if (!ok) break;
-                }
-                uint8_t *stage = B.dev + (size_t)slot * SNAP_CHUNK;
-                ok = q4_gpu_kv_export(kv, layer, which, t0, n, stage) &&
-                     cudaMemcpyAsync(B.host[slot], stage, (size_t)n * tb, cudaMemcpyDeviceToHost, g_q4.stream) == cudaSuccess &&
-                     cudaEventRecord(B.ev[slot], g_q4.stream) == cudaSuccess;
-                pending[slot] = (size_t)n * tb;
-                slot ^= 1;
-            }
-    for (int i = 0; i < 2 && ok; i++, slot ^= 1)   /* drain in order: the older chunk first */
-        if (pending[slot]) {
-            ok = cudaEventSynchronize(B.ev[slot]) == cudaSuccess && write_all(fd, B.host[slot], pending[slot]);
-            pending[slot] = 0;
-        }
-    (void)cudaStreamSynchronize(g_q4.stream);
-    return ok ? true : q4i_fail(Q4E_CUDA, "kv_write_fd: copy or write failed");
-}
-
-extern "C" bool q4_gpu_kv_read_fd(q4_gpu_kv *kv, uint32_t n_kv, int fd) {
-    if (!g_q4.ok) return q4i_fail(Q4E_INIT, "kv_read_fd: library not initialised");
-    Q4_REQUIRE(kv && n_kv && n_kv <= kv->max_kv && fd >= 0 && !g_q4.capturing, "kv_read_fd: bad argument");
-    SnapBufs B;
-    if (!B.ok) return q4i_fail(Q4E_CUDA, "kv_read_fd: staging allocation failed");
-    const uint32_t tb = ref_token_bytes(kv);
-    const uint32_t rows_per_chunk = (uint32_t)(SNAP_CHUNK / tb);
-    int slot = 0;
-    bool used[2] = {false, false};
-    bool ok = true;
-    for (uint32_t layer = 0; layer < kv->n_layers && ok; layer++)
-        for (int which = 0; which < 2 && ok; which++)
-            for (uint32_t t0 = 0; t0 < n_kv && ok; t0 += rows_per_chunk) {
-                const uint32_t n = n_kv - t0 < rows_per_chunk ? n_kv - t0 : rows_per_chunk;
-                if (used[slot]) ok = cudaEventSynchronize(B.ev[slot]) == cudaSuccess;   /* slot's last import done */
-                if (!ok) break;
-                ok = read_all(fd, B.host[slot], (size_t)n * tb);   /* a short file fails here: nothing is half-applied silently */
-                if (!ok) break;
-                uint8_t *stage = B.dev + (size_t)slot * SNAP_CHUNK;
-                ok = cudaMemcpyAsync(stage, B.host[slot], (size_t)n * tb, cudaMemcpyHostToDevice, g_q4.stream) == cudaSuccess &&
-                     q4_gpu_kv_import(kv, layer, which, t0, n, stage) &&
-                     cudaEventRecord(B.ev[slot], g_q4.stream) == cudaSuccess;
-                used[slot] = true;
-                slot ^= 1;
-            }
-    (void)cudaStreamSynchronize(g_q4.stream);
-    return ok ? true : q4i_fail(Q4E_CUDA, "kv_read_fd: short file, read error or copy failure");
-}

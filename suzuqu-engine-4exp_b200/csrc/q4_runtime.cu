@@ -95,6 +95,7 @@ extern "C" void q4_hip_shutdown(void) {
     if (g_q4.pos_d) cudaFree(g_q4.pos_d);
     if (g_q4.pos_h) cudaFreeHost(g_q4.pos_h);
     q4i_prefill_release();
+    q4i_sess_release();
     if (g_q4.err_d) cudaFree(g_q4.err_d);
     if (g_q4.own_stream) cudaStreamDestroy(g_q4.own_stream);
     if (g_q4.copy_stream) cudaStreamDestroy(g_q4.copy_stream);

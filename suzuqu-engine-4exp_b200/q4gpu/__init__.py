@@ -58,6 +58,10 @@ SIGNATURES = {
     "q4_gpu_kv_snapshot_bytes": (_u64, [_v, _u32]),
     "q4_gpu_kv_save": (_b, [_v, _u32, _v, _i]), "q4_gpu_kv_restore": (_b, [_v, _u32, _v, _i]),
     "q4_gpu_kv_write_fd": (_b, [_v, _u32, _i]), "q4_gpu_kv_read_fd": (_b, [_v, _u32, _i]),
+    "q4_gpu_sess_file_bytes": (_u64, [_v, _u32, _v]),
+    "q4_gpu_sess_file_write": (_b, [_v, _u32, _v, C.c_char_p]),
+    "q4_gpu_sess_file_read": (_i, [_v, _v, _v, _i, C.c_char_p]),
+    "q4_gpu_sess_file_peek_ids": (_i, [_v, C.c_char_p, _v, _i, _v, _v, _v]),
     "q4_gpu_kv_decode": (_b, [_v, _u32, _v, _i, _v, _v, _u32, _v, _u32, _u32, _u32, _f]),
     "q4_gpu_kv_decode_noalloc": (_b, [_v, _u32, _v, _i, _v, _v, _u32, _v, _u32, _u32, _u32, _f]),
     "q4_gpu_kv_decode_idx_n": (_b, [_v, _u32, _v, _i, _v, _v, _u32, _v, _u32, _u32, _u32, _u32, _f]),
@@ -83,6 +87,17 @@ SIGNATURES = {
     "q4_gpu_batch_append_decode": (_b, [_v, _u32, _v, _v, _v, _i, _v, _v, _v, _u32, _u32, _u32, _u32, _f]),
     "q4_gpu_kv_append_decode_d": (_b, [_v, _u32, _v, _v, _v, _i, _v, _v, _u32, _v, _u32, _u32, _f]),
 }
+
+class SessDesc(C.Structure):
+    """q4_gpu_sess_desc of include/q4_gpu.h: the host's part of a version-5 session file"""
+    _fields_ = [("bytes_total", C.c_uint64), ("n_layer", C.c_uint32), ("n_expert", C.c_uint32), ("pos", C.c_uint32),
+                ("n_gdn", C.c_uint32), ("n_v_h", C.c_uint32), ("d_v", C.c_uint32), ("conv_hist", C.c_uint32),
+                ("conv_ch", C.c_uint32), ("hc_dim", C.c_uint32), ("prompt_n", C.c_uint32), ("nmsg", C.c_uint32),
+                ("user_hash", C.c_uint64), ("ids", C.c_void_p), ("n_ids", C.c_uint32), ("ple_hist", C.c_int32 * 8),
+                ("state_a", C.c_void_p), ("state_a_bytes", C.c_uint64), ("state_b", C.c_void_p),
+                ("state_b_bytes", C.c_uint64), ("idx_dim", C.c_uint32), ("idx_has_raw", C.c_uint32),
+                ("idx_raw", C.c_void_p), ("idx_raw_bytes", C.c_uint64)]
+
 
 _lib = None
 
@@ -192,6 +207,14 @@ class KVStore:
 
     def read_fd(self, n_kv, fd):
         check(self.L.q4_gpu_kv_read_fd(self.h, n_kv, fd), "q4_gpu_kv_read_fd")
+
+    def sess_file_write(self, n_kv, desc, path):
+        """the whole version-5 session file (q4_sess_save); desc: SessDesc"""
+        check(self.L.q4_gpu_sess_file_write(self.h, n_kv, C.byref(desc), os.fsencode(path)), "q4_gpu_sess_file_write")
+
+    def sess_file_read(self, desc, ids, path):
+        """q4_sess_restore: the saved prefix length, or 0 when the file is refused; ids: int32 numpy array"""
+        return self.L.q4_gpu_sess_file_read(self.h, C.byref(desc), ids.ctypes.data, len(ids), os.fsencode(path))
 
     def decode(self, layer, q, out, n_head, scale, gate=None, idx=None, width=0, idx_kvh_stride=0,
                n_kv=0, q_bf16=False):
