@@ -795,8 +795,10 @@ def measure_seqshard(args, torch, q4gpu, L, dist, rank, world, peak_gbs):
     res = {}
     stream = torch.cuda.Stream()
     xw = q4gpu.Exchange(rank, world, N_HEAD, N_KVH, HD)
+    comm = None
     if world > 1:
         xw.attach_all(dist)
+        comm = q4gpu.Comm(rank, world, dist)
     for name, kind, rowb in (("q8_0", 2, 136), ("f16", 1, 256), ("f32", 0, 512)):
         if name not in args.dense_kinds.split(","):
             continue
@@ -857,7 +859,16 @@ def measure_seqshard(args, torch, q4gpu, L, dist, rank, world, peak_gbs):
                     dt = float(t.item())
                 return 1e6 * dt / (args.steps * N_LAYERS)
 
+            def step_comm():
+                # the library's own communicator (q4_gpu_comm_*): all-gather + merge behind one C call per layer
+                for layer in range(N_LAYERS):
+                    st.decode_partial(layer, q[layer], part[layer], N_HEAD, SCALE, n_kv=rows, q_bf16=True)
+                    comm.allgather_merge(part[layer], parts_all[layer], N_HEAD, HD, out_c[layer])
+
             out_f = torch.zeros_like(out)
+            out_c = torch.zeros_like(out)
+            parts_all = torch.empty(N_LAYERS, world, N_HEAD, HD + 2, device="cuda")
+            us_comm = time_graph(step_comm) if world > 1 else None
             us_nccl = time_graph(step_nccl) if world > 1 else None
             us = time_graph(step_fused)
             stream.synchronize()
@@ -865,19 +876,22 @@ def measure_seqshard(args, torch, q4gpu, L, dist, rank, world, peak_gbs):
             assert status == 0, "device status %#x" % status
             agree = None
             if world > 1:      # the two exchanges must agree (same records, same merge arithmetic up to rounding)
-                agree = float((out_f - out).abs().max())
-                assert agree < 2e-3, "fused exchange differs from the all-gather path: %g" % agree
+                agree = max(float((out_f - out).abs().max()), float((out_c - out).abs().max()))
+                assert agree < 2e-3, "the exchanges differ: %g" % agree
         by = ctx * N_KVH * rowb * 2
-        res[name] = {"us_per_layer": us, "us_per_layer_nccl_allgather": us_nccl, "bytes_per_layer_all_ranks": by,
+        res[name] = {"us_per_layer": us, "us_per_layer_nccl_allgather": us_nccl, "us_per_layer_library_nccl": us_comm,
+                     "bytes_per_layer_all_ranks": by,
                      "achieved_gbs_all_ranks": by / us / 1e3,
                      "frac_of_measured_hbm_x_ranks": by / us / 1e3 / (peak_gbs * world),
                      "max_abs_diff_in_kernel_vs_nccl": agree}
         st.close()
     L.q4_gpu_set_stream(None)
     xw.close()
+    if comm is not None:
+        comm.close()
     res["exchange"] = ("in-kernel: %d B of {value, epoch} packets stored per peer per layer over NVLink, polled and merged "
-                       "by the same launch; us_per_layer_nccl_allgather is the same step with an NCCL all-gather + merge "
-                       "kernel" % (N_HEAD * (HD + 4) * 8))
+                       "by the same launch; us_per_layer_nccl_allgather is the same step with torch.distributed's NCCL all-gather + "
+                       "the merge kernel, us_per_layer_library_nccl with the library's own communicator (q4_gpu_comm_*)" % (N_HEAD * (HD + 4) * 8))
     return res
 
 

@@ -375,6 +375,21 @@ bool q4_gpu_xchg_set_timeout_ms(q4_gpu_xchg *x, uint32_t ms);
 bool q4_gpu_kv_decode_xchg(const q4_gpu_kv *kv, q4_gpu_xchg *x, uint32_t layer, const void *q, int q_bf16,
                            const float *gate, float *out, uint32_t n_kv, float scale, int phase);
 
+/* ---- the same exchange as a collective: NCCL all-gather of the ranks' records + merge.  No counterpart in
+ * the reference (one GPU, no collective); the merge is gqa_dec_comb_k's (src/q4_rocm.cu:6968-7012).  The
+ * communicator comes from a 128-byte unique id made on one rank (q4_gpu_comm_unique_id) and handed to the
+ * others by the host over any channel; one process per GPU.  NCCL is loaded at run time (libnccl.so.2, or
+ * $Q4_NCCL_LIB): the library does not link it, and a host that never calls these never loads it.
+ *   allgather_merge: part [n_head][hd+2] (from q4_gpu_kv_decode_partial) -> parts_all [world][n_head][hd+2]
+ *   on every rank -> out [n_head][hd], times sigmoid(gate) when gate != NULL; enqueued on the compute
+ *   stream (capturable in a graph like any NCCL call). */
+typedef struct q4_gpu_comm q4_gpu_comm;
+bool q4_gpu_comm_unique_id(void *id128);
+q4_gpu_comm *q4_gpu_comm_create(const void *id128, uint32_t rank, uint32_t world);
+void q4_gpu_comm_destroy(q4_gpu_comm *c);
+bool q4_gpu_comm_allgather_merge(q4_gpu_comm *c, const float *part, float *parts_all, uint32_t n_head, uint32_t hd,
+                                 const float *gate, float *out);
+
 /* ---- batched multi-session decode: one launch per layer for every session of the batch. */
 typedef struct q4_gpu_batch q4_gpu_batch;
 q4_gpu_batch *q4_gpu_batch_create(uint32_t max_sessions);

@@ -79,6 +79,8 @@ SIGNATURES = {
     "q4_gpu_xchg_attach": (_b, [_v, _u32, _v]), "q4_gpu_xchg_attach_ptr": (_b, [_v, _u32, _v]),
     "q4_gpu_xchg_set_timeout_ms": (_b, [_v, _u32]),
     "q4_gpu_kv_decode_xchg": (_b, [_v, _v, _u32, _v, _i, _v, _v, _u32, _f, _i]),
+    "q4_gpu_comm_unique_id": (_b, [_v]), "q4_gpu_comm_create": (_v, [_v, _u32, _u32]),
+    "q4_gpu_comm_destroy": (None, [_v]), "q4_gpu_comm_allgather_merge": (_b, [_v, _v, _v, _u32, _u32, _v, _v]),
     "q4_gpu_kv_prefill": (_b, [_v, _u32, _v, _v, _v, _u32, _u32, _u32, _f]),
     "q4_gpu_batch_create": (_v, [_u32]), "q4_gpu_batch_destroy": (None, [_v]),
     "q4_gpu_batch_bind": (_b, [_v, _u32, _v]), "q4_gpu_batch_set_pos": (_b, [_v, _v, _u32]),
@@ -295,6 +297,34 @@ class Exchange:
     def close(self):
         if self.h:
             self.L.q4_gpu_xchg_destroy(self.h)
+            self.h = None
+
+
+class Comm:
+    """NCCL communicator of the library (q4_gpu_comm_*), built from a unique id that the host distributes --
+    here over a torch.distributed process group, by broadcast from rank 0."""
+
+    def __init__(self, rank, world, dist=None):
+        self.L = init()
+        buf = C.create_string_buffer(128)
+        if rank == 0:
+            check(self.L.q4_gpu_comm_unique_id(C.cast(buf, C.c_void_p)), "q4_gpu_comm_unique_id")
+        box = [bytes(buf.raw)]
+        if world > 1:
+            dist.broadcast_object_list(box, src=0)
+        idbuf = C.create_string_buffer(box[0], 128)
+        self.h = self.L.q4_gpu_comm_create(C.cast(idbuf, C.c_void_p), rank, world)
+        if not self.h:
+            raise RuntimeError("q4_gpu_comm_create failed (status %#x)" % self.L.q4_gpu_last_error())
+        self.world = world
+
+    def allgather_merge(self, part, parts_all, n_head, hd, out, gate=None):
+        check(self.L.q4_gpu_comm_allgather_merge(self.h, _ptr(part), _ptr(parts_all), n_head, hd, _ptr(gate), _ptr(out)),
+              "q4_gpu_comm_allgather_merge")
+
+    def close(self):
+        if self.h:
+            self.L.q4_gpu_comm_destroy(self.h)
             self.h = None
 
 

@@ -115,3 +115,28 @@ def test_argument_checks():
     assert not L.q4_gpu_kv_decode_xchg(None, x.h, 0, None, 0, None, out.data_ptr(), 0, 0.1, 2)
     assert L.q4_gpu_last_error() & 1
     x.close()
+
+
+def test_library_communicator_on_one_rank(oracle):
+    """q4_gpu_comm_* with a world of one (what a one-GPU box can run): unique id, communicator, all-gather of
+    the single record + merge == the decode's own output; the multi-rank form runs in test_gpu_xchg_multi.py"""
+    L = lib()
+    n_head, n_kvh, hd, ctx = 16, 2, 128, 700
+    k = oracle.normal(61, 0, ctx * n_kvh * hd).reshape(ctx, n_kvh * hd)
+    v = oracle.normal(61, 1, ctx * n_kvh * hd).reshape(ctx, n_kvh * hd)
+    q = oracle.normal(61, 2, n_head * hd)
+    gate = oracle.normal(61, 3, n_head * hd)
+    st = q4gpu.KVStore(1, n_kvh, hd, ctx, 2)
+    st.append(0, dev(k), dev(v), 0, ctx)
+    comm = q4gpu.Comm(0, 1)
+    part = torch.empty(n_head, hd + 2, device="cuda")
+    parts = torch.empty(1, n_head, hd + 2, device="cuda")
+    out = torch.empty(n_head * hd, device="cuda")
+    st.decode_partial(0, dev(q), part, n_head, 0.0884, n_kv=ctx)
+    comm.allgather_merge(part, parts, n_head, hd, out, gate=dev(gate))
+    ref = oracle.attn(q, oracle.kv_write(k, 2), oracle.kv_write(v, 2), gate, n_head, n_kvh, hd, 1, ctx - 1, ctx, 0.0884, 2)[0]
+    assert_close(host(out).reshape(n_head, hd), ref, "collective form, world 1")
+    assert torch.equal(parts[0], part)
+    comm.close()
+    assert not L.q4_gpu_comm_create(None, 0, 1) and L.q4_gpu_last_error() & 1
+    st.close()

@@ -50,6 +50,25 @@ def main():
         if not ok:
             sys.exit(1)
     assert L.q4_gpu_last_error() == 0
+    # ---- the collective form: the library's own NCCL communicator from a unique id handed over by the host
+    # (here: broadcast over the gloo group), all-gather of the ranks' records + merge, against the oracle
+    comm = q4gpu.Comm(rank, world, dist)
+    part = torch.empty(n_head, hd + 2, device="cuda")
+    parts = torch.empty(world, n_head, hd + 2, device="cuda")
+    for call in range(2):
+        q = oracle.normal(780, call, n_head * hd).reshape(n_head, hd)
+        gate = oracle.normal(781, call, n_head * hd) if call else None
+        st.decode_partial(0, torch.from_numpy(q).cuda(), part, n_head, scale, n_kv=e - b)
+        comm.allgather_merge(part, parts, n_head, hd, out, gate=None if gate is None else torch.from_numpy(gate).cuda())
+        torch.cuda.synchronize()
+        ref = oracle.attn(q, kc, vc, gate, n_head, n_kvh, hd, 1, ctx - 1, ctx, scale, kind)[0].reshape(-1)
+        err = np.abs(out.cpu().numpy() - ref)
+        ok = bool((err <= 2e-3 + 1e-3 * np.abs(ref)).all())
+        print("rank %d comm call %d max err %.2e %s" % (rank, call, err.max(), "ok" if ok else "FAIL"), flush=True)
+        if not ok:
+            sys.exit(1)
+    comm.close()
+    assert L.q4_gpu_last_error() == 0
     # ---- a peer that stops calling (between steps, nothing in flight): the others' bounded wait runs
     # out, they get status bit 32 and their own part, and keep working
     dist.barrier()
