@@ -1539,49 +1539,50 @@ __global__ void q4_lse_merge_k(const float *parts, uint32_t n_parts, uint32_t n_
 template <int LAY, int HD, int NHT>
 bool launch(const DecParams &p_in, dim3 grid) {
     constexpr size_t smem_base = DecCfg<LAY, HD, NHT>::SMEM;
-    /* room for the receive area of the push merge: at most 2 heads x 16 records per block */
-    constexpr size_t smem_max = smem_base + 2u * DEC_CLUSTER_MAX * (HD + 4) * sizeof(float);
+    constexpr size_t SMEM_LIMIT = smem_base + 2u * DEC_CLUSTER_MAX * (HD + 4) * sizeof(float);   /* ring / epilogue + the largest receive area of the push merge */
     static bool attr_done = false;
-    if (!attr_done && smem_max > 48 * 1024) {
+    if (!attr_done) {
         if (!q4i_check(cudaFuncSetAttribute(q4_decode_k<LAY, HD, NHT>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max),
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT),
                        "decode smem attribute"))
             return false;
+        (void)cudaFuncSetAttribute(q4_decode_k<LAY, HD, NHT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     }
     attr_done = true;
-    /* The push merge needs extra shared memory; it is used only if that leaves the grid in one wave
-     * (at 8 sessions x 16 blocks the extra 8 KB pushed the clusters into a second wave). */
     DecParams p = p_in;
-    if (p.push_bytes) {
-        static uint32_t cached_bytes = 0, cached_cluster = 0;
-        static int cached_clusters = 0;
-        if (cached_bytes != p.push_bytes || cached_cluster != p.cluster) {
-            if (p.cluster > 8)
-                (void)cudaFuncSetAttribute(q4_decode_k<LAY, HD, NHT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-            cudaLaunchConfig_t qc;
-            memset(&qc, 0, sizeof(qc));
-            qc.gridDim = grid;
-            qc.blockDim = dim3(DEC_THREADS);
-            qc.dynamicSmemBytes = smem_base + p.push_bytes;
-            cudaLaunchAttribute qa[1];
-            qa[0].id = cudaLaunchAttributeClusterDimension;
-            qa[0].val.clusterDim.x = p.cluster;
-            qa[0].val.clusterDim.y = 1;
-            qa[0].val.clusterDim.z = 1;
-            qc.attrs = qa;
-            qc.numAttrs = 1;
-            int n = 0;
-            if (cudaOccupancyMaxActiveClusters(&n, q4_decode_k<LAY, HD, NHT>, &qc) != cudaSuccess) {
-                (void)cudaGetLastError();
-                n = 0;
-            }
-            cached_bytes = p.push_bytes;
-            cached_cluster = p.cluster;
-            cached_clusters = n;
+    const uint64_t blocks = (uint64_t)grid.x * grid.y * grid.z;
+    /* how many clusters of this shape can be resident at once with `bytes` of dynamic shared memory per block */
+    auto resident_clusters = [&](size_t bytes) -> uint64_t {
+        static size_t c_bytes[4];
+        static uint32_t c_cluster[4];
+        static int c_n[4], c_used = 0;
+        for (int i = 0; i < c_used; i++)
+            if (c_bytes[i] == bytes && c_cluster[i] == p.cluster) return (uint64_t)c_n[i];
+        cudaLaunchConfig_t qc;
+        memset(&qc, 0, sizeof(qc));
+        qc.gridDim = grid;
+        qc.blockDim = dim3(DEC_THREADS);
+        qc.dynamicSmemBytes = bytes;
+        cudaLaunchAttribute qa[1];
+        qa[0].id = cudaLaunchAttributeClusterDimension;
+        qa[0].val.clusterDim.x = p.cluster;
+        qa[0].val.clusterDim.y = 1;
+        qa[0].val.clusterDim.z = 1;
+        qc.attrs = qa;
+        qc.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, q4_decode_k<LAY, HD, NHT>, &qc) != cudaSuccess) {
+            (void)cudaGetLastError();
+            n = 0;
         }
-        const uint64_t clusters = (uint64_t)grid.x * grid.y * grid.z / p.cluster;
-        if (clusters > (uint64_t)cached_clusters) p.push_bytes = 0;
-    }
+        const int slot = c_used < 4 ? c_used++ : 3;
+        c_bytes[slot] = bytes; c_cluster[slot] = p.cluster; c_n[slot] = n;
+        return (uint64_t)n;
+    };
+    /* The push merge needs extra shared memory; it is used only if that leaves the grid in one wave.
+     * (Asking for still more shared memory, so that a shallow grid spreads one or two blocks deep over all
+     * SMs instead of three deep over some, was measured: no gain at 1-8 sessions, 3 us slower at 16.) */
+    if (p.push_bytes && resident_clusters(smem_base + p.push_bytes) < blocks / p.cluster) p.push_bytes = 0;
     const size_t smem = smem_base + p.push_bytes;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
@@ -1591,15 +1592,6 @@ bool launch(const DecParams &p_in, dim3 grid) {
     cfg.stream = g_q4.stream;
     cudaLaunchAttribute at[2];
     unsigned n_at = 0;
-    if (p.cluster > 8) {
-        static bool big_ok = false;   /* clusters above the portable size need the kernel's consent */
-        if (!big_ok) {
-            if (!q4i_check(cudaFuncSetAttribute(q4_decode_k<LAY, HD, NHT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1),
-                           "decode cluster-size attribute"))
-                return false;
-            big_ok = true;
-        }
-    }
     if (p.cluster) {
         at[n_at].id = cudaLaunchAttributeClusterDimension;
         at[n_at].val.clusterDim.x = p.cluster;
