@@ -43,7 +43,7 @@ KVW = N_KVH * HD
 ROW_BYTES = 136                       # one (token, kv head) q8_0 row: 128 codes + 4 fp16 scales
 SCALE = 1.0 / math.sqrt(HD)
 SEED = 20261125
-PAD = 64                              # token slots appended during the run
+PAD = 64                              # token slots a session can append between two rewinds (raised to fit --steps)
 L2_BYTES = 126e6
 # dram bytes (read + write) per algorithmic byte of the batched decode kernel, from one ncu capture of the
 # kernel on a small case: 81.1 MB of dram traffic for 71.1 MB gathered (272-byte records are 16-byte, not
@@ -327,14 +327,22 @@ class Group:
                                      idx_sess_stride=N_KVH * WIDTH, q_bf16=True)
 
     def capture(self, L):
+        """one decode step = one graph: every session's position moves on by one on the device, then the layers"""
         assert L.q4_hip_graph_begin() == 1
+        self.batch.advance(1)
         self.enqueue_layers()
         self.graph = L.q4_hip_graph_end()
         assert self.graph, "graph capture failed"
 
+    def rewind(self):
+        """positions back to one before the first free slot, so that the next step appends at slot ctx; called
+        between timed blocks (the stores have room for PAD appended tokens)"""
+        self.batch.set_pos([c - 1 for c in self.ctxs])
+        self.t = 0
+
     def step(self, L):
-        """the token at slot ctx + t of every session (slots wrap inside the PAD region)"""
-        self.batch.set_pos([c + (self.t % PAD) for c in self.ctxs])
+        """the token at slot ctx + t of every session: a graph replay, nothing else"""
+        assert self.t < PAD, "more steps than the stores have room for between two rewinds"
         self.t += 1
         assert L.q4_hip_graph_launch(self.graph)
 
@@ -362,7 +370,7 @@ class Group:
         self.ev_done.record(ds)
 
     def e2e_bytes(self):
-        h2d = self.in_h.numel() + 4 * self.n          # the packed inputs + the positions
+        h2d = self.in_h.numel()                       # the packed inputs (positions advance on the device)
         return h2d, self.out_h.numel() * 4
 
     def algorithmic_bytes_per_layer(self):
@@ -901,6 +909,8 @@ def measure_sessions(args, torch, q4gpu, L, dist, rank, world, local, mine, seed
     the library's stream, max over ranks per block; the median block is reported.  Then the same with host
     buffers (uploads, downloads inside the timed region), then one session's output of the last step against
     the CPU oracle.  Returns a dict; frees everything it built."""
+    global PAD
+    PAD = max(PAD, args.steps + args.warmup + 8)      # a group takes at most that many steps between two rewinds
     step_bytes = N_LAYERS * sum(gathered_bytes(c) for c in mine)
     groups_n = args.groups or max(2, int(math.ceil(512e6 / max(step_bytes, 1))))
     torch.manual_seed(seed0)
@@ -913,6 +923,7 @@ def measure_sessions(args, torch, q4gpu, L, dist, rank, world, local, mine, seed
         g.batch.set_pos(g.ctxs)
         g.enqueue_layers()                    # eager once: scratch grows outside the capture
         g.capture(L)
+        g.rewind()
     assert L.q4_hip_stream_sync()
 
     def barrier():
@@ -936,6 +947,8 @@ def measure_sessions(args, torch, q4gpu, L, dist, rank, world, local, mine, seed
     windows, block_dt = [], []
     step_no = args.warmup
     for blk in range(blocks):
+        for g in groups:
+            g.rewind()
         barrier()
         w0 = time.perf_counter()
         if blk == 0:
@@ -967,9 +980,13 @@ def measure_sessions(args, torch, q4gpu, L, dist, rank, world, local, mine, seed
                 groups[i % groups_n].run_e2e(L, torch, ext, ds)
                 if i + 1 < n and groups_n == 1:          # one set of device buffers: no overlap possible
                     groups[0].copy_in(L, torch, cs)
+        for g in groups:
+            g.rewind()
         e2e_loop(3)
         e2e_dt = []
         for blk in range(max(3, blocks // 3)):
+            for g in groups:
+                g.rewind()
             barrier()
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             w0 = time.perf_counter()
@@ -1134,7 +1151,8 @@ def main():
             "e2e": {"value": args.sessions * args.steps / dt_e2e, "unit": "session*tok/s",
                     "h2d_bytes_per_step": m["h2d"] * world, "d2h_bytes_per_step": m["d2h"] * world,
                     "ms_per_step": 1e3 * dt_e2e / args.steps},
-            "gpu_launches": args.steps * N_LAYERS * world, "clocks": m["clocks"], "roofline": roofline,
+            "gpu_launches": args.steps * (N_LAYERS + 1) * world,   # per step: the position advance + one kernel per layer
+             "clocks": m["clocks"], "roofline": roofline,
             "us_per_layer": 1e6 * dt / (args.steps * N_LAYERS),
             "attn_roofline_session_tok_per_s": args.sessions / (N_LAYERS * sum(gathered_bytes(c) for c in ctxs)
                                                                 / world / (peak_gbs * 1e9))}

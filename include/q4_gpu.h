@@ -401,6 +401,12 @@ bool q4_gpu_batch_bind(q4_gpu_batch *b, uint32_t slot, q4_gpu_kv *kv);
  * later q4_gpu_batch_append / _decode / _append_decode covers exactly these n_sessions sessions (their k,
  * v, q, gate, out and idx arrays have n_sessions rows) until the next call. */
 bool q4_gpu_batch_set_pos(q4_gpu_batch *b, const int32_t *pos, uint32_t n_sessions);
+/* pos[s] += delta on the device for the sessions of the last q4_gpu_batch_set_pos: stream-ordered and
+ * capturable, so a decode step captured as one graph (advance by 1, then the layers) is replayed without a
+ * host upload per step.  No counterpart in the reference (its graph reads one position word that the host
+ * pushes every step, q4_hip_pos_push).  The dense split heuristic keeps using the largest position published
+ * by set_pos (plus the advances made outside a capture). */
+bool q4_gpu_batch_advance(q4_gpu_batch *b, int32_t delta);
 /* k, v: [n_sessions][n_kvh*hd] fp32; row s goes to slot pos[s] of session s. */
 bool q4_gpu_batch_append(q4_gpu_batch *b, uint32_t layer, const float *k, const float *v);
 /* q [n_sessions][n_head][hd]; gate, out likewise; idx [n_sessions][...] with idx_sess_stride

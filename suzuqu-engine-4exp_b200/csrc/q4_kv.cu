@@ -633,6 +633,20 @@ extern "C" bool q4_gpu_batch_set_pos(q4_gpu_batch *b, const int32_t *pos, uint32
                      "batch_set_pos upload") &&
            q4i_check(cudaEventRecord(b->pos_ev[slot], g_q4.stream), "batch_set_pos event");
 }
+/* Positions move on the device: pos[s] += delta for the sessions of the last set_pos.  Stream-ordered and
+ * capturable, so a decode step that is one CUDA graph (advance, then the layers) needs no host upload
+ * between two replays (the upload of q4_gpu_batch_set_pos costs 3-4 us per step as a copy node). */
+__global__ static void q4_batch_advance_k(int32_t *pos, uint32_t n, int32_t delta) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) pos[i] += delta;
+}
+extern "C" bool q4_gpu_batch_advance(q4_gpu_batch *b, int32_t delta) {
+    if (!g_q4.ok) return q4i_fail(Q4E_INIT, "batch_advance: library not initialised");
+    Q4_REQUIRE(b && b->n_active, "batch_advance: no positions published (q4_gpu_batch_set_pos)");
+    q4_batch_advance_k<<<(b->n_active + 127u) / 128u, 128, 0, g_q4.stream>>>(b->pos_d, b->n_active, delta);
+    if (!g_q4.capturing) b->max_pos = (uint32_t)((int64_t)b->max_pos + delta < 0 ? 0 : (int64_t)b->max_pos + delta);
+    return q4i_check(cudaGetLastError(), "batch_advance launch");
+}
 extern "C" bool q4_gpu_batch_append(q4_gpu_batch *b, uint32_t layer, const float *k, const float *v) {
     if (!g_q4.ok) return q4i_fail(Q4E_INIT, "batch_append: library not initialised");
     Q4_REQUIRE(b && b->n && k && v && b->kv[0] && layer < b->kv[0]->n_layers, "batch_append: bad argument");

@@ -84,6 +84,7 @@ SIGNATURES = {
     "q4_gpu_kv_prefill": (_b, [_v, _u32, _v, _v, _v, _u32, _u32, _u32, _f]),
     "q4_gpu_batch_create": (_v, [_u32]), "q4_gpu_batch_destroy": (None, [_v]),
     "q4_gpu_batch_bind": (_b, [_v, _u32, _v]), "q4_gpu_batch_set_pos": (_b, [_v, _v, _u32]),
+    "q4_gpu_batch_advance": (_b, [_v, _i32]),
     "q4_gpu_batch_append": (_b, [_v, _u32, _v, _v]),
     "q4_gpu_batch_decode": (_b, [_v, _u32, _v, _i, _v, _v, _v, _u32, _u32, _u32, _u32, _f]),
     "q4_gpu_batch_append_decode": (_b, [_v, _u32, _v, _v, _v, _i, _v, _v, _v, _u32, _u32, _u32, _u32, _f]),
@@ -354,6 +355,10 @@ class Batch:
     def set_pos(self, pos):
         arr = (C.c_int32 * len(pos))(*[int(p) for p in pos])
         check(self.L.q4_gpu_batch_set_pos(self.h, arr, len(pos)), "q4_gpu_batch_set_pos")
+
+    def advance(self, delta=1):
+        """pos[s] += delta on the device (capturable)"""
+        check(self.L.q4_gpu_batch_advance(self.h, delta), "q4_gpu_batch_advance")
 
     def append(self, layer, k, v):
         check(self.L.q4_gpu_batch_append(self.h, layer, _ptr(k), _ptr(v)), "q4_gpu_batch_append")

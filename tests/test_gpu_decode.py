@@ -410,6 +410,67 @@ def test_graph_captured_decode_follows_the_position_word(oracle):
     st.close()
 
 
+def test_graph_captured_batch_step_advances_its_positions_on_the_device(oracle):
+    """position advance + fused append + dense decode of three sessions captured once and replayed for
+    successive tokens with no position upload in between: after set_pos(p - 1) the k-th replay appends at
+    slot p + k - 1 of every session and attends p + k rows."""
+    L = lib()
+    L.q4_gpu_set_stream(None)
+    n_head, n_kvh, hd, max_kv = 16, 2, 128, 96
+    kvw = n_kvh * hd
+    starts = [5, 31, 48]
+    stores, rows = [], []
+    for s, p in enumerate(starts):
+        k = oracle.normal(820 + s, 0, p * kvw).reshape(p, kvw)
+        st = q4gpu.KVStore(1, n_kvh, hd, max_kv, 2)
+        st.append(0, dev(k), dev(k), 0, p)
+        stores.append(st)
+        rows.append(list(k))
+    b = q4gpu.Batch(stores)
+    n = len(starts)
+    kbuf, qbuf = torch.zeros(n, kvw, device="cuda"), torch.zeros(n, n_head * hd, device="cuda")
+    obuf = torch.zeros(n, n_head * hd, device="cuda")
+    torch.cuda.synchronize()
+    b.set_pos([p - 1 for p in starts])
+    assert L.q4_hip_graph_begin() == 1
+    b.advance(1)
+    b.append_decode(0, kbuf, kbuf, qbuf, obuf, n_head, 0.0884)
+    g = L.q4_hip_graph_end()
+    assert g
+    for step in range(20):
+        k = oracle.normal(830, step, n * kvw).reshape(n, kvw)
+        q = oracle.normal(831, step, n * n_head * hd).reshape(n, n_head * hd)
+        for d, h in ((kbuf, k), (qbuf, q)):
+            assert L.q4_hip_h2d(d.data_ptr(), h.ctypes.data, h.nbytes)
+        assert L.q4_hip_graph_launch(g)
+        out = np.empty((n, n_head * hd), np.float32)
+        assert L.q4_hip_d2h(out.ctypes.data, obuf.data_ptr(), out.nbytes)
+        for s in range(n):
+            rows[s].append(k[s])
+        if step in (0, 1, 10, 19):
+            for s in range(n):
+                kc = oracle.kv_write(np.stack(rows[s]), 2)
+                n_kv = starts[s] + step + 1
+                ref = oracle.attn(q[s], kc, kc, None, n_head, n_kvh, hd, 1, n_kv - 1, n_kv, 0.0884, 2)[0]
+                assert_close(out[s].reshape(n_head, hd), ref, "replay %d session %d" % (step, s))
+    # outside a capture the advance is an ordinary launch; a negative step takes positions back
+    b.advance(-20)
+    b.advance(1)
+    assert L.q4_hip_graph_launch(g)                       # advances once more: slot p + 1 again, rewritten
+    out = np.empty((n, n_head * hd), np.float32)
+    assert L.q4_hip_d2h(out.ctypes.data, obuf.data_ptr(), out.nbytes)
+    for s in range(n):
+        kc = oracle.kv_write(np.stack(rows[s][:starts[s] + 1] + [k[s]]), 2)
+        ref = oracle.attn(q[s], kc, kc, None, n_head, n_kvh, hd, 1, starts[s] + 1, starts[s] + 2, 0.0884, 2)[0]
+        assert_close(out[s].reshape(n_head, hd), ref, "after rewind, session %d" % s)
+    assert L.q4_gpu_last_error() == 0
+    L.q4_hip_graph_free(g)
+    q4gpu.use_torch_stream()
+    b.close()
+    for st in stores:
+        st.close()
+
+
 @pytest.mark.parametrize("q_bf16", [False, True])
 @pytest.mark.parametrize("mode", ["sigma8", "head_x50"])
 def test_large_magnitude_queries(oracle, mode, q_bf16):
