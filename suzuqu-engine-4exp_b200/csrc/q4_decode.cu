@@ -79,6 +79,8 @@ struct DecParams {
     const float *new_k, *new_v;   /* fused append of the newest row (native q8_0 store), or null */
     uint32_t pdl;                 /* launched with programmatic stream serialization */
     uint32_t push_bytes;          /* > 0: the launch carries this much extra shared memory and merges by pushing */
+    uint32_t push_async;          /* pushes complete an mbarrier of the receiving block (its last 16 bytes) instead of
+                                   * meeting at a cluster barrier */
     uint32_t bulk_runs;           /* tiles of 16 consecutive positions come in by one bulk copy each (else by cp.async) */
 };
 
@@ -497,6 +499,7 @@ __device__ __noinline__ void cluster_merge(uint32_t rec_saddr, uint32_t S, uint3
     }
 }
 
+constexpr uint32_t PUSH_SPIN_LIMIT = 1u << 22;   /* probes of the receive barrier before the block gives up */
 /* Push form of the cluster merge, for launches that carry extra shared memory for it (a few units in
  * flight, clusters of more than 8 blocks): every block stores head h of its record into the receive
  * area of block h % S (slot (h / S) * S + own rank) through distributed shared memory, one cluster
@@ -506,16 +509,39 @@ __device__ __noinline__ void cluster_merge(uint32_t rec_saddr, uint32_t S, uint3
  * peer may push while this block is still in its position loop. */
 template <int HD, int HEADS>
 __device__ __noinline__ void cluster_push_merge(const float *own, const float *recv, uint32_t S, uint32_t rank,
-                                                const MergeOut mo) {
+                                                const MergeOut mo, uint32_t bar, uint32_t *err) {
     constexpr int REC = HD + 4;
     const uint32_t recv_saddr = (uint32_t)__cvta_generic_to_shared(recv);
-    for (uint32_t i = threadIdx.x; i < mo.gqa * (REC / 4); i += DEC_THREADS) {
-        const uint32_t h = i / (REC / 4), c = i % (REC / 4);
-        const float4 v = *reinterpret_cast<const float4 *>(own + (size_t)h * REC + 4 * c);
-        const uint32_t dst = map_to_rank(recv_saddr + ((((h / S) * S + rank) * REC) + 4 * c) * 4, h % S);
-        asm volatile("st.shared::cluster.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+    if (bar) {
+        /* Every 16-byte store reports its bytes to the receiving block's barrier; a block that owns heads waits
+         * for exactly the bytes of its heads' S records, a block that owns none is done once it has pushed.
+         * Nobody waits for the slowest block of the cluster unless it needs that block's record. */
+        const uint32_t n_own = rank < mo.gqa ? (mo.gqa - rank + S - 1u) / S : 0u;
+        if (threadIdx.x == 0 && n_own) ring_bar_expect(bar, n_own * S * REC * 4u);
+        for (uint32_t i = threadIdx.x; i < mo.gqa * (REC / 4); i += DEC_THREADS) {
+            const uint32_t h = i / (REC / 4), c = i % (REC / 4);
+            const float4 v = *reinterpret_cast<const float4 *>(own + (size_t)h * REC + 4 * c);
+            const uint32_t dst = map_to_rank(recv_saddr + ((((h / S) * S + rank) * REC) + 4 * c) * 4, h % S);
+            const uint32_t rbar = map_to_rank(bar, h % S);
+            asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1,%2,%3,%4}, [%5];"
+                         ::"r"(dst), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "r"(rbar) : "memory");
+        }
+        if (!n_own) return;
+        uint32_t probes = 0;
+        while (!ring_bar_test(bar, 0u) && ++probes < PUSH_SPIN_LIMIT) {}
+        if (probes >= PUSH_SPIN_LIMIT) {      /* a peer's record never arrived: reported, the output is not valid */
+            atomicOr(err, (uint32_t)Q4E_CUDA);
+            return;
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < mo.gqa * (REC / 4); i += DEC_THREADS) {
+            const uint32_t h = i / (REC / 4), c = i % (REC / 4);
+            const float4 v = *reinterpret_cast<const float4 *>(own + (size_t)h * REC + 4 * c);
+            const uint32_t dst = map_to_rank(recv_saddr + ((((h / S) * S + rank) * REC) + 4 * c) * 4, h % S);
+            asm volatile("st.shared::cluster.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+        }
+        cluster_sync_all();
     }
-    cluster_sync_all();
     for (uint32_t h = rank, j = 0; h < mo.gqa; h += S, j++) {
         const float *base = recv + (size_t)j * S * REC;
         float m[DEC_CLUSTER_MAX], l[DEC_CLUSTER_MAX];
@@ -751,7 +777,18 @@ q4_decode_k(const DecParams P) {
      * shared memory may be accessed remotely only once that block runs, so every block announces itself here
      * and waits for its peers' announcements just before its first remote access: by then they have all
      * arrived long ago and the wait costs nothing. */
-    if (P.cluster) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+    if (P.cluster) {
+        if (P.push_async) {
+            /* the barrier that the peers' pushes complete: initialised before this block announces itself */
+            if (threadIdx.x == 0) {
+                ring_bar_init((uint32_t)__cvta_generic_to_shared(smem_raw + DecCfg<LAY, HD, NHT>::SMEM + P.push_bytes - 16u));
+                asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            }
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        } else {
+            asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+        }
+    }
     /* Programmatic dependent launch: the blocks of this launch may already be resident while the previous
      * kernel of the stream drains.  Only the cache view above (written when the store was created or bound)
      * is read before this point; positions, lists, queries and rows are read after it. */
@@ -1460,7 +1497,9 @@ q4_decode_k(const DecParams P) {
         merge_records<HD, HEADS>(sm, DEC_WARPS, false, own, mo, mscr);
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   /* every peer block has started (arrive at entry) */
         if (P.push_bytes) {
-            cluster_push_merge<HD, HEADS>(own, reinterpret_cast<const float *>(smem_raw + Cfg::SMEM), S, cluster_ctarank(), mo);
+            cluster_push_merge<HD, HEADS>(own, reinterpret_cast<const float *>(smem_raw + Cfg::SMEM), S, cluster_ctarank(), mo,
+                                          P.push_async ? (uint32_t)__cvta_generic_to_shared(smem_raw + Cfg::SMEM + P.push_bytes - 16u) : 0u,
+                                          P.err);
             return;
         }
         cluster_sync_all();
@@ -1539,7 +1578,7 @@ __global__ void q4_lse_merge_k(const float *parts, uint32_t n_parts, uint32_t n_
 template <int LAY, int HD, int NHT>
 bool launch(const DecParams &p_in, dim3 grid) {
     constexpr size_t smem_base = DecCfg<LAY, HD, NHT>::SMEM;
-    constexpr size_t SMEM_LIMIT = smem_base + 2u * DEC_CLUSTER_MAX * (HD + 4) * sizeof(float);   /* ring / epilogue + the largest receive area of the push merge */
+    constexpr size_t SMEM_LIMIT = smem_base + 2u * DEC_CLUSTER_MAX * (HD + 4) * sizeof(float) + 16u;   /* ring / epilogue + the largest receive area of the push merge */
     static bool attr_done = false;
     if (!attr_done) {
         if (!q4i_check(cudaFuncSetAttribute(q4_decode_k<LAY, HD, NHT>,
@@ -1583,6 +1622,7 @@ bool launch(const DecParams &p_in, dim3 grid) {
      * (Asking for still more shared memory, so that a shallow grid spreads one or two blocks deep over all
      * SMs instead of three deep over some, was measured: no gain at 1-8 sessions, 3 us slower at 16.) */
     if (p.push_bytes && resident_clusters(smem_base + p.push_bytes) < blocks / p.cluster) p.push_bytes = 0;
+    if (!p.push_bytes) p.push_async = 0;
     const size_t smem = smem_base + p.push_bytes;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
@@ -1726,7 +1766,13 @@ bool q4i_decode(const Q4DecodeArgs &a) {
     p.S = S;
     p.cluster = cluster;
     /* the push merge needs extra shared memory; the launcher drops it where that would cost a wave */
-    p.push_bytes = cluster > 1 ? ((gqa + cluster - 1u) / cluster) * cluster * (a.hd + 4u) * (uint32_t)sizeof(float) : 0u;
+    p.push_bytes = cluster > 1 ? ((gqa + cluster - 1u) / cluster) * cluster * (a.hd + 4u) * (uint32_t)sizeof(float) + 16u : 0u;
+    {
+        /* Q4_DEC_PUSH_ASYNC=0: the pushes meet at a cluster barrier instead of completing the receiver's mbarrier */
+        static int pa = -1;
+        if (pa < 0) { const char *e = getenv("Q4_DEC_PUSH_ASYNC"); pa = e ? atoi(e) : 1; }
+        p.push_async = p.push_bytes && pa ? 1u : 0u;
+    }
     p.scratch = scratch;
     p.counters = counters;
     p.err = g_q4.err_d;
