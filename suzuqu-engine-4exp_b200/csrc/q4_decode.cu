@@ -1630,7 +1630,7 @@ bool launch(const DecParams &p_in, dim3 grid) {
     cfg.blockDim = dim3(DEC_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = g_q4.stream;
-    cudaLaunchAttribute at[2];
+    cudaLaunchAttribute at[3];
     unsigned n_at = 0;
     if (p.cluster) {
         at[n_at].id = cudaLaunchAttributeClusterDimension;
@@ -1638,6 +1638,17 @@ bool launch(const DecParams &p_in, dim3 grid) {
         at[n_at].val.clusterDim.y = 1;
         at[n_at].val.clusterDim.z = 1;
         n_at++;
+        /* Where the blocks of a cluster land: the load-balancing preference keeps a shallow grid one or two
+         * blocks deep on every SM where the default stacks three on some (8 sessions: 8.7 against 9.8 us per
+         * launch with clusters of 12); no effect on full grids.  Q4_DEC_CLUSTER_POLICY=0 leaves the choice to the
+         * driver, 1 asks for the spread policy. */
+        static int pol = -1;
+        if (pol < 0) { const char *e = getenv("Q4_DEC_CLUSTER_POLICY"); pol = e ? atoi(e) : 2; }
+        if (pol) {
+            at[n_at].id = cudaLaunchAttributeClusterSchedulingPolicyPreference;
+            at[n_at].val.clusterSchedulingPolicyPreference = pol == 1 ? cudaClusterSchedulingPolicySpread : cudaClusterSchedulingPolicyLoadBalancing;
+            n_at++;
+        }
     }
     if (p.pdl) {
         at[n_at].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -1712,14 +1723,15 @@ bool q4i_decode(const Q4DecodeArgs &a) {
     uint32_t cluster = 0;   /* blocks per cluster; 0 = plain launch with the merge in global memory */
     if (a.xchg) Q4_REQUIRE(a.n_units == 1 && a.out && !a.part_out && !a.many, "decode: exchange mode is for one token of one session");
     if (use_cluster && !a.scratch_part && !a.xchg && (S <= 8 || steps <= 512)) {
-        /* a few units only (single session, small batch): clusters of 16 halve each warp's share again;
-         * every warp keeps at least two tiles */
-        /* 16 blocks per unit while that is at most one block per SM, 12 while it is at most two (measured at 8
-         * sessions: 10.1 us per launch against 10.6 with 16 and 10.2 with 8), else 8 */
+        /* A few units only (single session, small batch): larger clusters shorten each warp's share, as long as
+         * the blocks still spread one or two deep over the SMs.  Measured with the load-balancing placement, us
+         * per launch at 2 / 4 / 8 / 16 sessions of 2 kv heads: clusters of 16: 7.3 / 7.7 / 10.5 / 18.6, of 13:
+         * 7.3 / 7.7 / 8.5 / 18.6, of 12: 7.4 / 7.8 / 8.7 / 12.2, of 8: - / 8.7 / 10.0 / 13.3. */
         const uint32_t sms = (uint32_t)g_q4.sm_count;
         const uint32_t cmax = steps < 8u * DEC_CLUSTER_MAX ? 8u
-                              : units * DEC_CLUSTER_MAX <= sms ? DEC_CLUSTER_MAX
-                              : units * 12u <= sms * 2u ? 12u : 8u;
+                              : units * 32u <= sms ? DEC_CLUSTER_MAX
+                              : units * 26u <= sms * 3u ? 13u
+                              : units * 60u <= sms * 13u ? 12u : 8u;
         if (S > cmax) S = cmax;
         cluster = S > 1 ? S : 0u;
     }
