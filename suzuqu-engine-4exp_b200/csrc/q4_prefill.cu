@@ -44,12 +44,11 @@
 namespace {
 
 constexpr int PF_ROWS = 128, PF_BN = 64, PF_HD = 128;
-constexpr uint32_t PF_Q_BYTES = 2 * PF_ROWS * 128, PF_K_BYTES = 2 * PF_BN * 128, PF_V_BYTES = PF_HD * 128,
-                   PF_P_BYTES = PF_ROWS * 128;
+constexpr uint32_t PF_Q_BYTES = 2 * PF_ROWS * 128, PF_K_BYTES = 2 * PF_BN * 128, PF_V_BYTES = PF_HD * 128;
 constexpr uint32_t PF_STAGES = 2;
 constexpr uint32_t PF_THREADS = PF_ROWS + 64;   /* 4 softmax warps, the tensor-core issuer, the TMA producer */
 /* Q | P | K stages | V stages | barriers in the alignment slack */
-constexpr uint32_t PF_TILE_BYTES = PF_Q_BYTES + PF_P_BYTES + PF_STAGES * (PF_K_BYTES + PF_V_BYTES);
+constexpr uint32_t PF_TILE_BYTES = PF_Q_BYTES + PF_STAGES * (PF_K_BYTES + PF_V_BYTES);
 constexpr uint32_t PF_SMEM = PF_TILE_BYTES + 1024;
 constexpr uint32_t PF_TMEM_COLS = 256, PF_S_COL = 0, PF_O_COL = 128;   /* S0 at 0, S1 at 64, O at 128 */
 constexpr uint32_t PF_SPIN_LIMIT = 1u << 24;
@@ -89,6 +88,14 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+/* same product with the A operand in tensor memory (lane = row, one 32-bit column = two consecutive k) */
+__device__ __forceinline__ void umma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -211,10 +218,12 @@ __global__ void __launch_bounds__(PF_THREADS, 2) q4_prefill_k(const PrefillParam
 
     /* 1024-byte aligned operand tiles (the swizzle pattern is anchored to the address) */
     const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
-    const uint32_t sQ = base, sP = sQ + PF_Q_BYTES, sK = sP + PF_P_BYTES, sV = sK + PF_STAGES * PF_K_BYTES;
+    const uint32_t sQ = base, sK = sQ + PF_Q_BYTES, sV = sK + PF_STAGES * PF_K_BYTES;
     /* barriers in the alignment slack in front of the tiles when there is room, else behind them */
     const uint32_t bars = (base - smem_u32(smem_dyn) >= 96u) ? smem_u32(smem_dyn) : base + PF_TILE_BYTES;
-    const uint32_t full_k = bars, full_v = bars + 16, bar_s = bars + 32, bar_o = bars + 48, bar_p = bars + 56,
+    /* bar_p: one per score buffer.  A softmax warp may publish P of tile j + 1 before a slower warp has published
+     * tile j (nothing but the score buffers holds it back), so consecutive tiles must not count on one barrier. */
+    const uint32_t full_k = bars, full_v = bars + 16, bar_s = bars + 32, bar_o = bars + 48, bar_p = bars + 72,
                    s_tmem = bars + 64, s_abort = bars + 68;
 
     /* softmax thread r < 128 owns row r = (token t0 + r / gqa, head kh*gqa + r % gqa); rows past tpc*gqa or
@@ -239,6 +248,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) q4_prefill_k(const PrefillParam
             }
             mbar_init(bar_o, 1);
             mbar_init(bar_p, PF_ROWS);
+            mbar_init(bar_p + 8, PF_ROWS);
             asm volatile("st.shared.u32 [%0], %1;" ::"r"(s_abort), "r"(0u) : "memory");
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         }
@@ -360,14 +370,14 @@ __global__ void __launch_bounds__(PF_THREADS, 2) q4_prefill_k(const PrefillParam
                 ok = wait(full_v + 8 * st, use);
                 if (ok && tile + 2 < n_tiles) ok = wait(full_k + 8 * st, ((tile + 2) / PF_STAGES) & 1u);
                 /* softmax of this tile done: P is in shared memory, O is rescaled, S[st] has been read */
-                ok = ok && wait(bar_p, tile & 1u);
+                ok = ok && wait(bar_p + 8 * st, use);
                 tc_fence_after();
                 if (ok) {
 #pragma unroll
                     for (uint32_t kk = 0; kk < 4; kk++) {
-                        const uint64_t ad = umma_desc(sP + kk * 32);
                         const uint64_t bd = umma_desc(sV + st * PF_V_BYTES + kk * 32);
-                        umma_f16(tmem + PF_O_COL, ad, bd, IDESC_PV, (tile > 0 || kk > 0) ? 1u : 0u);
+                        umma_f16_ta(tmem + PF_O_COL, tmem + PF_S_COL + st * PF_BN + kk * 8, bd, IDESC_PV,
+                                    (tile > 0 || kk > 0) ? 1u : 0u);
                     }
                     umma_commit(bar_o);
                     if (tile + 2 < n_tiles) issue_qk(tile + 2);
@@ -418,33 +428,32 @@ __global__ void __launch_bounds__(PF_THREADS, 2) q4_prefill_k(const PrefillParam
                 pk[i] = h2u(__floats2half2_rn(e0, e1));
             }
             l_run += ls0 + ls1;
-            /* the previous P.V must have drained before P is overwritten and O is rescaled */
-            if (tile > 0) {
+            /* O is rescaled only when the stored maximum moved; the previous P.V must have drained first.  P itself
+             * waits for nothing: it goes into the first 32 columns of the score buffer this thread has just read
+             * (two fp16 per column), which the tensor core reads as the A operand of P.V before the scores of the
+             * tile two ahead are written there (products issued by one thread run in order). */
+            if (tile > 0 && __any_sync(0xffffffffu, grow)) {
                 ok = __all_sync(0xffffffffu, ok && wait(bar_o, (tile - 1u) & 1u));
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll
-                    for (int c = 0; c < 4; c++) {
-                        float o[32];
-                        tmem_ld32(t_lane + PF_O_COL + 32 * c, o);
-                        tmem_wait_ld();
+                for (int c = 0; c < 4; c++) {
+                    float o[32];
+                    tmem_ld32(t_lane + PF_O_COL + 32 * c, o);
+                    tmem_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; i++) o[i] *= alpha;
-                        tmem_st32(t_lane + PF_O_COL + 32 * c, o);
-                    }
-                    tmem_wait_st();
+                    for (int i = 0; i < 32; i++) o[i] *= alpha;
+                    tmem_st32(t_lane + PF_O_COL + 32 * c, o);
                 }
             }
-#pragma unroll
-            for (int c = 0; c < 8; c++) {
-                const uint32_t a = sP + sw128(tid, c);
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(pk[4 * c]), "r"(pk[4 * c + 1]),
-                             "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3]) : "memory");
-            }
-            fence_async_smem();
+            tmem_st32(t_lane + PF_S_COL + st * PF_BN, *reinterpret_cast<const float(*)[32]>(&pk[0]));
+            tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(bar_p);
+            mbar_arrive(bar_p + 8 * st);
         }
+        /* The last P.V.  A parity wait can tell the current phase from the one before it, no further: this thread
+         * has not followed the phases of bar_o tile by tile, and when it gets here the product of tile n - 3 is
+         * complete (the scores of tile n - 1 were committed behind it) but perhaps not yet that of tile n - 2. */
+        if (ok && n_tiles > 1) ok = wait(bar_o, (n_tiles - 2u) & 1u);
         if (ok && n_tiles > 0) ok = wait(bar_o, (n_tiles - 1u) & 1u);
         tc_fence_after();
 
