@@ -18,17 +18,21 @@
  *     operand layout, so no thread touches them:
  *
  *       producer warp (one thread): TMA loads, two tiles of K and of V^T in flight
- *       issuer warp (one thread): O[128 x 128] += P . V[j], 4 x tcgen05.mma (k = 16), as soon as the
- *                     softmax warps have published P, then S[j+2] = Q . K[j+2]^T, 8 x tcgen05.mma,
- *                     into the score buffer that the softmax of tile j has just released (two score
- *                     buffers in tensor memory, so the next tile's scores are always ready)
+ *       issuer warp (one thread): O[128 x 128] += P . V[j], 4 x tcgen05.mma (k = 16) with P as the A
+ *                     operand in tensor memory, as soon as the softmax warps have published P, then
+ *                     S[j+2] = Q . K[j+2]^T, 8 x tcgen05.mma, into the score buffer that held S[j]
+ *                     and P[j] (two score buffers in tensor memory, so the next tile's scores are
+ *                     always ready; products issued by one thread run in order, so P[j] is read
+ *                     before S[j+2] lands on it)
  *       4 softmax warps: thread r owns row r: tcgen05.ld its 64 scores of tile j, causal mask,
  *                     running max with lazy rescale (the stored max only moves when it would grow
  *                     by more than 2^8, so the O accumulator in tensor memory is rarely touched),
- *                     P = exp2(..) as fp16 -> shared memory, mbarrier arrive
+ *                     P = exp2(..) as fp16 -> tcgen05.st into the first 32 columns of the score
+ *                     buffer just read, mbarrier arrive.  Nothing here waits for the previous P . V
+ *                     unless O has to be rescaled.
  *
  *     The roles meet only at mbarriers (scores ready, P ready, P.V drained, tiles landed): there
- *     is no block-wide barrier inside the tile loop.  Two blocks fit on an SM (113 KB of shared
+ *     is no block-wide barrier inside the tile loop.  Two blocks fit on an SM (97 KB of shared
  *     memory, 256 of the 512 tensor-memory columns each).
  *
  * Every mbarrier wait is bounded: on expiry the thread raises a block-wide abort flag that every
