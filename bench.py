@@ -317,7 +317,7 @@ class Group:
         self.out = torch.empty(N_LAYERS, n, N_HEAD, HD, device="cuda")
         self.t = 0
         self.graph = None
-        self.ev_in = self.ev_comp = self.ev_done = None
+        self.pipe = None                      # events of this group's upload / graph / download (q4_gpu_pipe)
 
     def enqueue_layers(self):
         # one launch per layer: the attention kernel quantises and stores each session's new K/V row itself
@@ -346,28 +346,20 @@ class Group:
         self.t += 1
         assert L.q4_hip_graph_launch(self.graph)
 
-    def copy_in(self, L, torch, cs):
-        """this step's inputs from pinned host memory, on the library's copy stream (C ABI), after the
-        previous step that read these device buffers"""
-        if self.ev_comp is not None:
-            cs.wait_event(self.ev_comp)
-        assert L.q4_hip_copy_h2d(self.in_d.data_ptr(), self.in_h.data_ptr(), self.in_h.numel())
-        self.ev_in = torch.cuda.Event()
-        self.ev_in.record(cs)
+    def copy_in(self, L):
+        """this step's inputs from pinned host memory, on the library's copy stream, after the previous step
+        that read these device buffers (the pipe orders it)"""
+        if self.pipe is None:
+            self.pipe = L.q4_gpu_pipe_create()
+            assert self.pipe
+        assert L.q4_gpu_pipe_upload(self.pipe, self.in_d.data_ptr(), self.in_h.data_ptr(), self.in_h.numel())
 
-    def run_e2e(self, L, torch, xs, ds):
-        """compute on the library's stream once the inputs are in and the previous result of this group is
-        out; the result goes back on the download stream"""
-        xs.wait_event(self.ev_in)
-        if self.ev_done is not None:
-            xs.wait_event(self.ev_done)
-        self.step(L)
-        self.ev_comp = torch.cuda.Event()
-        self.ev_comp.record(xs)
-        ds.wait_event(self.ev_comp)
-        assert L.q4_gpu_copy_d2h(self.out_h.data_ptr(), self.out.data_ptr(), self.out.numel() * 4)
-        self.ev_done = torch.cuda.Event()
-        self.ev_done.record(ds)
+    def run_e2e(self, L):
+        """the step's graph on the library's stream once the inputs are in and the previous result of this
+        group is out; the result goes back on the download stream"""
+        assert self.t < PAD, "more steps than the stores have room for between two rewinds"
+        self.t += 1
+        assert L.q4_gpu_pipe_run(self.pipe, self.graph, self.out_h.data_ptr(), self.out.data_ptr(), self.out.numel() * 4)
 
     def e2e_bytes(self):
         h2d = self.in_h.numel()                       # the packed inputs (positions advance on the device)
@@ -965,21 +957,21 @@ def measure_sessions(args, torch, q4gpu, L, dist, rank, world, local, mine, seed
     res = {"dt": dt, "block_ms": [1e3 * x for x in block_dt], "groups": groups_n, "sessions_here": len(mine),
            "algorithmic_bytes_per_launch": groups[0].algorithmic_bytes_per_layer()}
     # ---- end to end: host buffers in, outputs out, every step
-    # Uploads ride the library's copy stream (q4_hip_copy_h2d) and are ordered against the compute
-    # stream with events, so the inputs of step i+1 travel while step i computes; every step's copies in
-    # and out are inside the timed region.
+    # Uploads ride the library's copy stream and downloads its download stream, ordered against the compute
+    # stream by the events of a q4_gpu_pipe per group (two C calls per step), so the inputs of step i+1 travel
+    # while step i computes; every step's copies in and out are inside the timed region.
     if e2e:
         cs = torch.cuda.ExternalStream(L.q4_gpu_copy_stream())
         ds = torch.cuda.ExternalStream(L.q4_gpu_download_stream())
 
         def e2e_loop(n):
-            groups[0].copy_in(L, torch, cs)
+            groups[0].copy_in(L)
             for i in range(n):
                 if i + 1 < n and groups_n > 1:
-                    groups[(i + 1) % groups_n].copy_in(L, torch, cs)
-                groups[i % groups_n].run_e2e(L, torch, ext, ds)
+                    groups[(i + 1) % groups_n].copy_in(L)
+                groups[i % groups_n].run_e2e(L)
                 if i + 1 < n and groups_n == 1:          # one set of device buffers: no overlap possible
-                    groups[0].copy_in(L, torch, cs)
+                    groups[0].copy_in(L)
         for g in groups:
             g.rewind()
         e2e_loop(3)
@@ -1015,6 +1007,8 @@ def measure_sessions(args, torch, q4gpu, L, dist, rank, world, local, mine, seed
         res["verified"], res["max_err"] = ok, err
     for g in groups:
         L.q4_hip_graph_free(g.graph)
+        if g.pipe:
+            L.q4_gpu_pipe_destroy(g.pipe)
         g.batch.close()
         for st in g.stores:
             st.close()

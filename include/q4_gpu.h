@@ -182,6 +182,21 @@ bool q4_gpu_copy_d2h(void *dst, const void *src, size_t n);
 void *q4_gpu_download_stream(void);
 bool q4_gpu_set_stream(void *cuda_stream);
 int q4_gpu_device(void);
+/* A pipelined step loop over one set of step buffers (no counterpart in the reference, whose decode step
+ * uploads, computes and reads back on one stream).  A host that decodes step after step from host buffers
+ * keeps two or three sets of device input / output buffers, each with a captured graph that reads and writes
+ * them; a pipe holds the events that order one set's upload (copy stream), graph (compute stream) and
+ * download (download stream), so step i + 1 travels in while step i computes and step i - 1 travels out:
+ *     q4_gpu_pipe_upload(next, ...); q4_gpu_pipe_run(this, graph, ...);   per step, nothing else.
+ * upload: pinned host memory -> the set's device input buffer, after the set's previous graph launch.
+ * run: the graph, after the set's upload and its previous download; then src_d -> dst_h (n bytes; n = 0: no
+ * download).  Both return at once.  sync: blocks until the set's last download has landed. */
+typedef struct q4_gpu_pipe q4_gpu_pipe;
+q4_gpu_pipe *q4_gpu_pipe_create(void);
+void q4_gpu_pipe_destroy(q4_gpu_pipe *p);
+bool q4_gpu_pipe_upload(q4_gpu_pipe *p, void *dst_d, const void *src_h, size_t n);
+bool q4_gpu_pipe_run(q4_gpu_pipe *p, void *graph_exec, void *dst_h, const void *src_d, size_t n);
+bool q4_gpu_pipe_sync(q4_gpu_pipe *p);
 /* Device address of the position word written by q4_hip_pos_push. */
 const int32_t *q4_gpu_pos_word(void);
 

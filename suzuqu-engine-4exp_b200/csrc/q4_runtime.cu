@@ -282,6 +282,73 @@ extern "C" void q4_hip_graph_free(void *exec) {
     if (exec) (void)cudaGraphExecDestroy((cudaGraphExec_t)exec);
 }
 
+/* ---- a pipelined step loop over one set of step buffers -------------------------------------------
+ * A host that decodes step after step from host buffers keeps two or three sets of device input / output
+ * buffers, each with a captured graph that reads and writes them, and overlaps the upload of step i + 1 and the
+ * download of step i - 1 with the kernels of step i.  A pipe holds the three events that order one set's
+ * upload (copy stream), graph (compute stream) and download (download stream), so that a step costs the host
+ * two calls and no event bookkeeping of its own. */
+struct q4_gpu_pipe {
+    cudaEvent_t in_done, run_done, out_done;
+    bool has_run, has_out;
+};
+extern "C" q4_gpu_pipe *q4_gpu_pipe_create(void) {
+    if (!g_q4.ok) { q4i_fail(Q4E_INIT, "pipe_create: library not initialised"); return nullptr; }
+    q4_gpu_pipe *p = (q4_gpu_pipe *)calloc(1, sizeof(q4_gpu_pipe));
+    if (!p) return nullptr;
+    if (cudaEventCreateWithFlags(&p->in_done, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&p->run_done, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&p->out_done, cudaEventDisableTiming) != cudaSuccess) {
+        q4i_fail(Q4E_CUDA, "pipe_create: event");
+        if (p->in_done) cudaEventDestroy(p->in_done);
+        if (p->run_done) cudaEventDestroy(p->run_done);
+        free(p);
+        return nullptr;
+    }
+    return p;
+}
+extern "C" void q4_gpu_pipe_destroy(q4_gpu_pipe *p) {
+    if (!p) return;
+    cudaEventDestroy(p->in_done);
+    cudaEventDestroy(p->run_done);
+    cudaEventDestroy(p->out_done);
+    free(p);
+}
+/* The step's inputs, pinned host memory -> the set's device buffer, on the copy stream, once the set's previous
+ * graph launch (which read that buffer) has run. */
+extern "C" bool q4_gpu_pipe_upload(q4_gpu_pipe *p, void *dst_d, const void *src_h, size_t n) {
+    if (!g_q4.ok) return q4i_fail(Q4E_INIT, "pipe_upload: library not initialised");
+    Q4_REQUIRE(p && dst_d && src_h && n, "pipe_upload: bad argument");
+    if (p->has_run && !q4i_check(cudaStreamWaitEvent(g_q4.copy_stream, p->run_done, 0), "pipe_upload wait")) return false;
+    return q4i_check(cudaMemcpyAsync(dst_d, src_h, n, cudaMemcpyHostToDevice, g_q4.copy_stream), "pipe_upload copy") &&
+           q4i_check(cudaEventRecord(p->in_done, g_q4.copy_stream), "pipe_upload record");
+}
+/* The set's graph on the compute stream, once its upload has landed and its previous download has left the output
+ * buffer; then the outputs, device -> pinned host memory, on the download stream.  Returns at once. */
+extern "C" bool q4_gpu_pipe_run(q4_gpu_pipe *p, void *graph_exec, void *dst_h, const void *src_d, size_t n) {
+    if (!g_q4.ok) return q4i_fail(Q4E_INIT, "pipe_run: library not initialised");
+    Q4_REQUIRE(p && graph_exec, "pipe_run: bad argument");
+    if (!q4i_check(cudaStreamWaitEvent(g_q4.stream, p->in_done, 0), "pipe_run wait")) return false;
+    if (p->has_out && !q4i_check(cudaStreamWaitEvent(g_q4.stream, p->out_done, 0), "pipe_run wait")) return false;
+    if (!q4i_check(cudaGraphLaunch((cudaGraphExec_t)graph_exec, g_q4.stream), "pipe_run launch") ||
+        !q4i_check(cudaEventRecord(p->run_done, g_q4.stream), "pipe_run record"))
+        return false;
+    p->has_run = true;
+    if (dst_h && src_d && n) {
+        if (!q4i_check(cudaStreamWaitEvent(g_q4.down_stream, p->run_done, 0), "pipe_run wait") ||
+            !q4i_check(cudaMemcpyAsync(dst_h, src_d, n, cudaMemcpyDeviceToHost, g_q4.down_stream), "pipe_run copy") ||
+            !q4i_check(cudaEventRecord(p->out_done, g_q4.down_stream), "pipe_run record"))
+            return false;
+        p->has_out = true;
+    }
+    return true;
+}
+/* Blocks until the set's last download has landed in host memory. */
+extern "C" bool q4_gpu_pipe_sync(q4_gpu_pipe *p) {
+    if (!g_q4.ok || !p) return false;
+    return q4i_check(cudaEventSynchronize(p->has_out ? p->out_done : p->run_done), "pipe_sync");
+}
+
 extern "C" bool q4_hip_qsa_topk_alloc(void) {
     if (!g_q4.ok) return false;
     /* 32 MB of records + 64 Ki counters: one session at the largest supported shape (4 kv heads x

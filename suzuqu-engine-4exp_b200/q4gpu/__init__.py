@@ -27,6 +27,9 @@ SIGNATURES = {
     "q4_hip_stream_sync": (_b, []),
     "q4_hip_copy_h2d": (_b, [_v, _v, _sz]), "q4_hip_copy_wait": (None, []), "q4_gpu_copy_stream": (_v, []),
     "q4_gpu_copy_d2h": (_b, [_v, _v, _sz]), "q4_gpu_download_stream": (_v, []),
+    "q4_gpu_pipe_create": (_v, []), "q4_gpu_pipe_destroy": (None, [_v]),
+    "q4_gpu_pipe_upload": (_b, [_v, _v, _v, _sz]), "q4_gpu_pipe_run": (_b, [_v, _v, _v, _v, _sz]),
+    "q4_gpu_pipe_sync": (_b, [_v]),
     "q4_hip_copy": (_b, [_v, _v, _u64]), "q4_hip_fill": (_b, [_v, _f, _u64]),
     "q4_hip_sync": (None, []), "q4_hip_clear": (None, []),
     "q4_hip_pos_push": (None, [_i32]), "q4_hip_capturing": (_i, []), "q4_hip_pos_dev_ok": (_i, []),

@@ -216,3 +216,51 @@ def test_graph_capture_on_the_legacy_default_stream_is_refused_with_a_reason():
     if g:
         L.q4_hip_graph_free(g)
     q4gpu.use_torch_stream()
+
+
+def test_pipelined_steps_over_two_buffer_sets():
+    """q4_gpu_pipe_*: upload on the copy stream, a captured graph on the compute stream, download on the download
+    stream, ordered by the pipe's events alone; two sets of buffers alternate, every step's result must be that
+    step's input (the graph copies input to output on the device)"""
+    L = lib()
+    assert L.q4_gpu_set_stream(None)
+    n = 1 << 18
+    sets = []
+    for _ in range(2):
+        in_h = torch.empty(n, dtype=torch.float32).pin_memory()
+        out_h = torch.zeros(n, dtype=torch.float32).pin_memory()
+        in_d = torch.zeros(n, device="cuda")
+        out_d = torch.zeros(n, device="cuda")
+        torch.cuda.synchronize()
+        assert L.q4_hip_graph_begin() == 1
+        assert L.q4_hip_copy(out_d.data_ptr(), in_d.data_ptr(), n)
+        g = L.q4_hip_graph_end()
+        assert g
+        pipe = L.q4_gpu_pipe_create()
+        assert pipe
+        sets.append((in_h, out_h, in_d, out_d, g, pipe))
+    steps = 9
+    expect = [None, None]
+    def upload(i):
+        in_h, _, in_d, _, _, pipe = sets[i % 2]
+        if expect[i % 2] is not None:                     # the set's previous result must be read before its input is reused
+            assert L.q4_gpu_pipe_sync(pipe)
+            assert (sets[i % 2][1] == expect[i % 2]).all(), "step %d" % (i - 2)
+        in_h.fill_(float(i + 1))
+        in_h[i] = -3.0
+        expect[i % 2] = in_h.clone()
+        assert L.q4_gpu_pipe_upload(pipe, in_d.data_ptr(), in_h.data_ptr(), 4 * n)
+    upload(0)
+    for i in range(steps):
+        if i + 1 < steps:
+            upload(i + 1)
+        _, out_h, _, out_d, g, pipe = sets[i % 2]
+        assert L.q4_gpu_pipe_run(pipe, g, out_h.data_ptr(), out_d.data_ptr(), 4 * n)
+    for k in range(2):
+        assert L.q4_gpu_pipe_sync(sets[k][5])
+        assert (sets[k][1] == expect[k]).all()
+    assert L.q4_gpu_last_error() == 0
+    for in_h, out_h, in_d, out_d, g, pipe in sets:
+        L.q4_hip_graph_free(g)
+        L.q4_gpu_pipe_destroy(pipe)
+    q4gpu.use_torch_stream()
