@@ -78,6 +78,8 @@ struct DecParams {
     uint32_t xchg_phase;
     const float *new_k, *new_v;   /* fused append of the newest row (native q8_0 store), or null */
     uint32_t pdl;                 /* launched with programmatic stream serialization */
+    uint32_t gridmerge;           /* long scans: every split's record goes to scratch, the unit's blocks meet at a counter,
+                                   * and (head, 32-dim) slices of the merge are shared out among them */
     uint32_t push_bytes;          /* > 0: the launch carries this much extra shared memory and merges by pushing */
     uint32_t push_async;          /* pushes complete an mbarrier of the receiving block (its last 16 bytes) instead of
                                    * meeting at a cluster barrier */
@@ -582,6 +584,93 @@ __device__ __noinline__ void cluster_push_merge(const float *own, const float *r
                 if (mo.gate) o *= 1.f / (1.f + __expf(-mo.gate[off]));
                 mo.out[off] = o;
             }
+        }
+    }
+}
+
+/* ---- merge of a long scan's records by all of the unit's blocks ---------------------------------
+ * A unit with hundreds of splits (a dense scan over 262144 rows: 222 blocks per kv head) used to merge in two
+ * levels, each a fence + atomic + the last block of a group reading 16 records: two serial round trips through L2
+ * behind the slowest block.  Here every block writes its record, the unit's S blocks meet at a counter (they are
+ * all resident: the launcher checks that the grid fits in one wave), and the first gqa * HD / 32 of them each
+ * merge one (head, 32 dims) slice of all S records: the weights once per record, then 16 record lanes x 8 threads
+ * of 4 dims stream the accumulators.  The wait is bounded; the last block to leave re-arms the two counters. */
+constexpr uint32_t GRID_SPIN_LIMIT = 1u << 22;
+template <int HD, int HEADS>
+__device__ __noinline__ void grid_merge(const float *recs, uint32_t S, uint32_t split, uint32_t *ctr, const MergeOut mo,
+                                        float *scr /* >= 256 + 16 * 32 + 8 floats of shared memory */, uint32_t *err) {
+    constexpr int REC = HD + 4, CH = HD / 32;
+    __shared__ uint32_t s_ok;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        atomicAdd(&ctr[0], 1u);
+        uint32_t spins = 0, seen;
+        do {
+            asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(seen) : "l"(ctr) : "memory");
+        } while (seen < S && ++spins < GRID_SPIN_LIMIT);
+        s_ok = seen >= S ? 1u : 0u;
+    }
+    __syncthreads();
+    const bool ok = s_ok != 0u;
+    float *s_w = scr, *s_part = scr + 256, *s_red = scr + 256 + 16 * 32;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (ok)
+        for (uint32_t task = split; task < mo.gqa * CH; task += S) {
+            const uint32_t h = task / CH, d0 = (task % CH) * 32;
+            /* weights of the S records of head h (m in log2 units; an empty record has l = 0) */
+            float mloc = -CUDART_INF_F;
+            for (uint32_t r = threadIdx.x; r < S; r += DEC_THREADS) {
+                const float2 ml = __ldcg(reinterpret_cast<const float2 *>(recs + ((size_t)r * HEADS + h) * REC + HD));
+                if (ml.y > 0.f) mloc = fmaxf(mloc, ml.x);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, o));
+            if (lane == 0) s_red[warp] = mloc;
+            __syncthreads();
+            const float M = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+            const float Mu = M == -CUDART_INF_F ? 0.f : M;
+            float lloc = 0.f;
+            for (uint32_t r = threadIdx.x; r < S; r += DEC_THREADS) {
+                const float2 ml = __ldcg(reinterpret_cast<const float2 *>(recs + ((size_t)r * HEADS + h) * REC + HD));
+                const float w = ml.y > 0.f ? ex2(ml.x - Mu) : 0.f;
+                s_w[r] = w;
+                lloc = fmaf(w, ml.y, lloc);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) lloc += __shfl_xor_sync(0xffffffffu, lloc, o);
+            __syncthreads();                       /* s_red read by everyone, s_w written */
+            if (lane == 0) s_red[4 + warp] = lloc;
+            __syncthreads();
+            const float L = (s_red[4] + s_red[5]) + (s_red[6] + s_red[7]);
+            /* 16 record lanes x 8 threads of 4 dims */
+            const uint32_t q = threadIdx.x >> 3, dq = (threadIdx.x & 7u) * 4u;
+            float4 A = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (uint32_t r = q; r < S; r += 16) {
+                const float w = s_w[r];
+                const float4 x = __ldcg(reinterpret_cast<const float4 *>(recs + ((size_t)r * HEADS + h) * REC + d0 + dq));
+                A.x = fmaf(w, x.x, A.x); A.y = fmaf(w, x.y, A.y); A.z = fmaf(w, x.z, A.z); A.w = fmaf(w, x.w, A.w);
+            }
+            *reinterpret_cast<float4 *>(s_part + q * 32 + dq) = A;
+            __syncthreads();
+            if (threadIdx.x < 8) {
+                float4 T = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int k = 0; k < 16; k++) {
+                    const float4 x = *reinterpret_cast<const float4 *>(s_part + k * 32 + dq);
+                    T.x += x.x; T.y += x.y; T.z += x.z; T.w += x.w;
+                }
+                merge_store<HD>(nullptr, mo, h, d0 + dq, M, L, T);
+            }
+            __syncthreads();
+        }
+    if (threadIdx.x == 0) {
+        if (!ok) atomicOr(err, (uint32_t)Q4E_CUDA);
+        __threadfence();
+        if (atomicAdd(&ctr[1], 1u) == S - 1u) {   /* everyone has passed the meeting point: ready for the next launch */
+            ctr[1] = 0u;
+            __threadfence();
+            ctr[0] = 0u;
         }
     }
 }
@@ -1513,6 +1602,12 @@ q4_decode_k(const DecParams P) {
     const uint32_t grp = split / DEC_GROUP;
     const uint32_t grp_size = min(DEC_GROUP, S - grp * DEC_GROUP);
     float *rec1 = P.scratch + (unit * (size_t)(S + n_groups)) * HEADS * REC;
+    if (P.gridmerge) {
+        merge_records<HD, HEADS>(sm, DEC_WARPS, false, rec1 + (size_t)split * HEADS * REC, mo, mscr);
+        __syncthreads();   /* the warp records in shared memory are no longer needed: their space is the scratch */
+        grid_merge<HD, HEADS>(rec1, S, split, P.counters + unit * (1u + DEC_MAX_SPLIT / DEC_GROUP), mo, sm, P.err);
+        return;
+    }
     float *rec2 = rec1 + (size_t)S * HEADS * REC;
     uint32_t *ctr = P.counters + unit * (1u + DEC_MAX_SPLIT / DEC_GROUP);
     /* one call site for every level keeps a single copy of the merge code in the kernel */
@@ -1623,6 +1718,15 @@ bool launch(const DecParams &p_in, dim3 grid) {
      * SMs instead of three deep over some, was measured: no gain at 1-8 sessions, 3 us slower at 16.) */
     if (p.push_bytes && resident_clusters(smem_base + p.push_bytes) < blocks / p.cluster) p.push_bytes = 0;
     if (!p.push_bytes) p.push_async = 0;
+    if (p.gridmerge) {
+        /* the blocks of a unit wait for one another: only when the whole grid is resident at once */
+        static int occ = -1;
+        if (occ < 0 && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, q4_decode_k<LAY, HD, NHT>, DEC_THREADS, smem_base) != cudaSuccess) {
+            (void)cudaGetLastError();
+            occ = 0;
+        }
+        if (blocks > (uint64_t)occ * (uint64_t)g_q4.sm_count) p.gridmerge = 0;
+    }
     const size_t smem = smem_base + p.push_bytes;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
@@ -1796,6 +1900,12 @@ bool q4i_decode(const Q4DecodeArgs &a) {
         static int bulk = -2;
         if (bulk == -2) { const char *e = getenv("Q4_DEC_BULK"); bulk = e ? atoi(e) : -1; }
         p.bulk_runs = bulk >= 0 ? (bulk ? 1u : 0u) : (a.idx ? 0u : 1u);
+    }
+    {
+        /* Q4_DEC_GRIDMERGE=0: long scans merge in two levels, each by the last block of a group to arrive */
+        static int gm = -1;
+        if (gm < 0) { const char *e = getenv("Q4_DEC_GRIDMERGE"); gm = e ? atoi(e) : 1; }
+        p.gridmerge = (gm && !cluster && S > DEC_GROUP && !a.xchg) ? 1u : 0u;
     }
     p.xchg = a.xchg;
     p.xchg_phase = (uint32_t)a.xchg_phase;

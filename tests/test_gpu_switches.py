@@ -2,7 +2,8 @@
 are read once per process): the merge through global scratch instead of a cluster, the cluster merge that meets
 at a cluster barrier instead of completing the receiver's mbarrier, launches without programmatic dependent
 launch, the driver's default cluster placement, bulk copies forced on for selection lists and off for dense
-scans, and the reference's split-count knob.  Every child runs the same parity tests against the oracle."""
+scans, the reference's split-count knob, and the two-level merge of long scans instead of the merge by all of the
+unit's blocks.  Every child runs the same parity tests against the oracle."""
 import os
 import subprocess
 import sys
@@ -15,11 +16,12 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CASES = ["test_gpu_decode.py::test_config1_ctx4096_reference_check",
          "test_gpu_decode.py::test_qsa_sparse_decode_per_kv_head_lists",
          "test_gpu_decode.py::test_batched_sessions_match_single_session",
+         "test_gpu_decode.py::test_sequence_shards_partial_and_merge",
          "test_gpu_fused_append.py"]
 
 
 @pytest.mark.parametrize("switch", ["Q4_DEC_CLUSTER=0", "Q4_DEC_PUSH_ASYNC=0", "Q4_DEC_PDL=0", "Q4_DEC_CLUSTER_POLICY=0",
-                                    "Q4_DEC_BULK=1", "Q4_DEC_BULK=0", "Q4_DEC_SPLIT_S=5"])
+                                    "Q4_DEC_BULK=1", "Q4_DEC_BULK=0", "Q4_DEC_SPLIT_S=5", "Q4_DEC_GRIDMERGE=0"])
 def test_parity_with_the_switch_set(switch):
     env = dict(os.environ)
     name, value = switch.split("=")
