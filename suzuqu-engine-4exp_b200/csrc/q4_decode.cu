@@ -1812,7 +1812,7 @@ bool q4i_decode(const Q4DecodeArgs &a) {
         if (!a.idx && a.n_units > 1) S = S > (steps + 63u) / 64u ? S : (steps + 63u) / 64u;
         /* every warp keeps at least one tile of a list, four of a dense scan (measured at 16384 / 32768 rows:
          * 12.0 / 14.6 us per layer against 13.5 / 15.4 with one tile per warp; no difference from 49152 rows on) */
-        const uint32_t per_block = a.idx ? DEC_WARPS : 4u * DEC_WARPS;
+        const uint32_t per_block = (a.idx || a.xchg) ? DEC_WARPS : 4u * DEC_WARPS;   /* the exchange form merges in two levels: finer splits serve it better (8 ranks x 32768 rows: 24.7 against 26.0 us) */
         const uint32_t cap = (steps + per_block - 1u) / per_block;
         if (S > cap) S = cap;
     }
