@@ -35,9 +35,13 @@
  *   and the softmax weights (fp16, and the denominator sums the same rounded weights).
  *
  * grid = (splits, kv heads, units).  Every block reduces its warps' partials in shared memory.  Up to
- * 8 splits form one thread-block cluster and merge through distributed shared memory (no scratch, no
- * atomics); more splits write (acc, m, l) records to scratch and the last block to arrive per group
- * of 16 (atomic counter) merges them, two levels at most.  Either way the layer is one launch.
+ * 16 splits form one thread-block cluster and merge through distributed shared memory (no scratch, no
+ * atomics: every block pushes the heads of its record to the blocks that own them, and the pushes
+ * complete an mbarrier there).  More splits write (acc, m, l) records to scratch; when the whole grid
+ * is resident the unit's blocks meet at a counter and share out (head, 32-dim) slices of the merge,
+ * otherwise -- and in the sequence-sharded exchange, whose last block must hold the rank's record --
+ * the last block to arrive per group of 16 merges, two levels at most.  Either way the layer is one
+ * launch.
  */
 #include <cuda_bf16.h>
 #include <math_constants.h>
